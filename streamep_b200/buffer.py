@@ -1,0 +1,476 @@
+"""`Buffer`: expert-parallel dispatch / combine over NVLink peer memory, and the
+`StreamingHandle` that carries one dispatch's state.
+
+Public surface and semantics follow the reference (stream_ep/buffer.py:14-782):
+``Buffer(group, num_nvl_bytes, ...)``, ``dispatch`` / ``dispatch_grads`` /
+``combine`` / ``combine_grads``, the launch-gate helpers, ``set_num_sms`` and the
+``get_*_config`` tables.  The transport underneath is different: there are no
+ring buffers and no receiver kernels.  Every rank maps every peer's *symmetric
+arena*; dispatch pushes each token row directly into its final, expert-major,
+128-row-padded pool slot in the owner's HBM and release-adds the owner's
+per-tile arrival counter; combine pulls the partial rows back and reduces them
+in fp32.  The layer-level fused kernels (see ``stream_moe``) reuse the same
+records and counters.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Any, List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _ext
+from .errors import StreamEPError, StreamEPTimeout
+
+topk_idx_t = torch.int64
+
+# launch-gate ids of the native runtime
+_GATE_DISPATCH, _GATE_DISPATCH_GRADS, _GATE_KERNEL_Y, _GATE_KERNEL_A_BWD = 0, 1, 2, 3
+
+
+def _C():
+    return _ext.load()
+
+
+def __getattr__(name):  # Config / EventHandle live in the native module
+    if name in ("Config", "EventHandle"):
+        return getattr(_C(), name)
+    raise AttributeError(name)
+
+
+@dataclass
+class StreamingHandle:
+    """All per-dispatch state (reference: stream_ep/buffer.py:14-95, same field
+    names and meanings).
+
+    Pool layout: rows are expert-major; expert ``e`` owns rows
+    ``[expert_pool_block_offset[e] * tile_m, expert_pool_block_offset[e+1] * tile_m)``
+    of which the first ``expert_frequency[e]`` are valid; padding rows have
+    ``pool_recv_token == -1``.
+    """
+    pool: torch.Tensor                        # [TK_padded, hidden] bf16
+    pool_topk_weight: torch.Tensor            # [TK_padded] f32
+    pool_recv_token: torch.Tensor             # [TK_padded] i32 (-1 = padding)
+    pool_k_slot: torch.Tensor                 # [TK_padded] i32 (-1 = padding)
+    send_head: torch.Tensor                   # [T, R] i32, gap-encoded stream positions
+    is_token_in_rank: torch.Tensor            # [T, R] bool
+    rank_prefix_matrix: torch.Tensor          # [R, R] i32 (own column)
+    channel_prefix_matrix: torch.Tensor       # [R, C] i32
+    recv_channel_prefix_matrix: torch.Tensor  # [R, C] i32
+    expert_frequency: torch.Tensor            # [E_local] i32
+    expert_pool_block_offset: torch.Tensor    # [E_local + 1] i32 (tile units)
+    base_pool: torch.Tensor                   # [C, R, E_local] i32
+    seen_per_substream: torch.Tensor          # [C, R, E_local] i32
+    tile_id_to_expert: torch.Tensor           # [total_tiles] i32
+    pool_arrival_target: torch.Tensor         # [total_tiles] i32
+    pool_arrival_count: torch.Tensor          # [total_tiles] i32
+    k_local_remaining: torch.Tensor           # [T_recv] i32
+    y_done_per_token: torch.Tensor            # [T_recv] i64
+    o: torch.Tensor                           # [T_recv, hidden] bf16, zero
+    recv_token_to_slots: torch.Tensor         # [T_recv, K] i32 (-1 = other rank)
+    k_local_total: torch.Tensor               # [T_recv] i32
+    total_tiles: int
+    tile_m: int
+    TK_padded: int
+    dispatch_seq: int
+    # native per-dispatch state: sender-side routing (destination slot of every pair, recv-token
+    # id of every token at every rank) and the per-slot source table used by the fused combine
+    _dispatch_out: Any = None
+
+    # Aliases in the wording of the reference's README (tile_ready / a_ready): a tile is ready when
+    # its arrival count equals its target.
+    @property
+    def tile_ready(self) -> torch.Tensor:
+        return self.pool_arrival_count == self.pool_arrival_target
+
+    @property
+    def pool_src(self) -> torch.Tensor:
+        """[TK_padded, 2] i32: (source rank, source token) of every slot (-1 = padding)."""
+        return self._dispatch_out.pool_src
+
+    @property
+    def num_recv_tokens(self) -> int:
+        return self._dispatch_out.num_recv_tokens
+
+
+class Buffer:
+    """Symmetric-memory communication buffer for one expert-parallel group.
+
+    Arguments follow stream_ep/buffer.py:125-151.  ``num_nvl_bytes`` sizes the
+    symmetric arena: unlike the reference's ring buffers, the arena holds the
+    pools, per-slot arrays and outputs that peers write into, so it must cover
+    what all layers keep alive between forward and backward (see
+    ``Buffer.get_arena_size_hint``).  ``num_rdma_bytes`` must be 0: the RDMA
+    path is out of scope on one NVSwitch domain.
+    """
+
+    num_sms: int = 80
+    _num_sms_explicit: bool = False
+
+    def __init__(self, group, num_nvl_bytes: int = 0, num_rdma_bytes: int = 0,
+                 allow_mnnvl: bool = False, use_fabric: bool = False,
+                 explicitly_destroy: bool = False, enable_shrink: bool = False,
+                 comm=None, *, timeout_ms: Optional[int] = None,
+                 _local: Optional[Tuple["LocalWorld", int]] = None) -> None:
+        import torch.distributed as dist
+
+        if num_rdma_bytes:
+            raise StreamEPError("the internode (RDMA) path is not available: one NVSwitch domain only")
+        self._local = _local
+        if _local is not None:
+            world, rank = _local
+            self.rank, self.group_size, self.group = rank, world.num_ranks, world
+            all_gather_object = None
+        elif group is not None:
+            self.rank, self.group_size, self.group = group.rank(), group.size(), group
+
+            def all_gather_object(obj):
+                out = [None] * self.group_size
+                dist.all_gather_object(out, obj, group)
+                return out
+        elif comm is not None:
+            self.rank, self.group_size, self.group = comm.Get_rank(), comm.Get_size(), comm
+
+            def all_gather_object(obj):
+                return comm.allgather(obj)
+        else:
+            raise ValueError("Either 'group' or 'comm' must be provided.")
+        if self.group_size not in (1, 2, 4, 8):
+            raise StreamEPError(f"unsupported number of EP ranks: {self.group_size} (1, 2, 4 or 8)")
+        Buffer.autopick_num_sms(self.group_size)
+        from .utils.nvlink import check_nvlink_connections
+        if _local is None:
+            check_nvlink_connections(group if group is not None else comm)
+
+        self.num_nvl_bytes = int(num_nvl_bytes)
+        self.num_rdma_bytes = 0
+        self.explicitly_destroy = explicitly_destroy
+        self.enable_shrink = enable_shrink
+        self.num_channels = max(1, min(Buffer.num_sms // 2, _C().MAX_CHANNELS))
+        if timeout_ms is None:
+            timeout_ms = int(os.environ.get("STREAM_EP_TIMEOUT_MS", "10000"))
+        arena_bytes = self.num_nvl_bytes if self.num_nvl_bytes > 0 else int(
+            os.environ.get("STREAM_EP_ARENA_BYTES", str(2 << 30)))
+        self.runtime = _C().Runtime(self.rank, self.group_size, arena_bytes, self.num_channels,
+                                    _C().MAX_EXPERTS, timeout_ms)
+        if _local is None:
+            device_ids = all_gather_object(self.runtime.get_local_device_id())
+            handles = all_gather_object(self.runtime.get_local_ipc_handle() if self.group_size > 1 else None)
+            self.runtime.sync(device_ids, handles)
+            assert self.runtime.is_available()
+        self._next_seq = 0
+        self._push_blocks = 0  # 0 = auto
+
+    # ------------------------------------------------------------------ lifecycle
+    def destroy(self):
+        assert self.explicitly_destroy, "`explicitly_destroy` flag must be set"
+        self.runtime.destroy()
+        self.runtime = None
+
+    def state_dict(self) -> dict:
+        """The only state that matters across iterations is the sequence counter
+        (stream_ep/buffer.py:255-261); a resumed process builds a fresh Buffer."""
+        return {"next_seq": self._next_seq}
+
+    def load_state_dict(self, state: dict) -> None:
+        self._next_seq = int(state["next_seq"])
+
+    # ------------------------------------------------------------------ failure reporting
+    def check_status(self) -> None:
+        """Synchronise the device and raise :class:`StreamEPTimeout` if any bounded
+        device wait gave up since the last check.  The context stays usable."""
+        msg = self.runtime.poll_status(True)
+        if msg:
+            raise StreamEPTimeout(f"rank {self.rank}: {msg}")
+
+    def set_timeout_ms(self, ms: int) -> None:
+        self.runtime.set_timeout_ms(int(ms))
+
+    # ------------------------------------------------------------------ symmetric memory
+    def alloc_symmetric(self, shape: Sequence[int], dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """A tensor in the peer-mapped arena.  Gates and rows that peers read while they
+        are still being produced (``o``, ``y_done_per_token``, ``dL_dx_per_r``,
+        ``bwd_a_done_per_token``) must live here; the block returns to the arena when
+        the tensor is garbage collected."""
+        return self.runtime.alloc_symmetric(list(shape), dtype, zero)
+
+    def get_local_buffer_tensor(self, dtype: torch.dtype, size: Optional[torch.Size] = None,
+                                offset: int = 0, use_rdma_buffer: bool = False) -> torch.Tensor:
+        """API parity with stream_ep/buffer.py:381-400: a scratch tensor in the arena."""
+        assert not use_rdma_buffer, "no RDMA buffer on one NVSwitch domain"
+        numel = size.numel() if size is not None else 1024
+        t = self.alloc_symmetric([offset + numel], dtype)
+        t = t[offset:]
+        return t if size is None else t.view(size)
+
+    @staticmethod
+    def get_arena_size_hint(num_tokens: int, hidden: int, num_topk: int, num_ranks: int,
+                            num_local_experts: int, layers_in_flight: int = 1,
+                            imbalance: float = 1.5) -> int:
+        """Bytes of symmetric memory for ``layers_in_flight`` layers (forward state
+        kept until backward) plus one backward's transients."""
+        per_layer = _C().layer_bytes_hint(num_tokens, hidden, num_topk, num_ranks, num_local_experts, imbalance)
+        return int(per_layer * (layers_in_flight + 1.5))
+
+    # ------------------------------------------------------------------ launch gates
+    def _raw(self, stream):
+        return (stream if stream is not None else torch.cuda.current_stream()).cuda_stream
+
+    def wait_dispatch_main_started(self, stream=None) -> None:
+        """Hold ``stream`` at the GPU front-end until the last dispatch kernel is resident
+        (reference: stream_ep/buffer.py:274-284)."""
+        self.runtime.gate_wait_started(_GATE_DISPATCH, self._raw(stream))
+
+    def wait_dispatch_grads_started(self, stream=None) -> None:
+        self.runtime.gate_wait_started(_GATE_DISPATCH_GRADS, self._raw(stream))
+
+    def wait_kernel_y_started(self, stream=None) -> None:
+        self.runtime.gate_wait_started(_GATE_KERNEL_Y, self._raw(stream))
+
+    def wait_kernel_a_bwd_started(self, stream=None) -> None:
+        self.runtime.gate_wait_started(_GATE_KERNEL_A_BWD, self._raw(stream))
+
+    def bump_kernel_y_issued(self) -> None:
+        self.runtime.gate_bump_issued(_GATE_KERNEL_Y)
+
+    def bump_kernel_a_bwd_issued(self) -> None:
+        self.runtime.gate_bump_issued(_GATE_KERNEL_A_BWD)
+
+    def kernel_y_started_flag_view(self) -> torch.Tensor:
+        return self.runtime.gate_flag_tensor(_GATE_KERNEL_Y)
+
+    def kernel_a_bwd_started_flag_view(self) -> torch.Tensor:
+        return self.runtime.gate_flag_tensor(_GATE_KERNEL_A_BWD)
+
+    # ------------------------------------------------------------------ config policy
+    @staticmethod
+    def is_sm90_compiled() -> bool:
+        return False
+
+    @staticmethod
+    def is_sm100_compiled() -> bool:
+        return bool(_C().is_sm100_compiled())
+
+    @staticmethod
+    def set_num_sms(new_num_sms: int) -> None:
+        assert new_num_sms % 2 == 0, "The SM count must be even"
+        Buffer.num_sms = new_num_sms
+        Buffer._num_sms_explicit = True
+
+    @staticmethod
+    def autopick_num_sms(group_size: int) -> int:
+        """80 for one or two nodes, 64 beyond (stream_ep/buffer.py:363-379).  Here the
+        value sets the number of channels (num_sms // 2) of the deterministic pool
+        layout and the grid of the stand-alone push / pull kernels."""
+        if not Buffer._num_sms_explicit:
+            nodes = (group_size + 7) // 8
+            Buffer.num_sms = 80 if nodes <= 2 else 64
+        return Buffer.num_sms
+
+    @staticmethod
+    def get_dispatch_config(num_ranks: int):
+        Buffer.autopick_num_sms(num_ranks)
+        table = {1: (24, 256), 2: (24, 256), 4: (6, 256), 8: (6, 256)}
+        assert num_ranks in table, f"Unsupported number of EP ranks: {num_ranks}"
+        s, r = table[num_ranks]
+        return _C().Config(Buffer.num_sms, s, r, 6, 128)
+
+    @staticmethod
+    def get_combine_config(num_ranks: int):
+        Buffer.autopick_num_sms(num_ranks)
+        table = {1: (10, 256), 2: (10, 256), 4: (9, 256), 8: (4, 256)}
+        assert num_ranks in table, f"Unsupported number of EP ranks: {num_ranks}"
+        s, r = table[num_ranks]
+        return _C().Config(Buffer.num_sms, s, r, 6, 128)
+
+    def _is_internode(self) -> bool:
+        return False
+
+    def _blocks(self, config) -> int:
+        if self._push_blocks:
+            return self._push_blocks
+        n = config.num_sms if config is not None else Buffer.num_sms
+        return max(1, int(n))
+
+    # ------------------------------------------------------------------ dispatch
+    def _dispatch_begin(self, x, topk_idx, topk_weights, num_experts, tile_m, dispatch_seq):
+        if dispatch_seq is None:
+            self._next_seq += 1
+            seq = self._next_seq
+        else:
+            seq = int(dispatch_seq)
+        if topk_idx.dtype != torch.int64:
+            topk_idx = topk_idx.to(torch.int64)
+        st = self.runtime.dispatch_begin(x.contiguous(), topk_idx.contiguous(),
+                                         topk_weights.contiguous().float(), num_experts, tile_m, seq)
+        return st, seq
+
+    def _make_handle(self, st, is_token_in_rank, seq, tile_m) -> StreamingHandle:
+        return StreamingHandle(
+            pool=st.pool, pool_topk_weight=st.pool_topk_weight, pool_recv_token=st.pool_recv_token,
+            pool_k_slot=st.pool_k_slot, send_head=st.send_head,
+            is_token_in_rank=is_token_in_rank if is_token_in_rank is not None else st.is_token_in_rank,
+            rank_prefix_matrix=st.rank_prefix_matrix, channel_prefix_matrix=st.channel_prefix_matrix,
+            recv_channel_prefix_matrix=st.recv_channel_prefix_matrix,
+            expert_frequency=st.expert_frequency, expert_pool_block_offset=st.expert_pool_block_offset,
+            base_pool=st.base_pool, seen_per_substream=st.seen_per_substream,
+            tile_id_to_expert=st.tile_id_to_expert, pool_arrival_target=st.pool_arrival_target,
+            pool_arrival_count=st.pool_arrival_count, k_local_remaining=st.k_local_remaining,
+            y_done_per_token=st.y_done_per_token, o=st.o, recv_token_to_slots=st.recv_token_to_slots,
+            k_local_total=st.k_local_total, total_tiles=st.total_tiles, tile_m=tile_m,
+            TK_padded=st.total_tiles * tile_m, dispatch_seq=seq, _dispatch_out=st)
+
+    def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
+                 is_token_in_rank: Optional[torch.Tensor], num_experts: int, *,
+                 expert_alignment: int = 1, tile_m: int = 128, dispatch_seq: Optional[int] = None,
+                 config=None, launch_push: bool = True):
+        """Pool-layout dispatch (reference: stream_ep/buffer.py:493-610).
+
+        Two kernels and one host poll: the metadata kernel (count exchange +
+        layout for every rank), a host read of ``total_tiles`` / ``T_recv`` to size
+        the pool exactly, and the push kernel.  Runs on the current stream.
+        Returns ``(pool, handle, metadata_done_event)``; the event is recorded
+        before the push kernel so consumers can read metadata while rows are
+        still arriving and gate per tile on ``pool_arrival_count``.
+
+        ``launch_push=False`` stops before the push kernel (the fused
+        dispatch+GEMM-A kernel of ``stream_moe`` ships the rows itself).
+        """
+        assert expert_alignment == 1, "expert_alignment other than 1 is not supported"
+        st, seq = self._dispatch_begin(x, topk_idx, topk_weights, num_experts, tile_m, dispatch_seq)
+        self.runtime.dispatch_metadata(st, 3)
+        self.runtime.dispatch_allocate(st)
+        if launch_push:
+            cfg = self.get_dispatch_config(self.group_size) if config is None else config
+            self.runtime.dispatch_push(st, 7, self._blocks(cfg))
+        handle = self._make_handle(st, is_token_in_rank, seq, tile_m)
+        return st.pool, handle, st.metadata_done_event
+
+    # ------------------------------------------------------------------ dispatch_grads
+    def dispatch_grads(self, handle: StreamingHandle, dL_dy: torch.Tensor, *,
+                       dispatch_seq: Optional[int] = None, config=None, launch_push: bool = True):
+        """Backward dispatch along the forward routing (reference:
+        stream_ep/buffer.py:613-667).  Returns ``(dL_do_pool,
+        bwd_dispatch_arrival_count, grads_started_event)``."""
+        st = handle._dispatch_out
+        g = self.runtime.grads_begin(st)
+        if launch_push:
+            cfg = self.get_dispatch_config(self.group_size) if config is None else config
+            self.runtime.grads_push(st, g, dL_dy.contiguous(), 7, self._blocks(cfg))
+        handle._grads_state = g
+        return g.dl_do_pool, g.bwd_dispatch_arrival_count, g.started_event
+
+    # ------------------------------------------------------------------ combine
+    def combine(self, x: torch.Tensor, handle: StreamingHandle, *, combine_seq: Optional[int] = None,
+                config=None) -> Tuple[torch.Tensor, None]:
+        """Reduce per-recv-token rows back to their source tokens (reference:
+        stream_ep/buffer.py:670-722).  Each source rank waits, per token and per
+        contributing rank, for ``handle.y_done_per_token[r] >= combine_seq`` in the
+        owner's memory, then reads the row over NVLink and accumulates in fp32."""
+        seq = handle.dispatch_seq if combine_seq is None else combine_seq
+        st = handle._dispatch_out
+        c = self.runtime.combine_begin(st, x, handle.y_done_per_token, None, True)
+        cfg = self.get_combine_config(self.group_size) if config is None else config
+        self.runtime.combine_launch(st, c, True, int(seq), 7, self._blocks(cfg))
+        return c.out, None
+
+    def combine_grads(self, dL_dx_per_r: torch.Tensor, handle: StreamingHandle,
+                      weight_grads: torch.Tensor, bwd_a_done_per_token: torch.Tensor, *,
+                      dispatch_seq: Optional[int] = None, config=None):
+        """Backward combine (reference: stream_ep/buffer.py:725-780): returns
+        ``(dL_dx [T, H] bf16, dL_dtopk_weights [T, K] f32)``."""
+        seq = handle.dispatch_seq if dispatch_seq is None else dispatch_seq
+        st = handle._dispatch_out
+        c = self.runtime.combine_begin(st, dL_dx_per_r, bwd_a_done_per_token, weight_grads, False)
+        cfg = self.get_combine_config(self.group_size) if config is None else config
+        self.runtime.combine_launch(st, c, False, int(seq), 7, self._blocks(cfg))
+        return c.out, c.out_topk_weights
+
+    def barrier(self) -> None:
+        """Device-side barrier over the group on the current stream (bounded wait)."""
+        self.runtime.barrier()
+
+
+class LocalWorld:
+    """Several ranks emulated in ONE process on ONE device.
+
+    Kernels of different ranks that wait on one another must never run as
+    separate launches on one GPU, so every collective is issued phase by phase:
+    first the phase that only writes (count exchange, record publish, row push)
+    for all ranks, then the phase that reads.  No kernel ever waits for a kernel
+    that has not been launched yet.  Used by the single-GPU tests of the
+    multi-rank data paths; production runs one process per GPU.
+    """
+
+    def __init__(self, num_ranks: int, arena_bytes: int = 256 << 20, timeout_ms: int = 2000):
+        self.num_ranks = num_ranks
+        self.buffers: List[Buffer] = [
+            Buffer(None, arena_bytes, _local=(self, r), timeout_ms=timeout_ms) for r in range(num_ranks)]
+        ptrs = [b.runtime.get_local_base_ptr() for b in self.buffers]
+        for b in self.buffers:
+            b.runtime.sync_local(ptrs)
+
+    def size(self):
+        return self.num_ranks
+
+    def check_status(self):
+        for b in self.buffers:
+            b.check_status()
+
+    def dispatch(self, xs, topk_idxs, topk_weights, num_experts, tile_m=128, seqs=None, push=True):
+        R = self.num_ranks
+        sts = []
+        for r, b in enumerate(self.buffers):
+            sts.append(b._dispatch_begin(xs[r], topk_idxs[r], topk_weights[r], num_experts, tile_m,
+                                         None if seqs is None else seqs[r]))
+        for (st, _), b in zip(sts, self.buffers):
+            b.runtime.dispatch_metadata(st, 1)
+        for (st, _), b in zip(sts, self.buffers):
+            b.runtime.dispatch_metadata(st, 2)
+            b.runtime.dispatch_allocate(st)
+        if push:
+            for (st, _), b in zip(sts, self.buffers):
+                b.runtime.dispatch_push(st, 1, 1)
+            for (st, _), b in zip(sts, self.buffers):
+                b.runtime.dispatch_push(st, 2, b._blocks(None))
+            for (st, _), b in zip(sts, self.buffers):
+                b.runtime.dispatch_push(st, 4, 8)
+        return [b._make_handle(st, None, seq, tile_m) for (st, seq), b in zip(sts, self.buffers)]
+
+    def publish_dispatch_records(self, handles):
+        for h, b in zip(handles, self.buffers):
+            b.runtime.dispatch_push(h._dispatch_out, 1, 1)
+
+    def dispatch_grads(self, handles, dL_dys, push=True):
+        gs = [b.runtime.grads_begin(h._dispatch_out) for h, b in zip(handles, self.buffers)]
+        for h, g in zip(handles, gs):
+            h._grads_state = g
+        if push:
+            for h, g, d, b in zip(handles, gs, dL_dys, self.buffers):
+                b.runtime.grads_push(h._dispatch_out, g, d.contiguous(), 1, 1)
+            for h, g, d, b in zip(handles, gs, dL_dys, self.buffers):
+                b.runtime.grads_push(h._dispatch_out, g, d.contiguous(), 2, b._blocks(None))
+            for h, g, d, b in zip(handles, gs, dL_dys, self.buffers):
+                b.runtime.grads_push(h._dispatch_out, g, d.contiguous(), 4, 8)
+        return [(g.dl_do_pool, g.bwd_dispatch_arrival_count) for g in gs]
+
+    def combine(self, xs, handles, seqs=None):
+        cs = [b.runtime.combine_begin(h._dispatch_out, x, h.y_done_per_token, None, True)
+              for x, h, b in zip(xs, handles, self.buffers)]
+        for c, h, b in zip(cs, handles, self.buffers):
+            b.runtime.combine_launch(h._dispatch_out, c, True, h.dispatch_seq if seqs is None else seqs[b.rank], 1, 1)
+        for c, h, b in zip(cs, handles, self.buffers):
+            b.runtime.combine_launch(h._dispatch_out, c, True, h.dispatch_seq if seqs is None else seqs[b.rank], 2,
+                                     b._blocks(None))
+        return [c.out for c in cs]
+
+    def combine_grads(self, dxs, handles, weight_grads, dones, seqs=None):
+        cs = [b.runtime.combine_begin(h._dispatch_out, x, d, w, False)
+              for x, h, w, d, b in zip(dxs, handles, weight_grads, dones, self.buffers)]
+        for c, h, b in zip(cs, handles, self.buffers):
+            b.runtime.combine_launch(h._dispatch_out, c, False, h.dispatch_seq if seqs is None else seqs[b.rank], 1, 1)
+        for c, h, b in zip(cs, handles, self.buffers):
+            b.runtime.combine_launch(h._dispatch_out, c, False, h.dispatch_seq if seqs is None else seqs[b.rank], 2,
+                                     b._blocks(None))
+        return [(c.out, c.out_topk_weights) for c in cs]

@@ -1,0 +1,663 @@
+// Communication kernels: dispatch metadata (count exchange + deterministic pool layout), tile
+// metadata fill, push dispatch (forward rows / backward gradient rows), pull combine, device
+// barrier, test tile producer and pool <-> recv row copies.
+//
+// Design (differs from the reference on purpose): there are no ring buffers and no receiver
+// CTAs.  Every rank learns all ranks' per-(channel, expert) pair counts, derives every
+// destination's pool layout itself, and pushes each token row straight into its final pool slot
+// in the owner's HBM with 16-byte peer stores, then release-adds the owner's per-tile arrival
+// counter.  Reference counterparts: csrc/kernels/intranode.cu:124-440 (metadata), :551-599 (tile
+// fill), :601-1106 (dispatch), :1161-1439 (dispatch_grads), :1505-1880 (combine),
+// csrc/kernels/runtime.cu:18-31 (barrier).
+#include <cstdio>
+
+#include "comm_common.cuh"
+
+namespace sep {
+
+ControlLayout make_control_layout(int num_ranks, int num_channels, int num_experts_cap) {
+  ControlLayout c{};
+  c.num_ranks = num_ranks;
+  c.num_channels = num_channels;
+  c.num_experts_cap = num_experts_cap;
+  size_t off = 0;
+  auto take = [&](size_t bytes) { size_t o = off; off += (bytes + 255) / 256 * 256; return o; };
+  c.flags = take(sizeof(int) * kNumKinds * kMaxRanks);
+  c.mailbox = take(sizeof(unsigned long long) * kNumKinds * 2 * kMaxRanks * kMailboxWords);
+  c.inbox_counts = take(sizeof(int) * 2 * kMaxRanks * num_channels * num_experts_cap);
+  c.inbox_tokens = take(sizeof(int) * 2 * kMaxRanks * num_channels * kMaxRanks);
+  c.total_bytes = off;
+  return c;
+}
+
+// =============================================================================================
+// Metadata
+// =============================================================================================
+constexpr int kMetaThreads = 1024;
+
+__device__ __forceinline__ int warp_excl_scan(int v, int lane, int& total) {
+  int x = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  total = __shfl_sync(0xffffffffu, x, 31);
+  return x - v;
+}
+
+__global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(const MetadataParams p) {
+  __shared__ int s_hist[kMaxExperts];          // phase A: running per-expert count; phase B: freq
+  __shared__ int s_off[kMaxExperts];           // phase B: tile offset of each expert inside its owner
+  __shared__ int s_u[kMaxRanks];               // phase A: per-dst token count of this channel
+  __shared__ int s_U[kMaxRanks][kMaxRanks];    // phase B: tokens from src to dst
+  __shared__ int s_total_tiles[kMaxRanks];
+  __shared__ int s_is_last;
+  __shared__ int s_ok;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int R = p.num_ranks, K = p.num_topk, E = p.num_experts, C = p.num_channels;
+  const int EL = E / R, T = p.num_tokens;
+  const int parity = p.epoch & 1;
+  const int per = (T + C - 1) / C;
+  void* own = p.peer_base[p.rank];
+
+  if (p.phase_mask & 1) {
+    const int c = blockIdx.x;
+    const int lo = min(per * c, T), hi = min(lo + per, T);
+    for (int e = tid; e < E; e += blockDim.x) s_hist[e] = 0;
+    if (tid < kMaxRanks) s_u[tid] = 0;
+    __syncthreads();
+    if (warp == 0) {
+      // Order-preserving rank of every pair inside its (channel, expert) substream.
+      const int n = (hi - lo) * K;
+      for (int base = 0; base < n; base += 32) {
+        const int i = base + lane;
+        long long e = -1;
+        if (i < n) e = p.topk_idx[static_cast<size_t>(lo) * K + i];
+        const bool valid = (e >= 0 && e < E);
+        const int key = valid ? static_cast<int>(e) : (-1 - lane);
+        const unsigned peers = __match_any_sync(0xffffffffu, key);
+        int rank_in = -1;
+        if (valid) {
+          rank_in = s_hist[e] + __popc(peers & ((1u << lane) - 1u));
+        }
+        __syncwarp();
+        if (valid && (__ffs(peers) - 1) == lane) s_hist[e] += __popc(peers);
+        __syncwarp();
+        if (i < n) p.pair_rank[static_cast<size_t>(lo) * K + i] = rank_in;
+      }
+    } else if (warp <= R) {
+      // Order-preserving rank of every token among the channel's tokens that go to rank d.
+      const int d = warp - 1;
+      int run = 0;
+      for (int base = lo; base < hi; base += 32) {
+        const int t = base + lane;
+        bool hit = false;
+        if (t < hi) {
+          for (int k = 0; k < K; ++k) {
+            const long long e = p.topk_idx[static_cast<size_t>(t) * K + k];
+            hit |= (e >= 0 && e < E && static_cast<int>(e / EL) == d);
+          }
+        }
+        const unsigned m = __ballot_sync(0xffffffffu, hit);
+        if (t < hi) {
+          p.token_rank_in_channel[static_cast<size_t>(t) * R + d] = hit ? run + __popc(m & ((1u << lane) - 1u)) : -1;
+          p.is_token_in_rank[static_cast<size_t>(t) * R + d] = hit ? 1 : 0;
+        }
+        run += __popc(m);
+      }
+      if (lane == 0) s_u[d] = run;
+    }
+    __syncthreads();
+    // Ship this channel's count rows to every rank (own included).
+    for (int i = tid; i < R * E; i += blockDim.x) {
+      const int peer = i / E, e = i - peer * E;
+      ctl_inbox_counts(p.peer_base[peer], p.ctl, parity, p.rank, c)[e] = s_hist[e];
+    }
+    if (tid < R * kMaxRanks) {
+      const int peer = tid / kMaxRanks, d = tid % kMaxRanks;
+      ctl_inbox_tokens(p.peer_base[peer], p.ctl, parity, p.rank, c)[d] = (d < R) ? s_u[d] : 0;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+      const int old = atomicAdd(p.blocks_done, 1);
+      s_is_last = (old == static_cast<int>(gridDim.x) - 1);
+    }
+    __syncthreads();
+    if (!s_is_last) return;
+    __threadfence_system();
+    if (tid < R) flags_signal(p.peer_base, p.ctl, kKindMetadata, p.epoch, p.rank, tid);
+    if (tid == 0) *p.blocks_done = 0;
+    if (!(p.phase_mask & 2)) return;
+  } else if (blockIdx.x != 0) {
+    return;
+  }
+
+  // ------------------------------------------------------------------ phase B (one block)
+  if (tid == 0) s_ok = 1;
+  __syncthreads();
+  if (tid < R) {
+    if (!flags_wait(own, p.ctl, kKindMetadata, p.epoch, tid, p.wait_budget_ns, p.status, kKernelMetadata,
+                    p.rank, kStatusTimeoutBarrier))
+      s_ok = 0;
+  }
+  __syncthreads();
+  if (!s_ok) {
+    if (tid == 0) {   // unblock the host poll with an error marker
+      p.host->total_tiles = -1;
+      p.host->num_recv_tokens = -1;
+      __threadfence_system();
+      p.host->epoch = p.epoch;
+    }
+    return;
+  }
+  const int num_warps = blockDim.x >> 5;
+  // 1. expert frequencies over all sources and channels
+  for (int e = warp; e < E; e += num_warps) {
+    int acc = 0;
+    for (int i = lane; i < R * C; i += 32) {
+      const int s = i / C, c = i - s * C;
+      acc += ctl_inbox_counts(own, p.ctl, parity, s, c)[e];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) s_hist[e] = acc;
+  }
+  // tokens from s to d
+  if (tid < R * R) {
+    const int s = tid / R, d = tid % R;
+    int acc = 0;
+    for (int c = 0; c < C; ++c) acc += ctl_inbox_tokens(own, p.ctl, parity, s, c)[d];
+    s_U[s][d] = acc;
+  }
+  __syncthreads();
+  // 2. per-owner tile offsets
+  if (tid < R) {
+    int run = 0;
+    for (int el = 0; el < EL; ++el) {
+      const int e = tid * EL + el;
+      s_off[e] = run;
+      run += (s_hist[e] + p.tile_m - 1) / p.tile_m;
+    }
+    s_total_tiles[tid] = run;
+    p.peer_total_tiles[tid] = run;
+    int recv = 0;
+    for (int s = 0; s < R; ++s) recv += s_U[s][tid];
+    p.peer_num_recv[tid] = recv;
+  }
+  __syncthreads();
+  // 3. host-visible sizes first, so the host poll overlaps the rest of this kernel
+  if (tid < EL) {
+    p.host->recv_per_expert[tid] = s_hist[p.rank * EL + tid];
+    p.expert_frequency[tid] = s_hist[p.rank * EL + tid];
+    p.expert_pool_block_offset[tid] = s_off[p.rank * EL + tid];
+  }
+  if (tid == 0) {
+    p.expert_pool_block_offset[EL] = s_total_tiles[p.rank];
+    int recv = 0;
+    for (int s = 0; s < R; ++s) recv += s_U[s][p.rank];
+    p.host->total_tiles = s_total_tiles[p.rank];
+    p.host->num_recv_tokens = recv;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence_system();
+    p.host->epoch = p.epoch;
+  }
+  // 4. substream bases: exclusive scan over (channel, source) in lexicographic order
+  for (int e = warp; e < E; e += num_warps) {
+    const int owner = e / EL, el = e - owner * EL;
+    int carry = s_off[e] * p.tile_m;
+    for (int base = 0; base < C * R; base += 32) {
+      const int i = base + lane;
+      int c = 0, s = 0, v = 0;
+      if (i < C * R) {
+        c = i / R; s = i - c * R;
+        v = ctl_inbox_counts(own, p.ctl, parity, s, c)[e];
+      }
+      int total;
+      const int excl = warp_excl_scan(v, lane, total);
+      if (i < C * R) {
+        if (owner == p.rank) {
+          p.base_pool[(static_cast<size_t>(c) * R + s) * EL + el] = carry + excl;
+          p.seen_per_substream[(static_cast<size_t>(c) * R + s) * EL + el] = v;
+        }
+        if (s == p.rank) p.send_base[static_cast<size_t>(c) * E + e] = carry + excl;
+      }
+      carry += total;
+    }
+  }
+  // 5. token-id bases and the prefix matrices of the handle
+  if (tid < R) {
+    const int d = tid;
+    int before = 0;
+    for (int s = 0; s < p.rank; ++s) before += s_U[s][d];
+    int run = before, incl = 0;
+    for (int c = 0; c < C; ++c) {
+      p.send_token_base[c * R + d] = run;
+      const int u = ctl_inbox_tokens(own, p.ctl, parity, p.rank, c)[d];
+      run += u; incl += u;
+      p.channel_prefix_matrix[d * C + c] = incl;
+    }
+    // receiver view: source s = tid
+    const int s = tid;
+    int cum = 0;
+    for (int ss = 0; ss <= s; ++ss) cum += s_U[ss][p.rank];
+    for (int dd = 0; dd < R; ++dd) p.rank_prefix_matrix[s * R + dd] = (dd == p.rank) ? cum : 0;
+    int rc = 0;
+    for (int c = 0; c < C; ++c) {
+      rc += ctl_inbox_tokens(own, p.ctl, parity, s, c)[p.rank];
+      p.recv_channel_prefix_matrix[s * C + c] = rc;
+    }
+  }
+  __syncthreads();
+  // 6. materialise destination slots and recv-token ids for this rank's pairs / tokens
+  for (size_t i = tid; i < static_cast<size_t>(T) * K; i += blockDim.x) {
+    const int t = static_cast<int>(i / K);
+    const long long e = p.topk_idx[i];
+    int slot = -1;
+    if (e >= 0 && e < E) slot = p.send_base[static_cast<size_t>(t / per) * E + e] + p.pair_rank[i];
+    p.pair_slot[i] = slot;
+  }
+  for (size_t i = tid; i < static_cast<size_t>(T) * R; i += blockDim.x) {
+    const int t = static_cast<int>(i / R), d = static_cast<int>(i - static_cast<size_t>(t) * R);
+    const int rk = p.token_rank_in_channel[i];
+    p.send_recv_token[i] = rk < 0 ? -1 : p.send_token_base[(t / per) * R + d] + rk;
+  }
+  // send_head: position in the (channel, dst) stream; gaps hold -(next valid position) - 1
+  for (int i = tid; i < C * R; i += blockDim.x) {
+    const int c = i / R, d = i - c * R;
+    const int lo = min(per * c, T), hi = min(lo + per, T);
+    int nxt = ctl_inbox_tokens(own, p.ctl, parity, p.rank, c)[d];
+    for (int t = hi - 1; t >= lo; --t) {
+      const int rk = p.token_rank_in_channel[static_cast<size_t>(t) * R + d];
+      if (rk >= 0) { nxt = rk; p.send_head[static_cast<size_t>(t) * R + d] = rk; }
+      else p.send_head[static_cast<size_t>(t) * R + d] = -nxt - 1;
+    }
+  }
+}
+
+void launch_dispatch_metadata(const MetadataParams& p, cudaStream_t stream) {
+  const int grid = (p.phase_mask & 1) ? p.num_channels : 1;
+  dispatch_metadata_kernel<<<grid, kMetaThreads, 0, stream>>>(p);
+}
+
+// =============================================================================================
+// Tile metadata + defaults of everything peers will write into
+// =============================================================================================
+__global__ void fill_tile_metadata_kernel(const FillParams p) {
+  const int gid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int stride = gridDim.x * blockDim.x;
+  for (int t = gid; t < p.total_tiles; t += stride) {
+    int e = 0;
+    while (e + 1 < p.num_local_experts && p.expert_pool_block_offset[e + 1] <= t) ++e;
+    const int j = t - p.expert_pool_block_offset[e];
+    p.tile_id_to_expert[t] = e;
+    p.pool_arrival_target[t] = min(p.tile_m, p.expert_frequency[e] - j * p.tile_m);
+    p.pool_arrival_count[t] = 0;
+  }
+  for (int i = gid; i < p.tk_padded; i += stride) {
+    p.pool_recv_token[i] = -1;
+    p.pool_k_slot[i] = -1;
+    p.pool_src[i] = make_int2(-1, -1);
+    p.pool_topk_weight[i] = 0.f;
+  }
+  for (int i = gid; i < p.num_recv_tokens; i += stride) {
+    p.k_local_total[i] = 0;
+    p.k_local_remaining[i] = 0;
+    p.y_done_per_token[i] = 0;
+    p.recv_src[i] = make_int2(-1, -1);
+  }
+  for (size_t i = gid; i < static_cast<size_t>(p.num_recv_tokens) * p.num_topk; i += stride)
+    p.recv_token_to_slots[i] = -1;
+}
+
+void launch_fill_tile_metadata(const FillParams& p, cudaStream_t stream) {
+  const int work = max(max(p.tk_padded, p.num_recv_tokens * p.num_topk), 1);
+  const int grid = min((work + 255) / 256, 592);
+  fill_tile_metadata_kernel<<<grid, 256, 0, stream>>>(p);
+}
+
+// =============================================================================================
+// Push dispatch
+// =============================================================================================
+constexpr int kPushThreads = 512;
+
+__global__ void __launch_bounds__(kPushThreads, 1) dispatch_push_kernel(const PushParams p) {
+  __shared__ PushTargets s_tg;
+  __shared__ int s_ok;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int R = p.num_ranks;
+  void* own = p.peer_base[p.rank];
+
+  if (blockIdx.x == 0 && tid == 0 && p.started_flag != nullptr) atomicAdd(p.started_flag, 1);
+  if ((p.flags & 1) && blockIdx.x == 0 && tid < R)
+    publish_record(p.own, p.peer_base, p.ctl, p.kind, p.epoch, p.rank, tid);
+  if (tid == 0) s_ok = 1;
+  __syncthreads();
+
+  if (p.flags & 2) {
+    if (tid < R) {
+      const unsigned long long* rec = fetch_record(own, p.ctl, p.kind, p.epoch, tid, p.wait_budget_ns, p.status,
+                                                   p.is_grads ? kKernelDispatchGrads : kKernelDispatch, p.rank);
+      if (rec == nullptr) s_ok = 0;
+      else resolve_push_targets(s_tg, tid, p.peer_base[tid], rec);
+    }
+    __syncthreads();
+    if (s_ok) {
+      const int tpc = p.tokens_per_chunk;
+      const int num_chunks = (p.num_tokens + tpc - 1) / tpc;
+      for (;;) {
+        int chunk = 0;
+        if (lane == 0) chunk = atomicAdd(p.work_counter, 1);
+        chunk = __shfl_sync(0xffffffffu, chunk, 0);
+        if (chunk >= num_chunks) break;
+        const int t0 = chunk * tpc;
+        push_chunk(p, s_tg, t0, min(t0 + tpc, p.num_tokens), lane);
+      }
+    }
+  }
+
+  if ((p.flags & 4) && s_ok) {
+    // All rows addressed to this rank have landed once every own tile reached its target.
+    const int gid = blockIdx.x * blockDim.x + tid;
+    for (int t = gid; t < p.own_total_tiles; t += gridDim.x * blockDim.x) {
+      const int target = p.own_arrival_target[t];
+      const int* cnt = p.own_arrival_count + t;
+      if (!spin_until([&] { return ld_acquire_sys(cnt) == target; }, p.wait_budget_ns, p.status)) {
+        report_failure(p.status, kStatusTimeoutTail, p.is_grads ? kKernelDispatchGrads : kKernelDispatch, 2,
+                       p.rank, t, target, ld_acquire_sys(cnt));
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const int old = atomicAdd(p.blocks_done, 1);
+    if (old == static_cast<int>(gridDim.x) - 1) {   // last block resets the launch-local counters
+      *p.work_counter = 0;
+      *p.blocks_done = 0;
+    }
+  }
+}
+
+void launch_dispatch_push(const PushParams& p, int num_blocks, cudaStream_t stream) {
+  dispatch_push_kernel<<<num_blocks, kPushThreads, 0, stream>>>(p);
+}
+
+// =============================================================================================
+// Pull combine
+// =============================================================================================
+constexpr int kCombineThreads = 512;
+
+__global__ void __launch_bounds__(kCombineThreads, 1) combine_pull_kernel(const CombineParams p) {
+  __shared__ const char* s_x[kMaxRanks];
+  __shared__ const long long* s_done[kMaxRanks];
+  __shared__ const float* s_w[kMaxRanks];
+  __shared__ int s_ok;
+  __shared__ int s_is_last;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int R = p.num_ranks, K = p.num_topk;
+  const int kernel_id = kKernelCombine;
+  void* own = p.peer_base[p.rank];
+
+  if ((p.flags & 1) && blockIdx.x == 0 && tid < R)
+    publish_record(p.own, p.peer_base, p.ctl, p.kind, p.epoch, p.rank, tid);
+  if (tid == 0) s_ok = 1;
+  __syncthreads();
+
+  if (p.flags & 2) {
+    if (tid < R) {
+      const unsigned long long* rec =
+          fetch_record(own, p.ctl, p.kind, p.epoch, tid, p.wait_budget_ns, p.status, kernel_id, p.rank);
+      if (rec == nullptr) s_ok = 0;
+      else {
+        const char* b = static_cast<const char*>(p.peer_base[tid]);
+        s_x[tid] = b + rec[10];
+        s_done[tid] = reinterpret_cast<const long long*>(b + rec[11]);
+        s_w[tid] = reinterpret_cast<const float*>(b + rec[12]);
+      }
+    }
+    __syncthreads();
+    const int warps_per_block = blockDim.x >> 5;
+    const int e_local = p.num_experts / R;
+    const size_t row_bytes = static_cast<size_t>(p.hidden) * 2;
+    const int vec_per_row = p.hidden / 8;
+    if (s_ok) {
+      for (int t = blockIdx.x * warps_per_block + warp; t < p.num_tokens; t += gridDim.x * warps_per_block) {
+        int my_r = -1;
+        if (lane < R) my_r = p.send_recv_token[static_cast<size_t>(t) * R + lane];
+        // gate: every contributing rank must have stamped its row
+        bool ok = true;
+        if (my_r >= 0) {
+          const long long* g = s_done[lane] + my_r;
+          ok = spin_until([&] { return ld_acquire_sys(g) >= p.seq; }, p.wait_budget_ns, p.status);
+          if (!ok) report_failure(p.status, kStatusTimeoutTokenGate, kernel_id, 3, p.rank, t,
+                                  static_cast<int>(p.seq), static_cast<int>(ld_acquire_sys(g)));
+        }
+        if (!__all_sync(0xffffffffu, ok)) break;
+        for (int v = lane; v < vec_per_row; v += 32) {
+          float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          for (int d = 0; d < R; ++d) {
+            const int r = __shfl_sync(0xffffffffu, my_r, d);
+            if (r < 0) continue;
+            const uint4 q = ld_relaxed_sys_v4(s_x[d] + static_cast<size_t>(r) * row_bytes + static_cast<size_t>(v) * 16);
+            const float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), c = unpack_bf16x2(q.z), e = unpack_bf16x2(q.w);
+            acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+            acc[4] += c.x; acc[5] += c.y; acc[6] += e.x; acc[7] += e.y;
+          }
+          uint4 o;
+          o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+          o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+          st_na_v4(static_cast<char*>(p.out) + static_cast<size_t>(t) * row_bytes + static_cast<size_t>(v) * 16, o);
+        }
+        if (!p.is_fwd && lane < K) {
+          const long long e = p.topk_idx[static_cast<size_t>(t) * K + lane];
+          const int slot = p.pair_slot[static_cast<size_t>(t) * K + lane];
+          float g = 0.f;
+          if (e >= 0 && slot >= 0) g = s_w[static_cast<int>(e / e_local)][slot];
+          p.out_topk_weights[static_cast<size_t>(t) * K + lane] = g;
+        }
+      }
+    }
+  }
+
+  if (p.flags & 4) {
+    // Tail handshake: peers may release the rows this rank read only after it is done reading.
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      const int old = atomicAdd(p.blocks_done, 1);
+      s_is_last = (old == static_cast<int>(gridDim.x) - 1);
+    }
+    __syncthreads();
+    if (s_is_last) {
+      if (tid == 0) *p.blocks_done = 0;
+      __threadfence_system();
+      if (tid < R) {
+        flags_signal(p.peer_base, p.ctl, p.kind, p.epoch, p.rank, tid);
+        flags_wait(own, p.ctl, p.kind, p.epoch, tid, p.wait_budget_ns, p.status, kernel_id, p.rank,
+                   kStatusTimeoutTail);
+      }
+    }
+  }
+}
+
+void launch_combine_pull(const CombineParams& p, int num_blocks, cudaStream_t stream) {
+  combine_pull_kernel<<<num_blocks, kCombineThreads, 0, stream>>>(p);
+}
+
+// =============================================================================================
+// Barrier, tile producer, pool <-> recv copies
+// =============================================================================================
+__global__ void device_barrier_kernel(const BarrierParams p) {
+  const int tid = threadIdx.x;
+  __threadfence_system();
+  if (tid < p.num_ranks) {
+    flags_signal(p.peer_base, p.ctl, kKindBarrier, p.epoch, p.rank, tid);
+    flags_wait(p.peer_base[p.rank], p.ctl, kKindBarrier, p.epoch, tid, p.wait_budget_ns, p.status,
+               kKernelBarrier, p.rank, kStatusTimeoutBarrier);
+  }
+}
+void launch_device_barrier(const BarrierParams& p, cudaStream_t stream) {
+  device_barrier_kernel<<<1, 32, 0, stream>>>(p);
+}
+
+__global__ void tile_producer_kernel(int* count, const int* target, int num_tiles, long long delay_ns) {
+  for (int t = 0; t < num_tiles; ++t) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < static_cast<unsigned long long>(delay_ns)) __nanosleep(100);
+    red_release_gpu_add(count + t, target[t]);
+  }
+}
+void launch_tile_producer(int* count, const int* target, int num_tiles, long long delay_ns, cudaStream_t stream) {
+  tile_producer_kernel<<<1, 1, 0, stream>>>(count, target, num_tiles, delay_ns);
+}
+
+template <bool kCompress>
+__global__ void pool_rows_kernel(const char* src, char* dst, const int* pool_recv_token, int tk_padded, int hidden) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t row_bytes = static_cast<size_t>(hidden) * 2;
+  const int vecs = hidden / 8;
+  for (int slot = blockIdx.x * warps_per_block + warp; slot < tk_padded; slot += gridDim.x * warps_per_block) {
+    const int r = pool_recv_token[slot];
+    if (r < 0) {
+      if (!kCompress)   // padding rows of a re-expanded pool are zero
+        for (int v = lane; v < vecs; v += 32)
+          st_na_v4(dst + static_cast<size_t>(slot) * row_bytes + static_cast<size_t>(v) * 16, make_uint4(0, 0, 0, 0));
+      continue;
+    }
+    const char* s = kCompress ? src + static_cast<size_t>(slot) * row_bytes : src + static_cast<size_t>(r) * row_bytes;
+    char* d = kCompress ? dst + static_cast<size_t>(r) * row_bytes : dst + static_cast<size_t>(slot) * row_bytes;
+    for (int v = lane; v < vecs; v += 32) st_na_v4(d + static_cast<size_t>(v) * 16, ld_nc_v4(s + static_cast<size_t>(v) * 16));
+  }
+}
+void launch_pool_compress(const void* pool, void* recv, const int* pool_recv_token, int tk_padded, int hidden,
+                          cudaStream_t stream) {
+  if (tk_padded == 0) return;
+  const int grid = min((tk_padded + 7) / 8, 148 * 8);
+  pool_rows_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const char*>(pool), static_cast<char*>(recv),
+                                                   pool_recv_token, tk_padded, hidden);
+}
+void launch_pool_expand(const void* recv, void* pool, const int* pool_recv_token, int tk_padded, int hidden,
+                        cudaStream_t stream) {
+  if (tk_padded == 0) return;
+  const int grid = min((tk_padded + 7) / 8, 148 * 8);
+  pool_rows_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const char*>(recv), static_cast<char*>(pool),
+                                                    pool_recv_token, tk_padded, hidden);
+}
+
+// =============================================================================================
+// Router: logits = x @ w_gate^T, softmax, top-k, renormalise, rank bitmap.  One warp per token.
+// The reference has no router; its harnesses build routing with torch ops
+// (stream_ep/stream_moe/profile_pipeline.py:102-139).
+// =============================================================================================
+constexpr int kRouterMaxExpertsPerLane = 16;   // up to 512 experts
+
+__global__ void router_kernel(const RouterParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int E = p.num_experts, H = p.hidden, K = p.num_topk;
+  const int e_local = E / p.num_ranks;
+  const __nv_bfloat16* xg = static_cast<const __nv_bfloat16*>(p.x);
+  const __nv_bfloat16* wg = static_cast<const __nv_bfloat16*>(p.w_gate);
+  __nv_bfloat16* s_x = reinterpret_cast<__nv_bfloat16*>(smem_raw) + static_cast<size_t>(warp) * H;
+
+  for (int t = blockIdx.x * warps_per_block + warp; t < p.num_tokens; t += gridDim.x * warps_per_block) {
+    for (int v = lane; v < H / 8; v += 32)
+      reinterpret_cast<uint4*>(s_x)[v] = ld_nc_v4(xg + static_cast<size_t>(t) * H + v * 8);
+    __syncwarp();
+    float logit[kRouterMaxExpertsPerLane];
+#pragma unroll
+    for (int j = 0; j < kRouterMaxExpertsPerLane; ++j) logit[j] = -INFINITY;
+    // expert e is owned by lane e % 32; every lane reduces its own rows of w_gate
+#pragma unroll
+    for (int j = 0; j < kRouterMaxExpertsPerLane; ++j) {
+      const int e = j * 32 + lane;
+      if (e < E) {
+        float acc = 0.f;
+        const uint4* wrow = reinterpret_cast<const uint4*>(wg + static_cast<size_t>(e) * H);
+        for (int v = 0; v < H / 8; ++v) {
+          const uint4 q = __ldg(wrow + v);
+          const uint4 xv = reinterpret_cast<const uint4*>(s_x)[v];
+          const float2 a0 = unpack_bf16x2(q.x), b0 = unpack_bf16x2(xv.x);
+          const float2 a1 = unpack_bf16x2(q.y), b1 = unpack_bf16x2(xv.y);
+          const float2 a2 = unpack_bf16x2(q.z), b2 = unpack_bf16x2(xv.z);
+          const float2 a3 = unpack_bf16x2(q.w), b3 = unpack_bf16x2(xv.w);
+          acc += a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y +
+                 a2.x * b2.x + a2.y * b2.y + a3.x * b3.x + a3.y * b3.y;
+        }
+        logit[j] = acc;
+      }
+    }
+    // softmax over all experts
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kRouterMaxExpertsPerLane; ++j) mx = fmaxf(mx, logit[j]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRouterMaxExpertsPerLane; ++j) {
+      const int e = j * 32 + lane;
+      logit[j] = (e < E) ? __expf(logit[j] - mx) : 0.f;
+      sum += logit[j];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.f / sum;
+#pragma unroll
+    for (int j = 0; j < kRouterMaxExpertsPerLane; ++j) {
+      logit[j] *= inv;
+      const int e = j * 32 + lane;
+      if (p.probs != nullptr && e < E) p.probs[static_cast<size_t>(t) * E + e] = logit[j];
+    }
+    // top-k by repeated arg-max (ties -> lowest expert id, as torch.topk on distinct values)
+    float wsum = 0.f;
+    float my_w = 0.f; int my_e = -1;
+    unsigned rank_mask = 0;
+    for (int k = 0; k < K; ++k) {
+      float best = -1.f; int best_e = 0x7fffffff;
+#pragma unroll
+      for (int j = 0; j < kRouterMaxExpertsPerLane; ++j) {
+        const int e = j * 32 + lane;
+        if (e < E && logit[j] > best) { best = logit[j]; best_e = e; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+        if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+      }
+#pragma unroll
+      for (int j = 0; j < kRouterMaxExpertsPerLane; ++j)
+        if (j * 32 + lane == best_e) logit[j] = -2.f;
+      if (lane == k) { my_w = best; my_e = best_e; }
+      wsum += best;
+      rank_mask |= 1u << (best_e / e_local);
+    }
+    if (lane < K) {
+      p.topk_idx[static_cast<size_t>(t) * K + lane] = my_e;
+      p.topk_weights[static_cast<size_t>(t) * K + lane] = p.renormalize ? my_w / wsum : my_w;
+    }
+    if (lane < p.num_ranks && p.is_token_in_rank != nullptr)
+      p.is_token_in_rank[static_cast<size_t>(t) * p.num_ranks + lane] = (rank_mask >> lane) & 1u;
+    __syncwarp();
+  }
+}
+
+void launch_router(const RouterParams& p, cudaStream_t stream) {
+  const int warps = 4;
+  const size_t smem = static_cast<size_t>(warps) * p.hidden * 2;
+  const int grid = min((p.num_tokens + warps - 1) / warps, 148 * 4);
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  router_kernel<<<grid, warps * 32, smem, stream>>>(p);
+}
+
+}  // namespace sep

@@ -1,0 +1,527 @@
+// Persistent grouped GEMM for sm_100a: TMA-fed shared-memory pipeline, tcgen05.mma with fp32
+// accumulators in tensor memory (two accumulator buffers so the epilogue of tile i overlaps the
+// main loop of tile i+1), and fused epilogues read back with tcgen05.ld.
+//
+// One kernel template covers every GEMM-shaped op of the MoE layer:
+//   kernel A      pool[rows,H]   x W1[e]^T  -> SwiGLU on adjacent column pairs (+ optional preact)
+//   kernel Y      postact[rows,I] x W2[e]^T -> x topk weight -> bf16x2 red.add scatter (local o, or the
+//                                              source rank's output over NVLink = fused combine)
+//   kernel Y_bwd  dL_do[rows,H]  x W2[e]    -> dswiglu, dL/dweight, zero padding rows
+//   kernel A_bwd  dswiglu[rows,2I] x W1[e]  -> red.add scatter (local, or fused combine_grads)
+//   dW1 / dW2     A[rows,M]^T x B[rows,N] per expert with true-length K masking
+//   preact recompute = kernel A with the plain store epilogue
+// and optionally carries extra "push" warps that ship token rows into peers' pools while the
+// tensor-core warps consume tiles as they complete (dispatch fused with the GEMM).
+//
+// Reference counterparts: stream_ep/stream_moe/kernel_a.py, kernel_y.py, kernel_y_bwd.py,
+// kernel_a_bwd.py, tile_scheduler.py, epi_ops.py and the quack.gemm calls at
+// stream_ep/stream_moe/stream_moe.py:993-1004,1111-1142 (all Hopper WGMMA through CuTeDSL there).
+#include <cstdio>
+#include <cuda.h>
+
+#include "comm_common.cuh"
+
+namespace sep {
+
+constexpr int BM = 128;          // rows per tile == pool tile_m
+constexpr int BK = 64;           // bf16 elements per k-block: one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kGemmWarps = 6;    // 0: TMA producer, 1: MMA issuer + TMEM owner, 2..5: epilogue
+constexpr int kPushWarps = 8;    // extra warps of the fused variant
+constexpr int kEpiThreads = 128;
+
+template <int BN> struct GemmCfg {
+  static constexpr int kABytes = BM * BK * 2;                 // 16 KB
+  static constexpr int kBBytes = BN * BK * 2;                 // 16 / 32 KB
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kTmemCols = 2 * BN;                    // two accumulator buffers
+  static constexpr int kBarrierBytes = 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+};
+
+size_t grouped_gemm_smem_bytes(int block_n) {
+  return block_n == 256 ? GemmCfg<256>::kSmemBytes : GemmCfg<128>::kSmemBytes;
+}
+
+struct TileCoord {
+  int m_tile, n_tile, expert;
+  int row0;        // first row of A (VarlenM: m_tile * BM; VarlenK: first pool row of the expert)
+  int k_blocks;    // number of BK blocks to accumulate
+  int k_tail;      // VarlenK: valid rows in the last block (0 = full)
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int lin) {
+  TileCoord t;
+  if (p.mode == kVarlenM) {
+    t.m_tile = lin / p.num_n_tiles;
+    t.n_tile = lin - t.m_tile * p.num_n_tiles;
+    t.expert = p.tile_id_to_expert[t.m_tile];
+    t.row0 = t.m_tile * BM;
+    t.k_blocks = (p.K + BK - 1) / BK;
+    t.k_tail = 0;
+  } else {
+    const int per_e = p.num_m_tiles * p.num_n_tiles;
+    t.expert = lin / per_e;
+    const int rem = lin - t.expert * per_e;
+    t.m_tile = rem / p.num_n_tiles;
+    t.n_tile = rem - t.m_tile * p.num_n_tiles;
+    t.row0 = p.expert_pool_block_offset[t.expert] * BM;
+    const int len = p.expert_frequency[t.expert];
+    t.k_blocks = (len + BK - 1) / BK;
+    t.k_tail = len % BK;
+  }
+  return t;
+}
+
+__device__ __forceinline__ void st_global_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" :: "l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ int atom_add_acq_rel_gpu(int* p, int v) {
+  int old;
+  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
+}
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int BN, bool A_MN, bool B_MN, int EPI, bool PUSH>
+__global__ void __launch_bounds__((kGemmWarps + (PUSH ? kPushWarps : 0)) * 32, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GemmParams p, const PushParams pp) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ unsigned char smem_dyn[];
+  // 128-byte swizzle atoms are 1024 bytes: align the operand ring accordingly.
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  unsigned char* stage_base = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* full_bar = bars;                               // [kStages]
+  uint64_t* empty_bar = bars + Cfg::kStages;               // [kStages]
+  uint64_t* tmem_full = bars + 2 * Cfg::kStages;           // [2]
+  uint64_t* tmem_empty = bars + 2 * Cfg::kStages + 2;      // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::kStages + 4);
+  int* s_flag = reinterpret_cast<int*>(tmem_slot + 1);     // epilogue broadcast word
+  __shared__ PushTargets s_tg;
+  __shared__ int s_push_ok;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = (p.mode == kVarlenM ? p.num_m_tiles : p.num_experts * p.num_m_tiles) * p.num_n_tiles;
+  const unsigned long long budget = p.wait_budget_ns;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], kEpiThreads); }
+    mbar_fence_init();
+    if (blockIdx.x == 0 && p.started_flag != nullptr) atomicAdd(p.started_flag, 1);
+    if (PUSH) s_push_ok = 1;
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  if (PUSH) {
+    if ((pp.flags & 1) && blockIdx.x == 0 && warp == kGemmWarps && lane < pp.num_ranks)
+      publish_record(pp.own, pp.peer_base, pp.ctl, pp.kind, pp.epoch, pp.rank, lane);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; int issued = 0; bool ok = true;
+      for (int lin = blockIdx.x; lin < total_tiles && ok; lin += gridDim.x) {
+        const TileCoord t = decode_tile(p, lin);
+        if (p.mode == kVarlenM && p.arrival_count != nullptr) {
+          const int target = p.arrival_target[t.m_tile];
+          const int* cnt = p.arrival_count + t.m_tile;
+          if (!spin_until([&] { return ld_acquire_sys(cnt) == target; }, budget, p.status)) {
+            report_failure(p.status, kStatusTimeoutTileGate, kKernelGemm, 0, p.rank, t.m_tile, target, ld_acquire_sys(cnt));
+            ok = false; break;
+          }
+          fence_proxy_async();   // rows were written through the generic proxy (possibly by a peer GPU)
+        }
+        for (int kb = 0; kb < t.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, budget, p.status)) {
+            report_failure(p.status, kStatusTimeoutPipeline, kKernelGemm, 0, p.rank, lin, kb, stage);
+            ok = false; break;
+          }
+          unsigned char* sa = stage_base + stage * Cfg::kStageBytes;
+          unsigned char* sb = sa + Cfg::kABytes;
+          mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_3d(sa + j * (BK * 128), &tmap_a, &full_bar[stage], t.m_tile * BM + j * 64, t.row0 + k0, 0);
+          } else {
+            tma_load_3d(sa, &tmap_a, &full_bar[stage], k0, t.row0, 0);
+          }
+          if (B_MN) {
+            const int kz = (p.mode == kVarlenM) ? k0 : t.row0 + k0;
+            const int ez = (p.mode == kVarlenM) ? t.expert : 0;
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(sb + j * (BK * 128), &tmap_b, &full_bar[stage], t.n_tile * BN + j * 64, kz, ez);
+          } else {
+            tma_load_3d(sb, &tmap_b, &full_bar[stage], k0, t.n_tile * BN, t.expert);
+          }
+          ++issued;
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Drain: every copy this thread issued must have landed before the CTA may exit.
+        const int pending = issued < Cfg::kStages ? issued : Cfg::kStages;
+        for (int i = 0; i < pending; ++i) {
+          int s = stage - 1 - i; uint32_t ph = phase;
+          if (s < 0) { s += Cfg::kStages; ph ^= 1; }
+          const unsigned long long t0 = globaltimer_ns();
+          while (!mbar_try_wait(&full_bar[s], ph) && globaltimer_ns() - t0 < 2000000ull) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+    int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
+    for (int lin = blockIdx.x; lin < total_tiles && ok; lin += gridDim.x) {
+      const TileCoord t = decode_tile(p, lin);
+      if (t.k_blocks == 0) continue;   // empty expert: the epilogue writes zeros on its own
+      if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, budget, p.status)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t tmem_d = tmem_base + acc * BN;
+      for (int kb = 0; kb < t.k_blocks; ++kb) {
+        if (!mbar_wait(&full_bar[stage], phase, budget, p.status)) { ok = false; break; }
+        unsigned char* sa = stage_base + stage * Cfg::kStageBytes;
+        unsigned char* sb = sa + Cfg::kABytes;
+        if (p.mode == kVarlenK && t.k_tail != 0 && kb == t.k_blocks - 1) {
+          // Rows past the expert's true length hold other data: zero them in both operands
+          // (MN-major boxes keep one 128-byte row per k index, so whole rows are cleared).
+          const int first = t.k_tail;
+          constexpr int kBoxes = BM / 64 + BN / 64;
+          for (int i = lane; i < kBoxes * (BK - first) * 8; i += 32) {
+            const int box = i / ((BK - first) * 8);
+            const int r = i - box * ((BK - first) * 8);
+            *reinterpret_cast<uint4*>(sa + box * (BK * 128) + (first + r / 8) * 128 + (r % 8) * 16) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+        }
+        tc_fence_after_sync();
+        if (elect_one()) {
+          const uint32_t a_addr = smem_u32(sa), b_addr = smem_u32(sb);
+#pragma unroll
+          for (int j = 0; j < BK / UMMA_K; ++j) {
+            const uint64_t da = A_MN ? umma_smem_desc(a_addr + j * (UMMA_K * 128), BK * 128, 1024)
+                                     : umma_smem_desc(a_addr + j * (UMMA_K * 2), 16, 1024);
+            const uint64_t db = B_MN ? umma_smem_desc(b_addr + j * (UMMA_K * 128), BK * 128, 1024)
+                                     : umma_smem_desc(b_addr + j * (UMMA_K * 2), 16, 1024);
+            umma_bf16_ss(tmem_d, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);                       // frees the smem stage when the MMAs retire
+          if (kb == t.k_blocks - 1) umma_commit(&tmem_full[acc]);  // accumulator complete
+        }
+        __syncwarp();
+        if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+      }
+      acc ^= 1; if (acc == 0) acc_phase ^= 1;
+    }
+    if (!ok) report_failure(p.status, kStatusTimeoutPipeline, kKernelGemm, 1, p.rank, 0, 0, 0);
+  } else if (warp < kGemmWarps) {
+    // ------------------------------------------------------------------ epilogue (4 warps, one row per thread)
+    const int quarter = warp & 3;                 // TMEM lanes this warp may read
+    const int row = quarter * 32 + lane;
+    const int epi_tid = (warp - 2) * 32 + lane;
+    int acc = 0; uint32_t acc_phase = 0; bool ok = true;
+    for (int lin = blockIdx.x; lin < total_tiles; lin += gridDim.x) {
+      const TileCoord t = decode_tile(p, lin);
+      const bool empty = (t.k_blocks == 0);
+      if (!empty && ok) {
+        if (!mbar_wait(&tmem_full[acc], acc_phase, budget, p.status)) {
+          report_failure(p.status, kStatusTimeoutPipeline, kKernelGemm, 2, p.rank, lin, acc, 0);
+          ok = false;
+        }
+        tc_fence_after_sync();
+      }
+      if (!ok) break;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      const int n0 = t.n_tile * BN;
+      // row bookkeeping
+      long long grow;       // global output row
+      bool row_ok = true;
+      if (p.mode == kVarlenM) {
+        grow = static_cast<long long>(t.row0) + row;
+      } else {
+        const int m = t.m_tile * BM + row;
+        row_ok = m < p.M_out;
+        grow = m;
+      }
+      int tok = 0; float w = 1.f;
+      if (EPI == kEpiScatter || EPI == kEpiDswiglu) {
+        tok = p.row_token[grow];
+        if (p.row_weight != nullptr && tok >= 0) w = p.row_weight[grow];
+      }
+      float dw_acc = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int n = n0 + c * 32;
+        if (n >= p.N) break;
+        uint32_t r[32];
+        if (!empty) {
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0;
+        }
+        if (EPI == kEpiStore) {
+          if (row_ok) {
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out0) +
+                                 static_cast<long long>(t.expert) * p.out_expert_stride + grow * p.ld0 + n;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (n + q * 8 < p.N)
+                st_global_v4(dst + q * 8,
+                             pack_bf16x2(__uint_as_float(r[q * 8 + 0]), __uint_as_float(r[q * 8 + 1])),
+                             pack_bf16x2(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3])),
+                             pack_bf16x2(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5])),
+                             pack_bf16x2(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7])));
+            }
+          }
+        } else if (EPI == kEpiSwiglu) {
+          // columns (2i, 2i+1) = (gate_i, up_i)
+          if (p.out1 != nullptr) {
+            __nv_bfloat16* pre = static_cast<__nv_bfloat16*>(p.out1) + grow * p.ld1 + n;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (n + q * 8 < p.N)
+                st_global_v4(pre + q * 8,
+                             pack_bf16x2(__uint_as_float(r[q * 8 + 0]), __uint_as_float(r[q * 8 + 1])),
+                             pack_bf16x2(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3])),
+                             pack_bf16x2(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5])),
+                             pack_bf16x2(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7])));
+            }
+          }
+          float a[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float g = __uint_as_float(r[2 * i]), u = __uint_as_float(r[2 * i + 1]);
+            a[i] = g / (1.f + __expf(-g)) * u;
+          }
+          __nv_bfloat16* post = static_cast<__nv_bfloat16*>(p.out0) + grow * p.ld0 + n / 2;
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            if (n + q * 16 < p.N)
+              st_global_v4(post + q * 8, pack_bf16x2(a[q * 8 + 0], a[q * 8 + 1]), pack_bf16x2(a[q * 8 + 2], a[q * 8 + 3]),
+                           pack_bf16x2(a[q * 8 + 4], a[q * 8 + 5]), pack_bf16x2(a[q * 8 + 6], a[q * 8 + 7]));
+          }
+        } else if (EPI == kEpiScatter) {
+          if (tok >= 0) {
+            __nv_bfloat16* dst;
+            if (p.scatter_remote) {
+              const int2 src = p.row_src[grow];
+              dst = static_cast<__nv_bfloat16*>(p.peer_out[src.x]) + static_cast<long long>(src.y) * p.N + n;
+            } else {
+              dst = static_cast<__nv_bfloat16*>(p.scatter_local) + static_cast<long long>(tok) * p.N + n;
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (n + q * 8 < p.N)
+                red_add_bf16x2_v4(dst + q * 8,
+                                  pack_bf16x2(w * __uint_as_float(r[q * 8 + 0]), w * __uint_as_float(r[q * 8 + 1])),
+                                  pack_bf16x2(w * __uint_as_float(r[q * 8 + 2]), w * __uint_as_float(r[q * 8 + 3])),
+                                  pack_bf16x2(w * __uint_as_float(r[q * 8 + 4]), w * __uint_as_float(r[q * 8 + 5])),
+                                  pack_bf16x2(w * __uint_as_float(r[q * 8 + 6]), w * __uint_as_float(r[q * 8 + 7])));
+            }
+          }
+        } else {   // kEpiDswiglu: r = g[row, n..n+32) = dL/d(postact) before the topk weight
+          __nv_bfloat16* din = static_cast<__nv_bfloat16*>(p.out0) + grow * p.ld0 + 2 * n;
+          __nv_bfloat16* pw = static_cast<__nv_bfloat16*>(p.out1) + grow * p.ld1 + n;
+          if (tok >= 0) {
+            const uint4* pre = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.preact) + grow * p.ld_preact + 2 * n);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {       // 8 output columns per step
+              if (n + q * 8 >= p.N) break;
+              const uint4 p0 = pre[q * 2], p1 = pre[q * 2 + 1];
+              const uint32_t pv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+              uint32_t o_in[8]; float post[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float2 gu = unpack_bf16x2(pv[i]);
+                const float g = __uint_as_float(r[q * 8 + i]);
+                const float sig = 1.f / (1.f + __expf(-gu.x));
+                const float silu = gu.x * sig;
+                post[i] = silu * gu.y;
+                dw_acc += post[i] * g;
+                const float dgate = w * g * gu.y * sig * (1.f + gu.x * (1.f - sig));
+                const float dup = w * g * silu;
+                o_in[i] = pack_bf16x2(dgate, dup);
+              }
+              st_global_v4(din + q * 16, o_in[0], o_in[1], o_in[2], o_in[3]);
+              st_global_v4(din + q * 16 + 8, o_in[4], o_in[5], o_in[6], o_in[7]);
+              st_global_v4(pw + q * 8, pack_bf16x2(w * post[0], w * post[1]), pack_bf16x2(w * post[2], w * post[3]),
+                           pack_bf16x2(w * post[4], w * post[5]), pack_bf16x2(w * post[6], w * post[7]));
+            }
+          } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (n + q * 8 >= p.N) break;
+              st_global_v4(din + q * 16, 0, 0, 0, 0);
+              st_global_v4(din + q * 16 + 8, 0, 0, 0, 0);
+              st_global_v4(pw + q * 8, 0, 0, 0, 0);
+            }
+          }
+        }
+      }
+      if (!empty) {
+        tc_fence_before_sync();
+        mbar_arrive(&tmem_empty[acc]);
+        acc ^= 1; if (acc == 0) acc_phase ^= 1;
+      }
+      if (EPI == kEpiDswiglu) {
+        if (tok >= 0 && p.dl_dweight != nullptr) red_add_f32(p.dl_dweight + grow, dw_acc);
+      }
+      if ((EPI == kEpiScatter && !p.scatter_remote && p.tile_stripes_done != nullptr) ||
+          (EPI == kEpiDswiglu && p.return_dweight)) {
+        // Per-M-tile completion: the CTA that finishes the last N stripe of a tile does the
+        // per-row bookkeeping once every stripe's writes are visible.
+        __threadfence();
+        epi_bar_sync();
+        if (epi_tid == 0) *s_flag = (atom_add_acq_rel_gpu(p.tile_stripes_done + t.m_tile, 1) == p.num_n_tiles - 1);
+        epi_bar_sync();
+        const bool last = (*s_flag != 0);
+        epi_bar_sync();
+        if (last && tok >= 0) {
+          if (EPI == kEpiScatter) {
+            if (atom_add_acq_rel_gpu(p.k_remaining + tok, -1) == 1) st_release_gpu(p.done_per_token + tok, p.seq);
+          } else {
+            const int2 src = p.row_src[grow];
+            const float v = *reinterpret_cast<volatile float*>(p.dl_dweight + grow);
+            p.peer_dw_out[src.x][static_cast<long long>(src.y) * p.num_topk + p.row_k_slot[grow]] = v;
+          }
+        }
+      }
+    }
+    if (p.tail.enabled) __threadfence_system();
+  } else if (PUSH) {
+    // ------------------------------------------------------------------ dispatch push warps
+    if (pp.flags & 2) {
+      const int pw = warp - kGemmWarps;
+      if (pw == 0 && lane < pp.num_ranks) {
+        const unsigned long long* rec = fetch_record(pp.peer_base[pp.rank], pp.ctl, pp.kind, pp.epoch, lane,
+                                                     pp.wait_budget_ns, pp.status, kKernelDispatch, pp.rank);
+        if (rec == nullptr) s_push_ok = 0;
+        else resolve_push_targets(s_tg, lane, pp.peer_base[lane], rec);
+      }
+      asm volatile("bar.sync 2, %0;" :: "r"(kPushWarps * 32) : "memory");
+      if (s_push_ok) {
+        const int tpc = pp.tokens_per_chunk;
+        const int num_chunks = (pp.num_tokens + tpc - 1) / tpc;
+        for (;;) {
+          int chunk = 0;
+          if (lane == 0) chunk = atomicAdd(pp.work_counter, 1);
+          chunk = __shfl_sync(0xffffffffu, chunk, 0);
+          if (chunk >= num_chunks) break;
+          const int t0 = chunk * tpc;
+          push_chunk(pp, s_tg, t0, min(t0 + tpc, pp.num_tokens), lane);
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (threadIdx.x == 0) {
+    int* done_ctr = p.tail.enabled ? p.tail.ctas_done : (PUSH ? pp.blocks_done : nullptr);
+    if (done_ctr != nullptr) {
+      __threadfence();
+      const int old = atomicAdd(done_ctr, 1);
+      if (old == static_cast<int>(gridDim.x) - 1) {
+        *done_ctr = 0;
+        if (PUSH) *pp.work_counter = 0;
+        if (p.tail.enabled) {
+          // Every CTA's remote reductions were fenced at system scope before it counted itself.
+          __threadfence_system();
+          for (int r = 0; r < p.tail.num_ranks; ++r)
+            flags_signal(p.tail.peer_base, p.tail.ctl, p.tail.kind, p.tail.epoch, p.tail.rank, r);
+          if (p.tail.wait)
+            for (int r = 0; r < p.tail.num_ranks; ++r)
+              if (!flags_wait(p.tail.peer_base[p.tail.rank], p.tail.ctl, p.tail.kind, p.tail.epoch, r,
+                              p.wait_budget_ns, p.status, kKernelGemm, p.rank, kStatusTimeoutTail))
+                break;
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host dispatch over the template instances
+// ---------------------------------------------------------------------------------------------
+template <int BN, bool A_MN, bool B_MN, int EPI, bool PUSH>
+static void launch_instance(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& tb,
+                            const PushParams& pp, int num_ctas, cudaStream_t stream) {
+  auto kernel = grouped_gemm_kernel<BN, A_MN, B_MN, EPI, PUSH>;
+  static bool configured = false;
+  const int smem = GemmCfg<BN>::kSmemBytes;
+  if (!configured) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    configured = true;
+  }
+  const int threads = (kGemmWarps + (PUSH ? kPushWarps : 0)) * 32;
+  kernel<<<num_ctas, threads, smem, stream>>>(ta, tb, p, pp);
+}
+
+template <int BN, bool PUSH>
+static bool dispatch_layout(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& tb,
+                            const PushParams& pp, int n, cudaStream_t s) {
+  if (p.mode == kVarlenM && !p.a_mn_major && !p.b_mn_major) {
+    if (p.epilogue == kEpiSwiglu) { launch_instance<BN, false, false, kEpiSwiglu, PUSH>(p, ta, tb, pp, n, s); return true; }
+    if (PUSH) return false;
+    if constexpr (!PUSH) {
+      if (p.epilogue == kEpiStore) { launch_instance<BN, false, false, kEpiStore, false>(p, ta, tb, pp, n, s); return true; }
+      if (p.epilogue == kEpiScatter) { launch_instance<BN, false, false, kEpiScatter, false>(p, ta, tb, pp, n, s); return true; }
+    }
+  }
+  if (p.mode == kVarlenM && !p.a_mn_major && p.b_mn_major) {
+    if (p.epilogue == kEpiDswiglu) { launch_instance<BN, false, true, kEpiDswiglu, PUSH>(p, ta, tb, pp, n, s); return true; }
+    if constexpr (!PUSH) {
+      if (p.epilogue == kEpiScatter) { launch_instance<BN, false, true, kEpiScatter, false>(p, ta, tb, pp, n, s); return true; }
+      if (p.epilogue == kEpiStore) { launch_instance<BN, false, true, kEpiStore, false>(p, ta, tb, pp, n, s); return true; }
+    }
+  }
+  if constexpr (!PUSH) {
+    if (p.mode == kVarlenK && p.a_mn_major && p.b_mn_major && p.epilogue == kEpiStore) {
+      launch_instance<BN, true, true, kEpiStore, false>(p, ta, tb, pp, n, s); return true;
+    }
+  }
+  return false;
+}
+
+void launch_grouped_gemm(const GemmParams& p, const void* tmap_a, const void* tmap_b, const PushParams* fused_push,
+                         int num_ctas, cudaStream_t stream) {
+  const CUtensorMap& ta = *static_cast<const CUtensorMap*>(tmap_a);
+  const CUtensorMap& tb = *static_cast<const CUtensorMap*>(tmap_b);
+  bool ok;
+  if (fused_push != nullptr) {
+    ok = (p.block_n == 256) ? dispatch_layout<256, true>(p, ta, tb, *fused_push, num_ctas, stream)
+                            : dispatch_layout<128, true>(p, ta, tb, *fused_push, num_ctas, stream);
+  } else {
+    PushParams none{};
+    ok = (p.block_n == 256) ? dispatch_layout<256, false>(p, ta, tb, none, num_ctas, stream)
+                            : dispatch_layout<128, false>(p, ta, tb, none, num_ctas, stream);
+  }
+  if (!ok) fprintf(stderr, "streamep_b200: unsupported grouped GEMM configuration (mode=%d epi=%d a_mn=%d b_mn=%d)\n",
+                   p.mode, p.epilogue, p.a_mn_major, p.b_mn_major);
+}
+
+}  // namespace sep

@@ -1,0 +1,926 @@
+// Host runtime of the library (pybind module `_C`): symmetric arena + peer mapping, the dispatch /
+// dispatch_grads / combine host paths split into phases, launch gates, grouped-GEMM launch with
+// TMA descriptors, and the status block every bounded device wait reports into.
+//
+// Reference counterpart: csrc/stream_ep.cpp (Buffer ctor/sync :129-264,458-543; launch gates
+// :387-456; intranode_dispatch :1125-1330; dispatch_grads :1332-1451; combine :1453-1561; pybind
+// :2070-2156), csrc/config.hpp, csrc/event.hpp.
+#include <ATen/cuda/CUDAContext.h>
+#include <ATen/cuda/CUDAEvent.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <pybind11/functional.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include <atomic>
+#include <chrono>
+#include <cstring>
+#include <optional>
+#include <sstream>
+#include <thread>
+
+#include "api.h"
+#include "arena.h"
+
+namespace py = pybind11;
+
+namespace sep {
+
+#define SEP_CUDA_CHECK(expr)                                                                        \
+  do {                                                                                              \
+    cudaError_t e__ = (expr);                                                                       \
+    if (e__ != cudaSuccess) {                                                                       \
+      std::ostringstream os__;                                                                      \
+      os__ << "CUDA error " << cudaGetErrorName(e__) << " (" << cudaGetErrorString(e__) << ") at "  \
+           << __FILE__ << ":" << __LINE__ << " in " #expr;                                          \
+      throw std::runtime_error(os__.str());                                                         \
+    }                                                                                               \
+  } while (0)
+
+#define SEP_ASSERT(cond, msg)                                                         \
+  do {                                                                                \
+    if (!(cond)) {                                                                    \
+      std::ostringstream os__;                                                        \
+      os__ << "streamep_b200: " << msg << " (" #cond ") at " << __FILE__ << ":" << __LINE__; \
+      throw std::invalid_argument(os__.str());                                        \
+    }                                                                                 \
+  } while (0)
+
+// ---------------------------------------------------------------------------------------------
+// Driver entry points fetched at run time (the extension does not link libcuda).
+// ---------------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+using StreamWaitValue32Fn = CUresult (*)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+
+template <class Fn>
+static Fn driver_fn(const char* name) {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  SEP_CUDA_CHECK(cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &q));
+  if (q != cudaDriverEntryPointSuccess || fn == nullptr)
+    throw std::runtime_error(std::string("streamep_b200: driver entry point not found: ") + name);
+  return reinterpret_cast<Fn>(fn);
+}
+
+// 3-D bf16 tensor map, 128-byte swizzle, OOB reads return zero.  dims/box are innermost-first.
+static CUtensorMap make_tmap(const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_elems,
+                             uint64_t stride2_elems, uint32_t b0, uint32_t b1) {
+  static EncodeTiledFn encode = driver_fn<EncodeTiledFn>("cuTensorMapEncodeTiled");
+  CUtensorMap m;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {stride1_elems * 2, stride2_elems * 2};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  SEP_ASSERT(reinterpret_cast<uintptr_t>(base) % 16 == 0, "TMA base address must be 16-byte aligned");
+  SEP_ASSERT(strides[0] % 16 == 0 && strides[1] % 16 == 0, "TMA row pitch must be a multiple of 16 bytes");
+  CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw std::runtime_error("streamep_b200: cuTensorMapEncodeTiled failed with code " + std::to_string(r));
+  return m;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Config (reference: csrc/config.hpp:23-132).  The five-tuple is kept for source compatibility;
+// this implementation has no rings, so the chunk sizes only bound the size hints.
+// ---------------------------------------------------------------------------------------------
+struct Config {
+  int num_sms, num_max_nvl_chunked_send_tokens, num_max_nvl_chunked_recv_tokens,
+      num_max_rdma_chunked_send_tokens, num_max_rdma_chunked_recv_tokens;
+  Config(int sms, int nvl_send, int nvl_recv, int rdma_send, int rdma_recv)
+      : num_sms(sms), num_max_nvl_chunked_send_tokens(nvl_send), num_max_nvl_chunked_recv_tokens(nvl_recv),
+        num_max_rdma_chunked_send_tokens(rdma_send), num_max_rdma_chunked_recv_tokens(rdma_recv) {
+    SEP_ASSERT(sms >= 0, "num_sms must be non-negative");
+    SEP_ASSERT(nvl_send > 0 && nvl_recv > 0 && nvl_send < nvl_recv, "NVL chunk sizes must satisfy 0 < send < recv");
+    SEP_ASSERT(rdma_send > 0 && rdma_recv > 0, "RDMA chunk sizes must be positive");
+  }
+};
+
+struct ArenaSizeHint {
+  // Bytes of symmetric memory one MoE layer keeps alive between its forward and its backward at
+  // `level` of activation checkpointing, for `tokens` source tokens per rank routed top-`k`.
+  static size_t layer_bytes(int64_t tokens, int64_t hidden, int64_t topk, int num_ranks, int64_t experts_local,
+                            double imbalance) {
+    const double pairs = static_cast<double>(tokens) * topk * imbalance;
+    const double rows = pairs + 128.0 * experts_local;
+    const double recv = std::min<double>(static_cast<double>(tokens) * num_ranks, pairs);
+    double b = rows * hidden * 2 /*pool*/ + rows * 24 /*per-slot*/ + recv * (topk * 4 + 32) /*per-token*/ +
+               recv * hidden * 2 /*o*/ + static_cast<double>(tokens) * hidden * 2 /*out*/;
+    return static_cast<size_t>(b * 1.05) + (8u << 20);
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
+// Event handle (reference: csrc/event.hpp:9-35)
+// ---------------------------------------------------------------------------------------------
+struct EventHandle {
+  std::shared_ptr<at::cuda::CUDAEvent> event;
+  EventHandle() : event(std::make_shared<at::cuda::CUDAEvent>()) { event->record(at::cuda::getCurrentCUDAStream()); }
+  explicit EventHandle(const at::cuda::CUDAStream& s) : event(std::make_shared<at::cuda::CUDAEvent>()) { event->record(s); }
+  void current_stream_wait() const { event->block(at::cuda::getCurrentCUDAStream()); }
+  void wait_on(int64_t raw_stream, int device) const {
+    event->block(at::cuda::getStreamFromExternal(reinterpret_cast<cudaStream_t>(raw_stream), device));
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
+// Per-dispatch state shared between the phases of one dispatch (and kept by the handle)
+// ---------------------------------------------------------------------------------------------
+struct DispatchState {
+  // inputs
+  at::Tensor x, topk_idx, topk_weights;
+  int num_tokens = 0, hidden = 0, num_topk = 0, num_experts = 0, tile_m = kTileM;
+  int64_t seq = 0;
+  int meta_epoch = 0, push_epoch = 0;
+  // sender side (regular device memory)
+  at::Tensor sender_slab;
+  at::Tensor pair_rank, pair_slot, token_rank_in_channel, send_recv_token, send_head, is_token_in_rank,
+      channel_prefix_matrix, send_base, send_token_base, peer_total_tiles, peer_num_recv;
+  // receiver side metadata (regular device memory)
+  at::Tensor expert_frequency, expert_pool_block_offset, base_pool, seen_per_substream, rank_prefix_matrix,
+      recv_channel_prefix_matrix, tile_id_to_expert, pool_arrival_target;
+  // receiver side, written by peers (symmetric arena)
+  at::Tensor meta_slab;
+  at::Tensor pool, pool_topk_weight, pool_recv_token, pool_k_slot, pool_src, recv_token_to_slots, k_local_total,
+      k_local_remaining, pool_arrival_count, recv_src, y_done_per_token, o;
+  int total_tiles = 0, num_recv_tokens = 0;
+  std::vector<int> recv_per_expert;
+  std::optional<EventHandle> metadata_done_event;
+  BufferRecord record{};
+
+  void release_o() { o = at::Tensor(); }
+  void release_pool() { pool = at::Tensor(); }
+};
+
+struct GradsState {
+  at::Tensor dl_do_pool, bwd_dispatch_arrival_count, slab;
+  int epoch = 0;
+  BufferRecord record{};
+  std::optional<EventHandle> started_event;
+};
+
+struct CombineState {
+  at::Tensor x_sym, done_sym, w_sym;   // arena-resident views/copies the peers read
+  at::Tensor out, out_topk_weights;
+  int epoch = 0;
+  BufferRecord record{};
+};
+
+// Optional-tensor bag for the grouped GEMM launcher.
+struct GemmArgs {
+  int mode = kVarlenM, epilogue = kEpiStore, block_n = 256, num_ctas = 0;
+  bool a_mn_major = false, b_mn_major = false;
+  at::Tensor a, b;                                  // operands
+  std::optional<at::Tensor> tile_id_to_expert, expert_pool_block_offset, expert_frequency;
+  std::optional<at::Tensor> arrival_count, arrival_target;
+  std::optional<at::Tensor> out0, out1, preact, row_weight, row_token, dl_dweight;
+  std::optional<at::Tensor> scatter_local, row_src, row_k_slot;
+  std::optional<at::Tensor> tile_stripes_done, k_remaining, done_per_token;
+  std::vector<int64_t> peer_out_offsets;            // remote scatter: arena offset of every rank's accumulator
+  std::vector<int64_t> peer_dw_offsets;             // remote dL/dweight return: arena offset of every rank's [T, K]
+  bool scatter_remote = false, return_dweight = false;
+  int num_topk = 0;
+  int64_t seq = 0;
+  int num_m_tiles = -1;                             // VarlenM: total tiles (defaults to len(tile_id_to_expert))
+  int started_flag = -1;                            // index of the launch-gate flag to bump (-1 = none)
+  bool tail = false; int tail_kind = kKindGemmYTail; bool tail_wait = true;
+  std::shared_ptr<DispatchState> fused_push;        // dispatch fused into this GEMM (forward rows)
+  std::shared_ptr<GradsState> fused_push_grads;     // dispatch_grads fused into this GEMM
+  std::shared_ptr<DispatchState> fused_push_routing;
+  at::Tensor fused_push_rows;
+  int push_flags = 7;
+};
+
+class Runtime {
+ public:
+  Runtime(int rank, int num_ranks, int64_t arena_bytes, int num_channels, int num_experts_cap, int64_t timeout_ms)
+      : rank_(rank), num_ranks_(num_ranks), num_channels_(num_channels) {
+    SEP_ASSERT(num_ranks >= 1 && num_ranks <= kMaxRanks, "1..8 ranks supported inside one NVSwitch domain");
+    SEP_ASSERT(num_channels >= 1 && num_channels <= kMaxChannels, "num_channels out of range");
+    SEP_ASSERT(num_experts_cap >= 1 && num_experts_cap <= kMaxExperts, "num_experts_cap out of range");
+    SEP_CUDA_CHECK(cudaGetDevice(&device_));
+    ctl_ = make_control_layout(num_ranks, num_channels, num_experts_cap);
+    arena_bytes_ = static_cast<size_t>(arena_bytes) + ctl_.total_bytes;
+    arena_bytes_ = (arena_bytes_ + (2u << 20) - 1) / (2u << 20) * (2u << 20);
+    SEP_CUDA_CHECK(cudaMalloc(&base_, arena_bytes_));
+    SEP_CUDA_CHECK(cudaMemset(base_, 0, ctl_.total_bytes));
+    arena_ = std::make_shared<Arena>(ctl_.total_bytes, arena_bytes_ - ctl_.total_bytes);
+    for (int i = 0; i < kMaxRanks; ++i) peer_base_[i] = nullptr;
+    peer_base_[rank] = base_;
+    // device scratch: status block, launch-gate flags, launch-local counters
+    SEP_CUDA_CHECK(cudaMalloc(&scratch_, 4096));
+    SEP_CUDA_CHECK(cudaMemset(scratch_, 0, 4096));
+    status_ = reinterpret_cast<StatusBlock*>(scratch_);
+    gate_flags_ = reinterpret_cast<int*>(static_cast<char*>(scratch_) + 256);       // [8]
+    counters_ = reinterpret_cast<int*>(static_cast<char*>(scratch_) + 512);          // [64]
+    SEP_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&host_), sizeof(HostCounters), cudaHostAllocMapped));
+    std::memset(reinterpret_cast<void*>(host_), 0, sizeof(HostCounters));
+    host_->epoch = -1;
+    SEP_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&host_dev_), host_, 0));
+    set_timeout_ms(timeout_ms);
+    for (int k = 0; k < kNumKinds; ++k) epochs_[k] = 0;
+    for (int g = 0; g < 8; ++g) gate_issued_[g] = 0;
+    SEP_CUDA_CHECK(cudaDeviceSynchronize());
+  }
+
+  ~Runtime() { destroy(); }
+
+  void destroy() {
+    if (destroyed_) return;
+    destroyed_ = true;
+    cudaDeviceSynchronize();
+    for (int i = 0; i < num_ranks_; ++i)
+      if (i != rank_ && peer_base_[i] != nullptr && opened_[i]) cudaIpcCloseMemHandle(peer_base_[i]);
+    // Tensors over arena blocks may outlive the runtime object; the slab itself is only freed when
+    // the last of them is gone (they hold the shared arena, see alloc_symmetric).
+    arena_guard_.reset();
+    if (scratch_ != nullptr) cudaFree(scratch_);
+    if (host_ != nullptr) cudaFreeHost(host_);
+    scratch_ = nullptr; host_ = nullptr;
+  }
+
+  // ---- bootstrap ---------------------------------------------------------------------------
+  int get_local_device_id() const { return device_; }
+  py::bytes get_local_ipc_handle() const {
+    cudaIpcMemHandle_t h;
+    SEP_CUDA_CHECK(cudaIpcGetMemHandle(&h, base_));
+    return py::bytes(reinterpret_cast<const char*>(&h), sizeof(h));
+  }
+  int64_t get_local_base_ptr() const { return reinterpret_cast<int64_t>(base_); }
+
+  // Multi-process: open every peer's IPC handle.  `handles[r]` is rank r's handle.
+  void sync(const std::vector<int>& device_ids, const std::vector<std::optional<py::bytes>>& handles) {
+    SEP_ASSERT(static_cast<int>(handles.size()) == num_ranks_, "one IPC handle per rank expected");
+    for (int r = 0; r < num_ranks_; ++r) {
+      if (r == rank_) continue;
+      SEP_ASSERT(handles[r].has_value(), "missing IPC handle");
+      std::string s = *handles[r];
+      SEP_ASSERT(s.size() == sizeof(cudaIpcMemHandle_t), "malformed IPC handle");
+      cudaIpcMemHandle_t h;
+      std::memcpy(&h, s.data(), sizeof(h));
+      SEP_CUDA_CHECK(cudaIpcOpenMemHandle(&peer_base_[r], h, cudaIpcMemLazyEnablePeerAccess));
+      opened_[r] = true;
+    }
+    (void)device_ids;
+    finish_sync();
+  }
+  // Single-process emulation of several ranks on one device: peers are plain pointers.
+  void sync_local(const std::vector<int64_t>& base_ptrs) {
+    SEP_ASSERT(static_cast<int>(base_ptrs.size()) == num_ranks_, "one base pointer per rank expected");
+    for (int r = 0; r < num_ranks_; ++r) peer_base_[r] = reinterpret_cast<void*>(base_ptrs[r]);
+    SEP_ASSERT(peer_base_[rank_] == base_, "own base pointer mismatch");
+    finish_sync();
+  }
+  bool is_available() const { return available_; }
+
+  // ---- misc ----------------------------------------------------------------------------------
+  void set_timeout_ms(int64_t ms) { budget_ns_ = static_cast<unsigned long long>(std::max<int64_t>(ms, 1)) * 1000000ull; timeout_ms_ = ms; }
+  int64_t get_timeout_ms() const { return timeout_ms_; }
+  int rank() const { return rank_; }
+  int num_ranks() const { return num_ranks_; }
+  int num_channels() const { return num_channels_; }
+  int64_t arena_bytes_in_use() const { return static_cast<int64_t>(arena_->bytes_in_use()); }
+  int64_t arena_high_water() const { return static_cast<int64_t>(arena_->high_water()); }
+  int64_t arena_capacity() const { return static_cast<int64_t>(arena_->capacity()); }
+
+  // A tensor over a fresh arena block; the block returns to the arena when the tensor dies.
+  at::Tensor alloc_symmetric(const std::vector<int64_t>& sizes, at::ScalarType dtype, bool zero, size_t* offset_out = nullptr) {
+    int64_t n = 1;
+    for (auto s : sizes) n *= s;
+    const size_t bytes = static_cast<size_t>(n) * c10::elementSize(dtype);
+    const size_t off = arena_->allocate(bytes);
+    if (offset_out != nullptr) *offset_out = off;
+    std::shared_ptr<Arena> arena = arena_;
+    std::shared_ptr<void> guard = arena_guard_;
+    void* ptr = static_cast<char*>(base_) + off;
+    auto t = at::from_blob(ptr, sizes, [arena, guard, off](void*) { arena->release(off); },
+                           at::TensorOptions().dtype(dtype).device(at::kCUDA, device_));
+    if (zero && bytes > 0) SEP_CUDA_CHECK(cudaMemsetAsync(ptr, 0, bytes, at::cuda::getCurrentCUDAStream()));
+    return t;
+  }
+  bool is_symmetric(const at::Tensor& t) const {
+    const char* p = static_cast<const char*>(t.data_ptr());
+    return t.is_cuda() && p >= static_cast<char*>(base_) && p < static_cast<char*>(base_) + arena_bytes_;
+  }
+  int64_t symmetric_offset(const at::Tensor& t) const {
+    SEP_ASSERT(is_symmetric(t), "tensor does not live in the symmetric arena");
+    return static_cast<const char*>(t.data_ptr()) - static_cast<char*>(base_);
+  }
+
+  // ---- status --------------------------------------------------------------------------------
+  // Reads the device status block (synchronises the device). Returns an empty string when clean.
+  std::string poll_status(bool reset) {
+    SEP_CUDA_CHECK(cudaDeviceSynchronize());
+    StatusBlock h;
+    SEP_CUDA_CHECK(cudaMemcpy(&h, status_, sizeof(h), cudaMemcpyDeviceToHost));
+    if (h.code == 0 && h.abort == 0) return "";
+    if (reset) SEP_CUDA_CHECK(cudaMemset(status_, 0, sizeof(StatusBlock)));
+    static const char* names[] = {"ok", "barrier timeout", "buffer-record timeout", "tile gate timeout",
+                                  "token gate timeout", "GEMM pipeline timeout", "tail wait timeout", "bad index"};
+    std::ostringstream os;
+    os << names[(h.code >= 0 && h.code < 8) ? h.code : 0] << " (code " << h.code << ") in kernel " << h.kernel_id
+       << " role " << h.role << " on rank " << h.rank << ": where=" << h.where << " expected=" << h.expected
+       << " observed=" << h.observed;
+    return os.str();
+  }
+
+  // ---- launch gates (reference: csrc/stream_ep.cpp:387-456) -----------------------------------
+  // gate ids: 0 dispatch_main, 1 dispatch_grads, 2 kernel_y, 3 kernel_a_bwd
+  void gate_wait_started(int gate, int64_t raw_stream) {
+    static StreamWaitValue32Fn wait_fn = driver_fn<StreamWaitValue32Fn>("cuStreamWaitValue32");
+    if (gate_issued_[gate] == 0) return;
+    CUresult r = wait_fn(reinterpret_cast<CUstream>(raw_stream), reinterpret_cast<CUdeviceptr>(gate_flags_ + gate),
+                         static_cast<cuuint32_t>(gate_issued_[gate]), CU_STREAM_WAIT_VALUE_GEQ);
+    if (r != CUDA_SUCCESS) throw std::runtime_error("streamep_b200: cuStreamWaitValue32 failed with code " + std::to_string(r));
+  }
+  void gate_bump_issued(int gate) { ++gate_issued_[gate]; }
+  at::Tensor gate_flag_tensor(int gate) {
+    return at::from_blob(gate_flags_ + gate, {1}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device_));
+  }
+
+  // ---- dispatch: phase 0, inputs + sender-side scratch ----------------------------------------
+  std::shared_ptr<DispatchState> dispatch_begin(const at::Tensor& x, const at::Tensor& topk_idx,
+                                                const at::Tensor& topk_weights, int num_experts, int tile_m,
+                                                int64_t seq) {
+    SEP_ASSERT(available_, "Buffer.sync has not completed");
+    SEP_ASSERT(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "x must be a contiguous [T, H] bf16 CUDA tensor");
+    SEP_ASSERT(topk_idx.dim() == 2 && topk_idx.is_contiguous() && topk_idx.scalar_type() == at::kLong, "topk_idx must be contiguous [T, K] int64");
+    SEP_ASSERT(topk_weights.sizes() == topk_idx.sizes() && topk_weights.is_contiguous() && topk_weights.scalar_type() == at::kFloat, "topk_weights must be contiguous [T, K] float32");
+    SEP_ASSERT(x.size(0) == topk_idx.size(0), "x and topk_idx disagree on the token count");
+    SEP_ASSERT(tile_m == kTileM, "tile_m must be 128 (one tcgen05 M tile)");
+    SEP_ASSERT(num_experts % num_ranks_ == 0 && num_experts <= ctl_.num_experts_cap, "num_experts must divide by the rank count and fit the Buffer's expert capacity");
+    SEP_ASSERT(x.size(1) % 8 == 0, "hidden must be a multiple of 8");
+    SEP_ASSERT(topk_idx.size(1) <= kMaxTopK, "num_topk too large");
+    auto st = std::make_shared<DispatchState>();
+    st->x = x; st->topk_idx = topk_idx; st->topk_weights = topk_weights;
+    st->num_tokens = x.size(0); st->hidden = x.size(1); st->num_topk = topk_idx.size(1);
+    st->num_experts = num_experts; st->tile_m = tile_m; st->seq = seq;
+    st->meta_epoch = ++epochs_[kKindMetadata];
+    const int64_t T = st->num_tokens, K = st->num_topk, R = num_ranks_, C = num_channels_, E = num_experts, EL = E / R;
+    // One int32 slab for all small tensors (each torch::empty costs microseconds on the host).
+    const int64_t n_i32 = T * K * 2 + T * R * 3 + (T * R + 3) / 4 + R * C + C * E + C * R + 2 * R + EL + (EL + 1) +
+                          2 * C * R * EL + R * R + R * C + 64;
+    st->sender_slab = at::empty({n_i32}, x.options().dtype(at::kInt));
+    int64_t off = 0;
+    auto take = [&](std::vector<int64_t> shape) {
+      int64_t n = 1; for (auto s : shape) n *= s;
+      auto t = st->sender_slab.narrow(0, off, n).view(shape);
+      off += (n + 3) / 4 * 4;
+      return t;
+    };
+    st->pair_rank = take({T, K}); st->pair_slot = take({T, K});
+    st->token_rank_in_channel = take({T, R}); st->send_recv_token = take({T, R}); st->send_head = take({T, R});
+    st->is_token_in_rank = take({(T * R + 3) / 4}).view(at::kBool).narrow(0, 0, T * R).view({T, R});
+    st->channel_prefix_matrix = take({R, C}); st->send_base = take({C, E}); st->send_token_base = take({C, R});
+    st->peer_total_tiles = take({R}); st->peer_num_recv = take({R});
+    st->expert_frequency = take({EL}); st->expert_pool_block_offset = take({EL + 1});
+    st->base_pool = take({C, R, EL}); st->seen_per_substream = take({C, R, EL});
+    st->rank_prefix_matrix = take({R, R}); st->recv_channel_prefix_matrix = take({R, C});
+    SEP_ASSERT(off <= n_i32, "sender slab overflow");
+    return st;
+  }
+
+  // ---- dispatch: phase 1, metadata kernel ------------------------------------------------------
+  void dispatch_metadata(const std::shared_ptr<DispatchState>& st, int phase_mask) {
+    MetadataParams p{};
+    p.topk_idx = st->topk_idx.data_ptr<int64_t>() ? reinterpret_cast<const long long*>(st->topk_idx.data_ptr<int64_t>()) : nullptr;
+    p.num_tokens = st->num_tokens; p.num_topk = st->num_topk; p.num_experts = st->num_experts;
+    p.num_ranks = num_ranks_; p.rank = rank_; p.num_channels = num_channels_; p.tile_m = st->tile_m;
+    p.epoch = st->meta_epoch; p.phase_mask = phase_mask;
+    fill_peers(p.peer_base); p.ctl = ctl_;
+    p.pair_rank = st->pair_rank.data_ptr<int>(); p.pair_slot = st->pair_slot.data_ptr<int>();
+    p.token_rank_in_channel = st->token_rank_in_channel.data_ptr<int>();
+    p.send_recv_token = st->send_recv_token.data_ptr<int>(); p.send_head = st->send_head.data_ptr<int>();
+    p.is_token_in_rank = reinterpret_cast<unsigned char*>(st->is_token_in_rank.data_ptr<bool>());
+    p.channel_prefix_matrix = st->channel_prefix_matrix.data_ptr<int>();
+    p.send_base = st->send_base.data_ptr<int>(); p.send_token_base = st->send_token_base.data_ptr<int>();
+    p.peer_total_tiles = st->peer_total_tiles.data_ptr<int>(); p.peer_num_recv = st->peer_num_recv.data_ptr<int>();
+    p.expert_frequency = st->expert_frequency.data_ptr<int>();
+    p.expert_pool_block_offset = st->expert_pool_block_offset.data_ptr<int>();
+    p.base_pool = st->base_pool.data_ptr<int>(); p.seen_per_substream = st->seen_per_substream.data_ptr<int>();
+    p.rank_prefix_matrix = st->rank_prefix_matrix.data_ptr<int>();
+    p.recv_channel_prefix_matrix = st->recv_channel_prefix_matrix.data_ptr<int>();
+    p.blocks_done = counters_ + 0;
+    p.host = host_dev_; p.status = status_; p.wait_budget_ns = budget_ns_;
+    launch_dispatch_metadata(p, at::cuda::getCurrentCUDAStream());
+    SEP_CUDA_CHECK(cudaGetLastError());
+  }
+
+  // ---- dispatch: phase 2, host poll + receiver allocation + defaults --------------------------
+  void dispatch_allocate(const std::shared_ptr<DispatchState>& st) {
+    // The metadata kernel writes the sizes to mapped pinned memory; the epoch word goes last.
+    const auto t0 = std::chrono::steady_clock::now();
+    bool timed_out = false;
+    {
+      py::gil_scoped_release nogil;
+      unsigned spins = 0;
+      while (host_->epoch != st->meta_epoch) {
+        if ((++spins & 0x3FFu) != 0) continue;
+        const auto dt = std::chrono::steady_clock::now() - t0;
+        // the kernel's own waits give up after timeout_ms and then publish an error marker; the
+        // extra margin only covers a kernel that never got to run
+        if (std::chrono::duration_cast<std::chrono::milliseconds>(dt).count() > 2 * timeout_ms_ + 5000) { timed_out = true; break; }
+      }
+    }
+    if (timed_out)
+      throw std::runtime_error("streamep_b200: timed out waiting for dispatch metadata on rank " + std::to_string(rank_) +
+                               " (did every rank call dispatch?)");
+    std::atomic_thread_fence(std::memory_order_acquire);
+    st->total_tiles = host_->total_tiles;
+    st->num_recv_tokens = host_->num_recv_tokens;
+    if (st->total_tiles < 0) {
+      std::string why = poll_status(true);
+      throw std::runtime_error("streamep_b200: dispatch metadata failed on rank " + std::to_string(rank_) + ": " + why);
+    }
+    const int EL = st->num_experts / num_ranks_;
+    st->recv_per_expert.resize(EL);
+    for (int e = 0; e < EL; ++e) st->recv_per_expert[e] = host_->recv_per_expert[e];
+
+    const int64_t tiles = st->total_tiles, TKp = tiles * st->tile_m, Tr = st->num_recv_tokens, K = st->num_topk, H = st->hidden;
+    auto opts = st->x.options();
+    st->tile_id_to_expert = at::empty({tiles * 2}, opts.dtype(at::kInt));
+    st->pool_arrival_target = st->tile_id_to_expert.narrow(0, tiles, tiles);
+    st->tile_id_to_expert = st->tile_id_to_expert.narrow(0, 0, tiles);
+    size_t off_pool = 0, off_slab = 0;   // empty tensors report a null data pointer, so offsets are tracked here
+    st->pool = alloc_symmetric({TKp, H}, at::kBFloat16, false, &off_pool);
+    st->o = alloc_symmetric({Tr, H}, at::kBFloat16, true);
+    // one arena block for everything small that peers write
+    auto al = [](int64_t b) { return (b + 255) / 256 * 256; };
+    const int64_t b_w = al(TKp * 4), b_rt = al(TKp * 4), b_ks = al(TKp * 4), b_src = al(TKp * 8), b_r2s = al(Tr * K * 4),
+                  b_klt = al(Tr * 4), b_klr = al(Tr * 4), b_cnt = al(tiles * 4), b_rsrc = al(Tr * 8), b_done = al(Tr * 8);
+    st->meta_slab = alloc_symmetric({b_w + b_rt + b_ks + b_src + b_r2s + b_klt + b_klr + b_cnt + b_rsrc + b_done}, at::kByte, false, &off_slab);
+    int64_t off = 0;
+    std::vector<unsigned long long> sub_off;
+    auto sub = [&](int64_t bytes, int64_t used, at::ScalarType dt, std::vector<int64_t> shape) {
+      auto t = st->meta_slab.narrow(0, off, used).view(dt).view(shape);
+      sub_off.push_back(off_slab + off);
+      off += bytes;
+      return t;
+    };
+    st->pool_topk_weight = sub(b_w, TKp * 4, at::kFloat, {TKp});
+    st->pool_recv_token = sub(b_rt, TKp * 4, at::kInt, {TKp});
+    st->pool_k_slot = sub(b_ks, TKp * 4, at::kInt, {TKp});
+    st->pool_src = sub(b_src, TKp * 8, at::kInt, {TKp, 2});
+    st->recv_token_to_slots = sub(b_r2s, Tr * K * 4, at::kInt, {Tr, K});
+    st->k_local_total = sub(b_klt, Tr * 4, at::kInt, {Tr});
+    st->k_local_remaining = sub(b_klr, Tr * 4, at::kInt, {Tr});
+    st->pool_arrival_count = sub(b_cnt, tiles * 4, at::kInt, {tiles});
+    st->recv_src = sub(b_rsrc, Tr * 8, at::kInt, {Tr, 2});
+    st->y_done_per_token = sub(b_done, Tr * 8, at::kLong, {Tr});
+
+    FillParams f{};
+    f.total_tiles = tiles; f.tile_m = st->tile_m; f.num_local_experts = EL; f.tk_padded = TKp; f.num_recv_tokens = Tr; f.num_topk = K;
+    f.expert_frequency = st->expert_frequency.data_ptr<int>();
+    f.expert_pool_block_offset = st->expert_pool_block_offset.data_ptr<int>();
+    f.tile_id_to_expert = st->tile_id_to_expert.data_ptr<int>(); f.pool_arrival_target = st->pool_arrival_target.data_ptr<int>();
+    f.pool_arrival_count = st->pool_arrival_count.data_ptr<int>();
+    f.pool_recv_token = st->pool_recv_token.data_ptr<int>(); f.pool_k_slot = st->pool_k_slot.data_ptr<int>();
+    f.pool_src = reinterpret_cast<int2*>(st->pool_src.data_ptr<int>()); f.pool_topk_weight = st->pool_topk_weight.data_ptr<float>();
+    f.recv_token_to_slots = st->recv_token_to_slots.data_ptr<int>(); f.k_local_total = st->k_local_total.data_ptr<int>();
+    f.k_local_remaining = st->k_local_remaining.data_ptr<int>();
+    f.y_done_per_token = reinterpret_cast<long long*>(st->y_done_per_token.data_ptr<int64_t>());
+    f.recv_src = reinterpret_cast<int2*>(st->recv_src.data_ptr<int>());
+    launch_fill_tile_metadata(f, at::cuda::getCurrentCUDAStream());
+    SEP_CUDA_CHECK(cudaGetLastError());
+
+    BufferRecord& r = st->record;
+    r.pool = off_pool; r.pool_topk_weight = sub_off[0]; r.pool_recv_token = sub_off[1]; r.pool_k_slot = sub_off[2];
+    r.pool_src = sub_off[3]; r.recv_token_to_slots = sub_off[4]; r.k_local_total = sub_off[5];
+    r.k_local_remaining = sub_off[6]; r.arrival_count = sub_off[7]; r.recv_src = sub_off[8];
+    st->push_epoch = ++epochs_[kKindDispatch];
+    st->metadata_done_event = EventHandle(at::cuda::getCurrentCUDAStream());
+  }
+
+  PushParams make_push_params(const DispatchState& st, const at::Tensor& rows, bool is_grads, const BufferRecord& rec,
+                              int kind, int epoch, int flags, const int* own_count, int counter_base) {
+    PushParams p{};
+    p.x = rows.data_ptr();
+    p.topk_idx = reinterpret_cast<const long long*>(st.topk_idx.data_ptr<int64_t>());
+    p.topk_weights = st.topk_weights.data_ptr<float>();
+    p.pair_slot = st.pair_slot.data_ptr<int>();
+    p.send_recv_token = st.send_recv_token.data_ptr<int>();
+    p.num_tokens = st.num_tokens; p.hidden = st.hidden; p.num_topk = st.num_topk; p.num_experts = st.num_experts;
+    p.num_ranks = num_ranks_; p.rank = rank_; p.tile_m = st.tile_m;
+    p.is_grads = is_grads ? 1 : 0; p.kind = kind; p.epoch = epoch; p.flags = flags;
+    p.tokens_per_chunk = std::max(1, std::min(8, 64 / std::max(1, st.num_topk)));
+    fill_peers(p.peer_base); p.ctl = ctl_; p.own = rec;
+    p.own_arrival_count = own_count; p.own_arrival_target = st.pool_arrival_target.data_ptr<int>();
+    p.own_total_tiles = st.total_tiles;
+    p.started_flag = gate_flags_ + (is_grads ? 1 : 0);
+    p.work_counter = counters_ + counter_base; p.blocks_done = counters_ + counter_base + 1;
+    p.status = status_; p.wait_budget_ns = budget_ns_;
+    return p;
+  }
+
+  // ---- dispatch: phase 3, push -----------------------------------------------------------------
+  void dispatch_push(const std::shared_ptr<DispatchState>& st, int flags, int num_blocks) {
+    PushParams p = make_push_params(*st, st->x, false, st->record, kKindDispatch, st->push_epoch, flags,
+                                    st->pool_arrival_count.data_ptr<int>(), 2);
+    if (flags & 2) ++gate_issued_[0];
+    launch_dispatch_push(p, num_blocks, at::cuda::getCurrentCUDAStream());
+    SEP_CUDA_CHECK(cudaGetLastError());
+  }
+
+  // ---- dispatch_grads --------------------------------------------------------------------------
+  std::shared_ptr<GradsState> grads_begin(const std::shared_ptr<DispatchState>& st) {
+    auto g = std::make_shared<GradsState>();
+    const int64_t tiles = st->total_tiles, TKp = tiles * st->tile_m;
+    size_t off_pool = 0, off_cnt = 0;
+    g->dl_do_pool = alloc_symmetric({TKp, static_cast<int64_t>(st->hidden)}, at::kBFloat16, false, &off_pool);
+    g->bwd_dispatch_arrival_count = alloc_symmetric({tiles}, at::kInt, true, &off_cnt);
+    g->record = BufferRecord{};
+    g->record.pool = off_pool;
+    g->record.arrival_count = off_cnt;
+    g->epoch = ++epochs_[kKindDispatchGrads];
+    g->started_event = EventHandle(at::cuda::getCurrentCUDAStream());
+    return g;
+  }
+  void grads_push(const std::shared_ptr<DispatchState>& st, const std::shared_ptr<GradsState>& g, const at::Tensor& dl_dy,
+                  int flags, int num_blocks) {
+    SEP_ASSERT(dl_dy.is_cuda() && dl_dy.is_contiguous() && dl_dy.scalar_type() == at::kBFloat16 && dl_dy.dim() == 2 &&
+               dl_dy.size(0) == st->num_tokens && dl_dy.size(1) == st->hidden, "dL_dy must be contiguous [T, H] bf16");
+    PushParams p = make_push_params(*st, dl_dy, true, g->record, kKindDispatchGrads, g->epoch, flags,
+                                    g->bwd_dispatch_arrival_count.data_ptr<int>(), 4);
+    if (flags & 2) ++gate_issued_[1];
+    launch_dispatch_push(p, num_blocks, at::cuda::getCurrentCUDAStream());
+    SEP_CUDA_CHECK(cudaGetLastError());
+  }
+
+  // ---- combine / combine_grads -------------------------------------------------------------------
+  std::shared_ptr<CombineState> combine_begin(const std::shared_ptr<DispatchState>& st, const at::Tensor& x,
+                                              const at::Tensor& done, const std::optional<at::Tensor>& weights, bool is_fwd) {
+    SEP_ASSERT(x.is_cuda() && x.is_contiguous() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 &&
+               x.size(0) == st->num_recv_tokens && x.size(1) == st->hidden, "combine input must be contiguous [T_recv, H] bf16");
+    SEP_ASSERT(done.scalar_type() == at::kLong && done.numel() == st->num_recv_tokens, "gate must be int64 [T_recv]");
+    auto c = std::make_shared<CombineState>();
+    auto stream = at::cuda::getCurrentCUDAStream();
+    // Peers read these through NVLink, so they must sit in the arena.  Tensors the caller already
+    // keeps there (handle.o, handle.y_done_per_token, Buffer.alloc_symmetric results) are used in
+    // place, which is what lets the gate be written while this kernel runs.
+    auto to_sym = [&](const at::Tensor& t) {
+      if (t.numel() == 0 || is_symmetric(t)) return t;
+      auto s = alloc_symmetric(t.sizes().vec(), t.scalar_type(), false);
+      if (t.numel() > 0) SEP_CUDA_CHECK(cudaMemcpyAsync(s.data_ptr(), t.data_ptr(), t.nbytes(), cudaMemcpyDeviceToDevice, stream));
+      return s;
+    };
+    c->x_sym = to_sym(x);
+    c->done_sym = to_sym(done);
+    c->record = BufferRecord{};
+    c->record.aux0 = x.numel() ? symmetric_offset(c->x_sym) : 0;
+    c->record.aux1 = done.numel() ? symmetric_offset(c->done_sym) : 0;
+    if (!is_fwd) {
+      SEP_ASSERT(weights.has_value() && weights->scalar_type() == at::kFloat && weights->is_contiguous(), "combine_grads needs fp32 per-slot weight grads");
+      c->w_sym = to_sym(*weights);
+      c->record.aux2 = weights->numel() ? symmetric_offset(c->w_sym) : 0;
+    }
+    c->out = at::empty({static_cast<int64_t>(st->num_tokens), static_cast<int64_t>(st->hidden)}, x.options());
+    if (!is_fwd) c->out_topk_weights = at::empty({static_cast<int64_t>(st->num_tokens), static_cast<int64_t>(st->num_topk)}, x.options().dtype(at::kFloat));
+    c->epoch = ++epochs_[is_fwd ? kKindCombine : kKindCombineGrads];
+    return c;
+  }
+  void combine_launch(const std::shared_ptr<DispatchState>& st, const std::shared_ptr<CombineState>& c, bool is_fwd,
+                      int64_t seq, int flags, int num_blocks) {
+    CombineParams p{};
+    p.num_tokens = st->num_tokens; p.hidden = st->hidden; p.num_topk = st->num_topk; p.num_ranks = num_ranks_;
+    p.rank = rank_; p.num_experts = st->num_experts; p.is_fwd = is_fwd ? 1 : 0; p.seq = seq;
+    p.kind = is_fwd ? kKindCombine : kKindCombineGrads; p.epoch = c->epoch; p.flags = flags;
+    p.send_recv_token = st->send_recv_token.data_ptr<int>(); p.pair_slot = st->pair_slot.data_ptr<int>();
+    p.topk_idx = reinterpret_cast<const long long*>(st->topk_idx.data_ptr<int64_t>());
+    p.out = c->out.data_ptr(); p.out_topk_weights = is_fwd ? nullptr : c->out_topk_weights.data_ptr<float>();
+    fill_peers(p.peer_base); p.ctl = ctl_; p.own = c->record;
+    p.blocks_done = counters_ + (is_fwd ? 6 : 7);
+    p.status = status_; p.wait_budget_ns = budget_ns_;
+    launch_combine_pull(p, num_blocks, at::cuda::getCurrentCUDAStream());
+    SEP_CUDA_CHECK(cudaGetLastError());
+  }
+
+  // ---- barrier ------------------------------------------------------------------------------------
+  void barrier() {
+    BarrierParams p{};
+    p.num_ranks = num_ranks_; p.rank = rank_; p.epoch = ++epochs_[kKindBarrier];
+    fill_peers(p.peer_base); p.ctl = ctl_; p.status = status_; p.wait_budget_ns = budget_ns_;
+    launch_device_barrier(p, at::cuda::getCurrentCUDAStream());
+    SEP_CUDA_CHECK(cudaGetLastError());
+  }
+  // Emulated ranks run one after another on one device: a barrier there is "every rank bumped its
+  // epoch and stored its flags", with nobody waiting.
+  int next_epoch(int kind) { return ++epochs_[kind]; }
+
+  // ---- grouped GEMM ---------------------------------------------------------------------------------
+  void grouped_gemm(const GemmArgs& a) {
+    SEP_ASSERT(a.a.is_cuda() && a.a.scalar_type() == at::kBFloat16 && a.a.is_contiguous(), "GEMM operand A must be contiguous bf16");
+    SEP_ASSERT(a.b.is_cuda() && a.b.scalar_type() == at::kBFloat16 && a.b.is_contiguous(), "GEMM operand B must be contiguous bf16");
+    SEP_ASSERT(a.block_n == 128 || a.block_n == 256, "block_n must be 128 or 256");
+    GemmParams p{};
+    p.mode = a.mode; p.epilogue = a.epilogue; p.block_n = a.block_n;
+    p.a_mn_major = a.a_mn_major; p.b_mn_major = a.b_mn_major;
+    p.rank = rank_; p.status = status_; p.wait_budget_ns = budget_ns_;
+    CUtensorMap ta, tb;
+    const int BN = a.block_n;
+    if (a.mode == kVarlenM) {
+      // A: [rows, K] row-major; B: weights [E, N, K] (K-major) or [E, K, N] (MN-major)
+      SEP_ASSERT(a.a.dim() == 2 && a.b.dim() == 3 && a.tile_id_to_expert.has_value(), "varlen-M GEMM needs A [rows, K], B [E, ., .] and tile_id_to_expert");
+      const int64_t rows = a.a.size(0), K = a.a.size(1), E = a.b.size(0);
+      const int64_t N = a.b_mn_major ? a.b.size(2) : a.b.size(1);
+      SEP_ASSERT((a.b_mn_major ? a.b.size(1) : a.b.size(2)) == K, "GEMM reduction lengths disagree");
+      SEP_ASSERT(K % 8 == 0 && N % 8 == 0, "K and N must be multiples of 8");
+      p.N = N; p.K = K; p.num_experts = E; p.total_rows = rows;
+      p.num_m_tiles = a.num_m_tiles >= 0 ? a.num_m_tiles : a.tile_id_to_expert->numel();
+      SEP_ASSERT(static_cast<int64_t>(p.num_m_tiles) * BM_ <= rows, "tile list longer than A");
+      p.num_n_tiles = (N + BN - 1) / BN;
+      p.tile_id_to_expert = a.tile_id_to_expert->data_ptr<int>();
+      if (rows == 0 || p.num_m_tiles == 0) return;
+      ta = make_tmap(a.a.data_ptr(), K, rows, 1, K, rows * K, 64, BM_);
+      if (a.b_mn_major) tb = make_tmap(a.b.data_ptr(), N, K, E, N, K * N, 64, 64);
+      else tb = make_tmap(a.b.data_ptr(), K, N, E, K, N * K, 64, BN);
+    } else {
+      // dW: A [rows, M], B [rows, N] row-major; out [E, M, N]
+      SEP_ASSERT(a.a.dim() == 2 && a.b.dim() == 2 && a.a.size(0) == a.b.size(0), "varlen-K GEMM needs A [rows, M] and B [rows, N]");
+      SEP_ASSERT(a.a_mn_major && a.b_mn_major && a.epilogue == kEpiStore, "varlen-K GEMM is MN-major x MN-major with the store epilogue");
+      SEP_ASSERT(a.expert_pool_block_offset.has_value() && a.expert_frequency.has_value() && a.out0.has_value(), "varlen-K GEMM needs expert offsets, true lengths and an output");
+      const int64_t rows = a.a.size(0), M = a.a.size(1), N = a.b.size(1), E = a.expert_frequency->numel();
+      SEP_ASSERT(M % 8 == 0 && N % 8 == 0, "M and N must be multiples of 8");
+      p.N = N; p.M_out = M; p.num_experts = E; p.total_rows = rows;
+      p.num_m_tiles = (M + BM_ - 1) / BM_; p.num_n_tiles = (N + BN - 1) / BN;
+      p.expert_pool_block_offset = a.expert_pool_block_offset->data_ptr<int>();
+      p.expert_frequency = a.expert_frequency->data_ptr<int>();
+      p.out_expert_stride = M * N;
+      if (rows == 0) { a.out0->zero_(); return; }
+      ta = make_tmap(a.a.data_ptr(), M, rows, 1, M, rows * M, 64, 64);
+      tb = make_tmap(a.b.data_ptr(), N, rows, 1, N, rows * N, 64, 64);
+    }
+    if (a.arrival_count.has_value()) {
+      SEP_ASSERT(a.arrival_target.has_value(), "arrival_count needs arrival_target");
+      p.arrival_count = a.arrival_count->data_ptr<int>(); p.arrival_target = a.arrival_target->data_ptr<int>();
+    }
+    if (a.started_flag >= 0) p.started_flag = gate_flags_ + a.started_flag;
+    auto ld = [](const at::Tensor& t) { return t.dim() >= 2 ? t.stride(t.dim() - 2) : t.numel(); };
+    if (a.out0.has_value()) { p.out0 = a.out0->data_ptr(); p.ld0 = ld(*a.out0); }
+    if (a.out1.has_value()) { p.out1 = a.out1->data_ptr(); p.ld1 = ld(*a.out1); }
+    if (a.preact.has_value()) { p.preact = a.preact->data_ptr(); p.ld_preact = ld(*a.preact); }
+    if (a.row_weight.has_value()) p.row_weight = a.row_weight->data_ptr<float>();
+    if (a.row_token.has_value()) p.row_token = a.row_token->data_ptr<int>();
+    if (a.dl_dweight.has_value()) p.dl_dweight = a.dl_dweight->data_ptr<float>();
+    if (a.scatter_local.has_value()) p.scatter_local = a.scatter_local->data_ptr();
+    if (a.row_src.has_value()) p.row_src = reinterpret_cast<const int2*>(a.row_src->data_ptr<int>());
+    if (a.row_k_slot.has_value()) p.row_k_slot = a.row_k_slot->data_ptr<int>();
+    if (a.tile_stripes_done.has_value()) p.tile_stripes_done = a.tile_stripes_done->data_ptr<int>();
+    if (a.k_remaining.has_value()) p.k_remaining = a.k_remaining->data_ptr<int>();
+    if (a.done_per_token.has_value()) p.done_per_token = reinterpret_cast<long long*>(a.done_per_token->data_ptr<int64_t>());
+    p.seq = a.seq; p.num_topk = a.num_topk;
+    p.scatter_remote = a.scatter_remote ? 1 : 0; p.return_dweight = a.return_dweight ? 1 : 0;
+    if (a.epilogue == kEpiScatter || a.epilogue == kEpiDswiglu) SEP_ASSERT(p.row_token != nullptr, "this epilogue needs pool_recv_token");
+    if (a.epilogue == kEpiScatter) {
+      if (a.scatter_remote) {
+        SEP_ASSERT(static_cast<int>(a.peer_out_offsets.size()) == num_ranks_ && p.row_src != nullptr, "remote scatter needs one accumulator offset per rank and pool_src");
+        for (int r = 0; r < num_ranks_; ++r) p.peer_out[r] = static_cast<char*>(peer_base_[r]) + a.peer_out_offsets[r];
+      } else {
+        SEP_ASSERT(p.scatter_local != nullptr, "local scatter needs a destination");
+      }
+    }
+    if (a.epilogue == kEpiDswiglu) {
+      SEP_ASSERT(p.preact != nullptr && p.out0 != nullptr && p.out1 != nullptr, "dswiglu epilogue needs preact and both outputs");
+      if (a.return_dweight) {
+        SEP_ASSERT(static_cast<int>(a.peer_dw_offsets.size()) == num_ranks_ && p.row_src != nullptr && p.row_k_slot != nullptr &&
+                   p.tile_stripes_done != nullptr && p.dl_dweight != nullptr, "dL/dweight return needs offsets, pool_src, pool_k_slot, stripe counters and dl_dweight");
+        for (int r = 0; r < num_ranks_; ++r) p.peer_dw_out[r] = reinterpret_cast<float*>(static_cast<char*>(peer_base_[r]) + a.peer_dw_offsets[r]);
+      }
+    }
+    if (a.epilogue == kEpiSwiglu || a.epilogue == kEpiStore) SEP_ASSERT(p.out0 != nullptr, "this epilogue needs out0");
+    if (a.tail) {
+      p.tail.enabled = 1; p.tail.kind = a.tail_kind; p.tail.epoch = ++epochs_[a.tail_kind];
+      p.tail.num_ranks = num_ranks_; p.tail.rank = rank_; p.tail.wait = a.tail_wait ? 1 : 0;
+      fill_peers(p.tail.peer_base); p.tail.ctl = ctl_;
+      p.tail.ctas_done = counters_ + (a.tail_kind == kKindGemmYTail ? 8 : 9);
+    }
+    int n_ctas = a.num_ctas > 0 ? a.num_ctas : num_sms();
+    const int64_t total = static_cast<int64_t>(a.mode == kVarlenM ? p.num_m_tiles : p.num_experts * p.num_m_tiles) * p.num_n_tiles;
+    PushParams pp{};
+    const PushParams* ppp = nullptr;
+    if (a.fused_push) {
+      pp = make_push_params(*a.fused_push, a.fused_push->x, false, a.fused_push->record, kKindDispatch,
+                            a.fused_push->push_epoch, a.push_flags, a.fused_push->pool_arrival_count.data_ptr<int>(), 2);
+      pp.started_flag = nullptr;
+      ppp = &pp;
+    } else if (a.fused_push_grads) {
+      SEP_ASSERT(a.fused_push_routing && a.fused_push_rows.defined(), "fused dispatch_grads needs the forward routing and dL_dy");
+      pp = make_push_params(*a.fused_push_routing, a.fused_push_rows, true, a.fused_push_grads->record, kKindDispatchGrads,
+                            a.fused_push_grads->epoch, a.push_flags, a.fused_push_grads->bwd_dispatch_arrival_count.data_ptr<int>(), 4);
+      pp.started_flag = nullptr;
+      ppp = &pp;
+    }
+    if (ppp == nullptr) n_ctas = static_cast<int>(std::min<int64_t>(n_ctas, std::max<int64_t>(total, 1)));
+    launch_grouped_gemm(p, &ta, &tb, ppp, n_ctas, at::cuda::getCurrentCUDAStream());
+    SEP_CUDA_CHECK(cudaGetLastError());
+  }
+
+  // ---- small ops ---------------------------------------------------------------------------------------
+  void tile_producer(const at::Tensor& count, const at::Tensor& target, double delay_us) {
+    launch_tile_producer(count.data_ptr<int>(), target.data_ptr<int>(), count.numel(), static_cast<long long>(delay_us * 1000.0),
+                         at::cuda::getCurrentCUDAStream());
+    SEP_CUDA_CHECK(cudaGetLastError());
+  }
+  at::Tensor pool_compress(const at::Tensor& pool, const at::Tensor& pool_recv_token, int64_t num_recv) {
+    SEP_ASSERT(pool.is_contiguous() && pool.scalar_type() == at::kBFloat16 && pool.size(1) % 8 == 0, "pool must be contiguous bf16 with hidden % 8 == 0");
+    auto out = at::empty({num_recv, pool.size(1)}, pool.options());
+    launch_pool_compress(pool.data_ptr(), out.data_ptr(), pool_recv_token.data_ptr<int>(), pool.size(0), pool.size(1), at::cuda::getCurrentCUDAStream());
+    SEP_CUDA_CHECK(cudaGetLastError());
+    return out;
+  }
+  at::Tensor pool_expand(const at::Tensor& recv, const at::Tensor& pool_recv_token, int64_t tk_padded) {
+    SEP_ASSERT(recv.is_contiguous() && recv.scalar_type() == at::kBFloat16 && recv.size(1) % 8 == 0, "recv must be contiguous bf16 with hidden % 8 == 0");
+    auto out = at::empty({tk_padded, recv.size(1)}, recv.options());
+    launch_pool_expand(recv.data_ptr(), out.data_ptr(), pool_recv_token.data_ptr<int>(), tk_padded, recv.size(1), at::cuda::getCurrentCUDAStream());
+    SEP_CUDA_CHECK(cudaGetLastError());
+    return out;
+  }
+  std::vector<at::Tensor> router(const at::Tensor& x, const at::Tensor& w_gate, int top_k, int num_ranks, bool renormalize, bool want_probs) {
+    SEP_ASSERT(x.is_contiguous() && w_gate.is_contiguous() && x.scalar_type() == at::kBFloat16 && w_gate.scalar_type() == at::kBFloat16, "router inputs must be contiguous bf16");
+    SEP_ASSERT(x.size(1) == w_gate.size(1) && x.size(1) % 8 == 0, "router hidden mismatch");
+    SEP_ASSERT(w_gate.size(0) <= 512 && top_k <= 32 && w_gate.size(0) % num_ranks == 0, "router supports up to 512 experts and top-32");
+    RouterParams p{};
+    p.x = x.data_ptr(); p.w_gate = w_gate.data_ptr();
+    p.num_tokens = x.size(0); p.hidden = x.size(1); p.num_experts = w_gate.size(0); p.num_topk = top_k;
+    p.num_ranks = num_ranks; p.renormalize = renormalize ? 1 : 0;
+    auto idx = at::empty({x.size(0), top_k}, x.options().dtype(at::kLong));
+    auto w = at::empty({x.size(0), top_k}, x.options().dtype(at::kFloat));
+    auto in_rank = at::empty({x.size(0), num_ranks}, x.options().dtype(at::kBool));
+    at::Tensor probs;
+    if (want_probs) probs = at::empty({x.size(0), w_gate.size(0)}, x.options().dtype(at::kFloat));
+    p.topk_idx = reinterpret_cast<long long*>(idx.data_ptr<int64_t>()); p.topk_weights = w.data_ptr<float>();
+    p.is_token_in_rank = reinterpret_cast<unsigned char*>(in_rank.data_ptr<bool>());
+    p.probs = want_probs ? probs.data_ptr<float>() : nullptr;
+    if (p.num_tokens > 0) launch_router(p, at::cuda::getCurrentCUDAStream());
+    SEP_CUDA_CHECK(cudaGetLastError());
+    return {idx, w, in_rank, probs};
+  }
+
+ private:
+  static constexpr int BM_ = kTileM;
+  void fill_peers(void** dst) const { for (int i = 0; i < kMaxRanks; ++i) dst[i] = peer_base_[i]; }
+  void finish_sync() {
+    // keeps the slab alive as long as any arena tensor or the runtime itself exists
+    void* base = base_;
+    arena_guard_ = std::shared_ptr<void>(base, [](void* p) { cudaFree(p); });
+    available_ = true;
+  }
+  int num_sms() {
+    if (num_sms_ == 0) {
+      cudaDeviceProp prop;
+      SEP_CUDA_CHECK(cudaGetDeviceProperties(&prop, device_));
+      num_sms_ = prop.multiProcessorCount;
+    }
+    return num_sms_;
+  }
+
+  int rank_, num_ranks_, num_channels_, device_ = 0, num_sms_ = 0;
+  ControlLayout ctl_{};
+  void* base_ = nullptr;
+  size_t arena_bytes_ = 0;
+  std::shared_ptr<Arena> arena_;
+  std::shared_ptr<void> arena_guard_;
+  void* peer_base_[kMaxRanks];
+  bool opened_[kMaxRanks] = {false, false, false, false, false, false, false, false};
+  void* scratch_ = nullptr;
+  StatusBlock* status_ = nullptr;
+  int* gate_flags_ = nullptr;
+  int* counters_ = nullptr;
+  HostCounters* host_ = nullptr;
+  HostCounters* host_dev_ = nullptr;
+  unsigned long long budget_ns_ = 0;
+  int64_t timeout_ms_ = 0;
+  int epochs_[kNumKinds];
+  int gate_issued_[8];
+  bool available_ = false, destroyed_ = false;
+};
+
+}  // namespace sep
+
+// -------------------------------------------------------------------------------------------------
+// Host-only arena exerciser (no CUDA calls) so the allocator logic is testable on a CPU-only box.
+// -------------------------------------------------------------------------------------------------
+struct ArenaProbe {
+  sep::Arena arena;
+  ArenaProbe(int64_t offset, int64_t size) : arena(offset, size) {}
+  int64_t allocate(int64_t bytes) { return arena.allocate(bytes); }
+  void release(int64_t off) { arena.release(off); }
+  int64_t in_use() const { return arena.bytes_in_use(); }
+  int64_t high_water() const { return arena.high_water(); }
+  int64_t capacity() const { return arena.capacity(); }
+  int64_t free_blocks() const { return arena.num_free_blocks(); }
+};
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  using namespace sep;
+  m.doc() = "streamep_b200 native runtime (sm_100a)";
+  m.attr("TILE_M") = kTileM;
+  m.attr("MAX_RANKS") = kMaxRanks;
+  m.attr("MAX_CHANNELS") = kMaxChannels;
+  m.attr("MAX_EXPERTS") = kMaxExperts;
+  m.def("is_sm100_compiled", [] { return true; });
+  m.def("layer_bytes_hint", &ArenaSizeHint::layer_bytes);
+
+  py::class_<ArenaProbe>(m, "ArenaProbe")
+      .def(py::init<int64_t, int64_t>())
+      .def("allocate", &ArenaProbe::allocate).def("release", &ArenaProbe::release)
+      .def("in_use", &ArenaProbe::in_use).def("high_water", &ArenaProbe::high_water)
+      .def("capacity", &ArenaProbe::capacity).def("free_blocks", &ArenaProbe::free_blocks);
+
+  py::class_<Config>(m, "Config")
+      .def(py::init<int, int, int, int, int>(), py::arg("num_sms") = 20, py::arg("num_max_nvl_chunked_send_tokens") = 6,
+           py::arg("num_max_nvl_chunked_recv_tokens") = 256, py::arg("num_max_rdma_chunked_send_tokens") = 6,
+           py::arg("num_max_rdma_chunked_recv_tokens") = 256)
+      .def_readonly("num_sms", &Config::num_sms)
+      .def_readonly("num_max_nvl_chunked_send_tokens", &Config::num_max_nvl_chunked_send_tokens)
+      .def_readonly("num_max_nvl_chunked_recv_tokens", &Config::num_max_nvl_chunked_recv_tokens)
+      .def_readonly("num_max_rdma_chunked_send_tokens", &Config::num_max_rdma_chunked_send_tokens)
+      .def_readonly("num_max_rdma_chunked_recv_tokens", &Config::num_max_rdma_chunked_recv_tokens);
+
+  py::class_<EventHandle>(m, "EventHandle")
+      .def(py::init<>())
+      .def("current_stream_wait", &EventHandle::current_stream_wait)
+      .def("wait_on", &EventHandle::wait_on);
+
+  py::class_<DispatchState, std::shared_ptr<DispatchState>>(m, "DispatchState")
+#define RO(name) .def_readonly(#name, &DispatchState::name)
+      RO(x) RO(topk_idx) RO(topk_weights) RO(num_tokens) RO(hidden) RO(num_topk) RO(num_experts) RO(tile_m) RO(seq)
+      RO(pair_rank) RO(pair_slot) RO(token_rank_in_channel) RO(send_recv_token) RO(send_head) RO(is_token_in_rank)
+      RO(channel_prefix_matrix) RO(send_base) RO(send_token_base) RO(peer_total_tiles) RO(peer_num_recv)
+      RO(expert_frequency) RO(expert_pool_block_offset) RO(base_pool) RO(seen_per_substream) RO(rank_prefix_matrix)
+      RO(recv_channel_prefix_matrix) RO(tile_id_to_expert) RO(pool_arrival_target)
+      RO(pool) RO(pool_topk_weight) RO(pool_recv_token) RO(pool_k_slot) RO(pool_src) RO(recv_token_to_slots)
+      RO(k_local_total) RO(k_local_remaining) RO(pool_arrival_count) RO(recv_src) RO(y_done_per_token) RO(o)
+      RO(total_tiles) RO(num_recv_tokens) RO(recv_per_expert) RO(metadata_done_event)
+#undef RO
+      .def("release_o", &DispatchState::release_o)
+      .def("release_pool", &DispatchState::release_pool);
+
+  py::class_<GradsState, std::shared_ptr<GradsState>>(m, "GradsState")
+      .def_readonly("dl_do_pool", &GradsState::dl_do_pool)
+      .def_readonly("bwd_dispatch_arrival_count", &GradsState::bwd_dispatch_arrival_count)
+      .def_readonly("started_event", &GradsState::started_event);
+
+  py::class_<CombineState, std::shared_ptr<CombineState>>(m, "CombineState")
+      .def_readonly("out", &CombineState::out)
+      .def_readonly("out_topk_weights", &CombineState::out_topk_weights);
+
+  py::class_<GemmArgs>(m, "GemmArgs")
+      .def(py::init<>())
+#define RW(name) .def_readwrite(#name, &GemmArgs::name)
+      RW(mode) RW(epilogue) RW(block_n) RW(num_ctas) RW(a_mn_major) RW(b_mn_major) RW(a) RW(b)
+      RW(tile_id_to_expert) RW(expert_pool_block_offset) RW(expert_frequency) RW(arrival_count) RW(arrival_target)
+      RW(out0) RW(out1) RW(preact) RW(row_weight) RW(row_token) RW(dl_dweight) RW(scatter_local) RW(row_src) RW(row_k_slot)
+      RW(tile_stripes_done) RW(k_remaining) RW(done_per_token) RW(peer_out_offsets) RW(peer_dw_offsets)
+      RW(scatter_remote) RW(return_dweight) RW(num_topk) RW(seq) RW(num_m_tiles) RW(started_flag)
+      RW(tail) RW(tail_kind) RW(tail_wait) RW(fused_push) RW(fused_push_grads) RW(fused_push_routing) RW(fused_push_rows)
+      RW(push_flags);
+#undef RW
+
+  py::class_<Runtime>(m, "Runtime")
+      .def(py::init<int, int, int64_t, int, int, int64_t>(), py::arg("rank"), py::arg("num_ranks"), py::arg("arena_bytes"),
+           py::arg("num_channels"), py::arg("num_experts_cap"), py::arg("timeout_ms"))
+      .def("destroy", &Runtime::destroy)
+      .def("get_local_device_id", &Runtime::get_local_device_id)
+      .def("get_local_ipc_handle", &Runtime::get_local_ipc_handle)
+      .def("get_local_base_ptr", &Runtime::get_local_base_ptr)
+      .def("sync", &Runtime::sync)
+      .def("sync_local", &Runtime::sync_local)
+      .def("is_available", &Runtime::is_available)
+      .def("set_timeout_ms", &Runtime::set_timeout_ms)
+      .def("get_timeout_ms", &Runtime::get_timeout_ms)
+      .def_property_readonly("rank", &Runtime::rank)
+      .def_property_readonly("num_ranks", &Runtime::num_ranks)
+      .def_property_readonly("num_channels", &Runtime::num_channels)
+      .def("arena_bytes_in_use", &Runtime::arena_bytes_in_use)
+      .def("arena_high_water", &Runtime::arena_high_water)
+      .def("arena_capacity", &Runtime::arena_capacity)
+      .def("alloc_symmetric", [](Runtime& r, const std::vector<int64_t>& sizes, py::object dtype, bool zero) {
+        return r.alloc_symmetric(sizes, torch::python::detail::py_object_to_dtype(dtype), zero);
+      }, py::arg("sizes"), py::arg("dtype"), py::arg("zero") = false)
+      .def("is_symmetric", &Runtime::is_symmetric)
+      .def("symmetric_offset", &Runtime::symmetric_offset)
+      .def("poll_status", &Runtime::poll_status, py::arg("reset") = true)
+      .def("gate_wait_started", &Runtime::gate_wait_started)
+      .def("gate_bump_issued", &Runtime::gate_bump_issued)
+      .def("gate_flag_tensor", &Runtime::gate_flag_tensor)
+      .def("dispatch_begin", &Runtime::dispatch_begin)
+      .def("dispatch_metadata", &Runtime::dispatch_metadata)
+      .def("dispatch_allocate", &Runtime::dispatch_allocate)
+      .def("dispatch_push", &Runtime::dispatch_push)
+      .def("grads_begin", &Runtime::grads_begin)
+      .def("grads_push", &Runtime::grads_push)
+      .def("combine_begin", &Runtime::combine_begin)
+      .def("combine_launch", &Runtime::combine_launch)
+      .def("barrier", &Runtime::barrier)
+      .def("next_epoch", &Runtime::next_epoch)
+      .def("grouped_gemm", &Runtime::grouped_gemm)
+      .def("tile_producer", &Runtime::tile_producer)
+      .def("pool_compress", &Runtime::pool_compress)
+      .def("pool_expand", &Runtime::pool_expand)
+      .def("router", &Runtime::router);
+}
