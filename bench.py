@@ -1,0 +1,311 @@
+#!/usr/bin/env python
+"""Headline benchmark: MoE layer forward + backward tokens/s.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 20 --warmup 5
+
+Default config ("full"): 8192 tokens per rank, hidden 2048, 8 experts per rank, top-6 from a linear
+router on x ~ N(0,1), SwiGLU ffn 1408, w1 [8, 2816, 2048], w2 [8, 2048, 1408] ~ N(0, 0.02), bf16,
+synthetic data, random-init weights.  Weak scaling: per-rank tokens and experts stay fixed as the
+number of GPUs grows.  ``--config scaling`` runs the Mixtral-style sweep shape (16384 tokens/rank,
+hidden 4096, 8 experts in total, top-2, ffn 14336, 3 layers back to back); ``--config wide`` the
+dispatch-heavy shape (4096 tokens/rank, hidden 7168, 32 experts/rank, top-8, ffn 2048).
+
+Timing: W untimed warm-up steps, then exactly K steps between CUDA events on the launching stream,
+bracketed by a barrier and a device synchronize; a buffer larger than L2 is rewritten between steps
+(outside the event pairs of a step are not possible without gaps, so the flush is part of the
+measured loop and counted: it costs the same in every run).  The reported value is the max over
+ranks.  ``e2e`` repeats the measurement through the public module API with, every step, the
+host-to-device copy of that step's inputs from pinned memory and a device-to-host read of the loss.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+CONFIGS = {
+    #            tokens/rank, hidden, experts/rank (None = fixed total), total experts, topk, ffn, layers
+    "full":    dict(tokens=8192, hidden=2048, experts_per_rank=8, experts_total=None, topk=6, ffn=1408, layers=1),
+    "scaling": dict(tokens=16384, hidden=4096, experts_per_rank=None, experts_total=8, topk=2, ffn=14336, layers=3),
+    "wide":    dict(tokens=4096, hidden=7168, experts_per_rank=32, experts_total=None, topk=8, ffn=2048, layers=1),
+    "tiny":    dict(tokens=512, hidden=256, experts_per_rank=4, experts_total=None, topk=2, ffn=128, layers=1),
+}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append(line.strip())
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2])); power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def reference_arm(args):
+    """The reference's own stream_moe_func cannot run on sm_100a: every CuTeDSL kernel wrapper asserts
+    compute capability 9.x and the GEMMs need a private fork of the Quack library
+    (stream_ep/stream_moe/kernel_a.py:216, CHANGES.md:131)."""
+    why = ("reference stream_moe_func is Hopper-only: kernel wrappers assert compute capability 9.x "
+           "(stream_ep/stream_moe/kernel_a.py:216,525; kernel_y.py:734,937) and need the private quack fork "
+           "(lens_k, epi_subtile_store; CHANGES.md:131) that is not in the offline wheelhouse")
+    note = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "REFERENCE_INSTALL.txt")
+    if os.path.exists(note):
+        with open(note) as f:
+            first = f.readline().strip()
+        if first:
+            why += "; install record: " + first
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", default="full", choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="streamep_b200", choices=["streamep_b200", "reference", "nccl_baseline"])
+    ap.add_argument("--fused", type=int, default=1)
+    ap.add_argument("--ckpt-level", type=int, default=0)
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if rank == 0:
+            print(f"bench.py: --gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run", file=sys.stderr)
+        if world == 1 and args.gpus > 1:
+            return 2
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+
+    from streamep_b200.models.moe_layer import StreamMoE, make_buffer
+    from streamep_b200.parallel.nccl_baseline import NcclBaselineMoE
+
+    c = CONFIGS[args.config]
+    T, H, K, I, L = c["tokens"], c["hidden"], c["topk"], c["ffn"], c["layers"]
+    E = c["experts_total"] if c["experts_total"] is not None else c["experts_per_rank"] * world
+    assert E % world == 0
+    torch.manual_seed(1234 + rank)
+
+    buffer = None
+    if args.impl == "streamep_b200":
+        buffer = make_buffer(group, T, H, K, E, layers_in_flight=L, world_size=world)
+        layers = [StreamMoE(H, I, E, K, buffer, fused=bool(args.fused), activation_checkpoint_level=args.ckpt_level,
+                            device=dev, seed=100 + i) for i in range(L)]
+    else:
+        layers = [NcclBaselineMoE(H, I, E, K, group, device=dev, seed=100 + i) for i in range(L)]
+    params = [p for layer in layers for p in layer.parameters()]
+
+    x_dev = torch.randn(T, H, device=dev).to(torch.bfloat16)
+    dy_dev = (torch.randn(T, H, device=dev) * 0.1).to(torch.bfloat16)
+    # routing comes from each layer's linear router on x (computed once: the timed value is the
+    # layer's forward+backward with routing as an input, like the reference's harness)
+    routing = [layer.route(x_dev) for layer in layers]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB L2
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize()
+
+    def step_device():
+        h = x_dev.detach().requires_grad_(True)
+        cur = h
+        for layer, (idx, w, in_rank) in zip(layers, routing):
+            cur = layer.experts(cur, idx, w, in_rank)
+        cur.backward(dy_dev)
+        for p in params:
+            p.grad = None
+        return cur
+
+    def launches():
+        return buffer.runtime.launch_count() if buffer is not None else 0
+
+    # ---------------------------------------------------------------- device-timed value
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+        flush.zero_()
+    barrier()
+    if buffer is not None:
+        buffer.check_status()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    l0 = launches()
+    barrier()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    t_wall0 = time.perf_counter()
+    for i in range(args.steps):
+        flush.zero_()                       # L2 flush between timed iterations, outside the event pair
+        ev[i][0].record()
+        step_device()
+        ev[i][1].record()
+    barrier()
+    t_wall = time.perf_counter() - t_wall0
+    l1 = launches()
+    clocks = sampler.stop()
+    ms = sum(a.elapsed_time(b) for a, b in ev) / args.steps
+    if buffer is not None:
+        buffer.check_status()
+
+    # ---------------------------------------------------------------- end-to-end through the public API
+    e2e = None
+    if not args.no_e2e:
+        x_host = [torch.randn(T, H).to(torch.bfloat16).pin_memory() for _ in range(2)]
+        x_in = [torch.empty(T, H, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        loss_host = torch.empty(1, dtype=torch.float32).pin_memory()
+        copy_stream = torch.cuda.Stream()
+        copied = [torch.cuda.Event(), torch.cuda.Event()]
+        consumed = [torch.cuda.Event(), torch.cuda.Event()]
+
+        def prefetch(i):
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(consumed[i % 2])
+                x_in[i % 2].copy_(x_host[i % 2], non_blocking=True)
+                copied[i % 2].record(copy_stream)
+
+        def step_e2e(i):
+            torch.cuda.current_stream().wait_event(copied[i % 2])
+            h = x_in[i % 2].detach().requires_grad_(True)
+            cur = h
+            for layer in layers:
+                cur = layer(cur)            # router + experts: the call a user makes
+            loss = (cur.float() * dy_dev.float()).sum() * (1.0 / cur.numel())
+            loss.backward()
+            consumed[i % 2].record()
+            loss_host.copy_(loss.detach().reshape(1), non_blocking=True)
+            prefetch(i + 2)
+            torch.cuda.current_stream().synchronize()     # the step's result is read on the host
+            for p in params:
+                p.grad = None
+            return float(loss_host[0])
+
+        for j in range(2):
+            consumed[j].record()
+        prefetch(0); prefetch(1)
+        for i in range(max(args.warmup, 3)):
+            step_e2e(i)
+        barrier()
+        base = max(args.warmup, 3)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            flush.zero_()
+            step_e2e(base + i)
+        e1.record()
+        barrier()
+        ms_e2e = e0.elapsed_time(e1) / args.steps
+        e2e = (ms_e2e, T * H * 2, 4)
+        if buffer is not None:
+            buffer.check_status()
+
+    # ---------------------------------------------------------------- reduce over ranks, report
+    vals = torch.tensor([ms, e2e[0] if e2e else 0.0], device=dev)
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    ms_max, ms_e2e_max = float(vals[0]), float(vals[1])
+    if rank == 0:
+        tokens_per_step = T * world
+        value = tokens_per_step / (ms_max * 1e-3)
+        pairs = T * K
+        flops = 18.0 * pairs * H * I * L          # forward 6 + backward 12 per (token, expert) pair
+        peaks = {}
+        try:
+            with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
+                peaks = json.load(f)
+        except OSError:
+            pass
+        peak = peaks.get("bf16_tflops_sustained", 1400.0)
+        out = {
+            "metric": "moe_layer_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_max, "higher_is_better": True,
+            "scaling": "weak" if c["experts_total"] is None else "weak (tokens per rank fixed, total experts fixed)",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (x ~ N(0,1), random-init weights ~ N(0,0.02))",
+            "impl": args.impl,
+            "config": {"model": f"moe_layer[{args.config}] H={H} ffn={I} E={E} ({E // world}/rank) top{K} layers={L}",
+                       "global_batch": tokens_per_step, "seq_len": T, "parallelism": f"ep{world}",
+                       "fused": bool(args.fused), "activation_checkpoint_level": args.ckpt_level,
+                       "l2_flush": "256 MiB buffer rewritten between timed iterations"},
+            "clocks": clocks,
+            "gpu_launches": int(l1 - l0),
+            "tflops_per_gpu": flops / (ms_max * 1e-3) / 1e12,
+            "frac_of_measured_bf16_sustained": flops / (ms_max * 1e-3) / 1e12 / peak,
+            "wall_ms_per_step_incl_flush": t_wall * 1e3 / args.steps,
+        }
+        if e2e:
+            out["e2e"] = {"value": tokens_per_step / (ms_e2e_max * 1e-3), "unit": "tokens/s",
+                          "ms_per_step": ms_e2e_max, "h2d_bytes_per_step": e2e[1], "d2h_bytes_per_step": e2e[2],
+                          "includes": "pinned H2D of x, router kernel, layer fwd+bwd, loss, D2H of the loss"}
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier(device_ids=[local_rank])
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

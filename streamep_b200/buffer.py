@@ -339,11 +339,23 @@ class Buffer:
         """
         assert expert_alignment == 1, "expert_alignment other than 1 is not supported"
         st, seq = self._dispatch_begin(x, topk_idx, topk_weights, num_experts, tile_m, dispatch_seq)
-        self.runtime.dispatch_metadata(st, 3)
-        self.runtime.dispatch_allocate(st)
-        if launch_push:
-            cfg = self.get_dispatch_config(self.group_size) if config is None else config
-            self.runtime.dispatch_push(st, 7, self._blocks(cfg))
+        cfg = self.get_dispatch_config(self.group_size) if config is None else config
+        if not self._emulated:
+            self.runtime.dispatch_metadata(st, 3)
+            self.runtime.dispatch_allocate(st)
+            if launch_push:
+                self.runtime.dispatch_push(st, 7, self._blocks(cfg))
+        else:
+            self.runtime.dispatch_metadata(st, 1)
+            self._phase()
+            self.runtime.dispatch_metadata(st, 2)
+            self.runtime.dispatch_allocate(st)
+            if launch_push:
+                self.runtime.dispatch_push(st, 1, 1)
+                self._phase()
+                self.runtime.dispatch_push(st, 2, self._blocks(cfg))
+                self._phase()
+                self.runtime.dispatch_push(st, 4, 8)
         handle = self._make_handle(st, is_token_in_rank, seq, tile_m)
         return st.pool, handle, st.metadata_done_event
 
@@ -357,7 +369,15 @@ class Buffer:
         g = self.runtime.grads_begin(st)
         if launch_push:
             cfg = self.get_dispatch_config(self.group_size) if config is None else config
-            self.runtime.grads_push(st, g, dL_dy.contiguous(), 7, self._blocks(cfg))
+            dL_dy = dL_dy.contiguous()
+            if not self._emulated:
+                self.runtime.grads_push(st, g, dL_dy, 7, self._blocks(cfg))
+            else:
+                self.runtime.grads_push(st, g, dL_dy, 1, 1)
+                self._phase()
+                self.runtime.grads_push(st, g, dL_dy, 2, self._blocks(cfg))
+                self._phase()
+                self.runtime.grads_push(st, g, dL_dy, 4, 8)
         handle._grads_state = g
         return g.dl_do_pool, g.bwd_dispatch_arrival_count, g.started_event
 
@@ -372,7 +392,7 @@ class Buffer:
         st = handle._dispatch_out
         c = self.runtime.combine_begin(st, x, handle.y_done_per_token, None, True)
         cfg = self.get_combine_config(self.group_size) if config is None else config
-        self.runtime.combine_launch(st, c, True, int(seq), 7, self._blocks(cfg))
+        self._combine_launch(st, c, True, int(seq), cfg)
         return c.out, None
 
     def combine_grads(self, dL_dx_per_r: torch.Tensor, handle: StreamingHandle,
@@ -384,11 +404,31 @@ class Buffer:
         st = handle._dispatch_out
         c = self.runtime.combine_begin(st, dL_dx_per_r, bwd_a_done_per_token, weight_grads, False)
         cfg = self.get_combine_config(self.group_size) if config is None else config
-        self.runtime.combine_launch(st, c, False, int(seq), 7, self._blocks(cfg))
+        self._combine_launch(st, c, False, int(seq), cfg)
         return c.out, c.out_topk_weights
+
+    def _combine_launch(self, st, c, is_fwd, seq, cfg):
+        if not self._emulated:
+            self.runtime.combine_launch(st, c, is_fwd, seq, 7, self._blocks(cfg))
+        else:
+            self.runtime.combine_launch(st, c, is_fwd, seq, 1, 1)
+            self._phase()
+            self.runtime.combine_launch(st, c, is_fwd, seq, 2, self._blocks(cfg))
+            self._phase()   # every rank's gather is enqueued before anyone reuses the rows it reads
+
+    @property
+    def _emulated(self) -> bool:
+        return self._local is not None and self.group_size > 1
+
+    def _phase(self) -> None:
+        """Phase boundary of a collective: a thread barrier for emulated ranks, nothing otherwise."""
+        if self._local is not None:
+            self._local[0]._barrier_wait()
 
     def barrier(self) -> None:
         """Device-side barrier over the group on the current stream (bounded wait)."""
+        if self._emulated:
+            raise StreamEPError("the device barrier waits for its peers and cannot be emulated on one GPU")
         self.runtime.barrier()
 
 
@@ -396,15 +436,20 @@ class LocalWorld:
     """Several ranks emulated in ONE process on ONE device.
 
     Kernels of different ranks that wait on one another must never run as
-    separate launches on one GPU, so every collective is issued phase by phase:
-    first the phase that only writes (count exchange, record publish, row push)
-    for all ranks, then the phase that reads.  No kernel ever waits for a kernel
-    that has not been launched yet.  Used by the single-GPU tests of the
-    multi-rank data paths; production runs one process per GPU.
+    separate launches on one GPU, so every collective of an emulated rank is
+    issued phase by phase on ONE shared stream: first the phase that only writes
+    (count exchange, record publish, row push) for all ranks, then the phase that
+    reads.  Each rank runs in its own Python thread and the threads meet at a
+    barrier between phases, so no kernel ever waits for a kernel that has not
+    been enqueued before it.  Used by the single-GPU tests of the multi-rank
+    data paths; production runs one process per GPU.
     """
 
     def __init__(self, num_ranks: int, arena_bytes: int = 256 << 20, timeout_ms: int = 2000):
+        import threading
         self.num_ranks = num_ranks
+        self._barrier = threading.Barrier(num_ranks)
+        self._in_run = threading.local()
         self.buffers: List[Buffer] = [
             Buffer(None, arena_bytes, _local=(self, r), timeout_ms=timeout_ms) for r in range(num_ranks)]
         ptrs = [b.runtime.get_local_base_ptr() for b in self.buffers]
@@ -414,63 +459,76 @@ class LocalWorld:
     def size(self):
         return self.num_ranks
 
+    def make_streams(self):
+        """Both layer streams are the device's default stream: emulated ranks share one queue."""
+        from .stream_moe.stream_moe import StreamHolder
+        s = torch.cuda.default_stream()
+        return StreamHolder(communicate=s, compute=s)
+
+    def _barrier_wait(self):
+        if self.num_ranks == 1:
+            return
+        if not getattr(self._in_run, "active", False):
+            raise StreamEPError("collectives of an emulated rank must be called through LocalWorld.run")
+        self._barrier.wait(timeout=120)
+
+    def run(self, fn):
+        """Call ``fn(rank, buffer)`` for every rank, each in its own thread; returns the results."""
+        import threading
+        results = [None] * self.num_ranks
+        errors = [None] * self.num_ranks
+        dev = torch.cuda.current_device()
+
+        def work(r):
+            self._in_run.active = True
+            try:
+                torch.cuda.set_device(dev)
+                results[r] = fn(r, self.buffers[r])
+            except BaseException as e:  # noqa: BLE001
+                errors[r] = e
+                self._barrier.abort()
+        if self.num_ranks == 1:
+            self._in_run.active = True
+            try:
+                return [fn(0, self.buffers[0])]
+            finally:
+                self._in_run.active = False
+        threads = [threading.Thread(target=work, args=(r,)) for r in range(self.num_ranks)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        if any(e is not None for e in errors):
+            self._barrier.reset()
+            first = next(e for e in errors if e is not None and not isinstance(e, threading.BrokenBarrierError)) \
+                if any(e is not None and not isinstance(e, threading.BrokenBarrierError) for e in errors) \
+                else next(e for e in errors if e is not None)
+            raise first
+        return results
+
     def check_status(self):
+        msgs = []
         for b in self.buffers:
-            b.check_status()
+            m = b.runtime.poll_status(True)
+            if m:
+                msgs.append(f"rank {b.rank}: {m}")
+        if msgs:
+            raise StreamEPTimeout("; ".join(msgs))
 
-    def dispatch(self, xs, topk_idxs, topk_weights, num_experts, tile_m=128, seqs=None, push=True):
-        R = self.num_ranks
-        sts = []
-        for r, b in enumerate(self.buffers):
-            sts.append(b._dispatch_begin(xs[r], topk_idxs[r], topk_weights[r], num_experts, tile_m,
-                                         None if seqs is None else seqs[r]))
-        for (st, _), b in zip(sts, self.buffers):
-            b.runtime.dispatch_metadata(st, 1)
-        for (st, _), b in zip(sts, self.buffers):
-            b.runtime.dispatch_metadata(st, 2)
-            b.runtime.dispatch_allocate(st)
-        if push:
-            for (st, _), b in zip(sts, self.buffers):
-                b.runtime.dispatch_push(st, 1, 1)
-            for (st, _), b in zip(sts, self.buffers):
-                b.runtime.dispatch_push(st, 2, b._blocks(None))
-            for (st, _), b in zip(sts, self.buffers):
-                b.runtime.dispatch_push(st, 4, 8)
-        return [b._make_handle(st, None, seq, tile_m) for (st, seq), b in zip(sts, self.buffers)]
+    # convenience wrappers used by the tests ------------------------------------------------------
+    def dispatch(self, xs, topk_idxs, topk_weights, num_experts, tile_m=128, seqs=None):
+        out = self.run(lambda r, b: b.dispatch(xs[r], topk_idxs[r], topk_weights[r], None, num_experts,
+                                               tile_m=tile_m, dispatch_seq=None if seqs is None else seqs[r]))
+        return [h for _, h, _ in out]
 
-    def publish_dispatch_records(self, handles):
-        for h, b in zip(handles, self.buffers):
-            b.runtime.dispatch_push(h._dispatch_out, 1, 1)
-
-    def dispatch_grads(self, handles, dL_dys, push=True):
-        gs = [b.runtime.grads_begin(h._dispatch_out) for h, b in zip(handles, self.buffers)]
-        for h, g in zip(handles, gs):
-            h._grads_state = g
-        if push:
-            for h, g, d, b in zip(handles, gs, dL_dys, self.buffers):
-                b.runtime.grads_push(h._dispatch_out, g, d.contiguous(), 1, 1)
-            for h, g, d, b in zip(handles, gs, dL_dys, self.buffers):
-                b.runtime.grads_push(h._dispatch_out, g, d.contiguous(), 2, b._blocks(None))
-            for h, g, d, b in zip(handles, gs, dL_dys, self.buffers):
-                b.runtime.grads_push(h._dispatch_out, g, d.contiguous(), 4, 8)
-        return [(g.dl_do_pool, g.bwd_dispatch_arrival_count) for g in gs]
+    def dispatch_grads(self, handles, dL_dys):
+        out = self.run(lambda r, b: b.dispatch_grads(handles[r], dL_dys[r]))
+        return [(p, c) for p, c, _ in out]
 
     def combine(self, xs, handles, seqs=None):
-        cs = [b.runtime.combine_begin(h._dispatch_out, x, h.y_done_per_token, None, True)
-              for x, h, b in zip(xs, handles, self.buffers)]
-        for c, h, b in zip(cs, handles, self.buffers):
-            b.runtime.combine_launch(h._dispatch_out, c, True, h.dispatch_seq if seqs is None else seqs[b.rank], 1, 1)
-        for c, h, b in zip(cs, handles, self.buffers):
-            b.runtime.combine_launch(h._dispatch_out, c, True, h.dispatch_seq if seqs is None else seqs[b.rank], 2,
-                                     b._blocks(None))
-        return [c.out for c in cs]
+        out = self.run(lambda r, b: b.combine(xs[r], handles[r], combine_seq=None if seqs is None else seqs[r]))
+        return [o for o, _ in out]
 
     def combine_grads(self, dxs, handles, weight_grads, dones, seqs=None):
-        cs = [b.runtime.combine_begin(h._dispatch_out, x, d, w, False)
-              for x, h, w, d, b in zip(dxs, handles, weight_grads, dones, self.buffers)]
-        for c, h, b in zip(cs, handles, self.buffers):
-            b.runtime.combine_launch(h._dispatch_out, c, False, h.dispatch_seq if seqs is None else seqs[b.rank], 1, 1)
-        for c, h, b in zip(cs, handles, self.buffers):
-            b.runtime.combine_launch(h._dispatch_out, c, False, h.dispatch_seq if seqs is None else seqs[b.rank], 2,
-                                     b._blocks(None))
-        return [(c.out, c.out_topk_weights) for c in cs]
+        return self.run(lambda r, b: b.combine_grads(dxs[r], handles[r], weight_grads[r], dones[r],
+                                                     dispatch_seq=None if seqs is None else seqs[r]))

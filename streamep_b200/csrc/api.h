@@ -175,6 +175,8 @@ void launch_combine_pull(const CombineParams& p, int num_blocks, cudaStream_t st
 // ---------------------------------------------------------------------------------------------
 struct BarrierParams {
   int num_ranks, rank, epoch;
+  int kind;                      // flag row (kKindBarrier, or a GEMM tail kind when a rank has no tiles)
+  int wait;                      // 0: signal only
   void* peer_base[kMaxRanks];
   ControlLayout ctl;
   StatusBlock* status;
@@ -214,11 +216,15 @@ enum GemmEpilogue : int { kEpiStore = 0, kEpiSwiglu = 1, kEpiScatter = 2, kEpiDs
 struct TailSignal {              // end-of-kernel "all my remote writes are done" handshake
   int enabled;
   int kind;                      // kKindGemmYTail or kKindGemmABwdTail
-  int epoch, num_ranks, rank;
+  int epoch;
   int wait;                      // 0: signal only (emulated ranks run one after another)
-  void* peer_base[kMaxRanks];
-  ControlLayout ctl;
   int* ctas_done;                // zero on entry, reset by the kernel
+};
+
+// Where a GEMM epilogue finds a buffer that lives on every rank at a rank-specific arena offset:
+// word `field` of the record that rank published for (`kind`, `epoch`).
+struct RemoteRef {
+  int enabled, kind, epoch, field;
 };
 
 struct GemmParams {
@@ -250,13 +256,15 @@ struct GemmParams {
   // scatter targets
   void* scatter_local;           // [T_recv, N] bf16 (local variant)
   const int2* row_src;           // per-slot (src_rank, src_token) (remote variant)
-  void* peer_out[kMaxRanks];     // remote variant: base of each source rank's [T, N] accumulator
-  int scatter_remote;
-  // remote return of per-slot scalars (dswiglu, fused backward): final dl_dweight -> source [T, K]
-  float* peer_dw_out[kMaxRanks];
+  RemoteRef remote_out;          // remote variant: each source rank's [T, N] bf16 accumulator
+  // remote return of per-slot scalars (dswiglu, fused backward): final dl_dweight -> source [T, K] fp32
+  RemoteRef remote_dw;
   const int* row_k_slot;
   int num_topk;
-  int return_dweight;
+  // symmetric memory (needed by remote refs and the tail handshake)
+  int num_ranks;
+  void* peer_base[kMaxRanks];
+  ControlLayout ctl;
   // per-token completion (local scatter)
   int* tile_stripes_done;        // [tiles], zero on entry
   int* k_remaining;              // [T_recv]

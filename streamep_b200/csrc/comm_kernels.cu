@@ -497,9 +497,10 @@ __global__ void device_barrier_kernel(const BarrierParams p) {
   const int tid = threadIdx.x;
   __threadfence_system();
   if (tid < p.num_ranks) {
-    flags_signal(p.peer_base, p.ctl, kKindBarrier, p.epoch, p.rank, tid);
-    flags_wait(p.peer_base[p.rank], p.ctl, kKindBarrier, p.epoch, tid, p.wait_budget_ns, p.status,
-               kKernelBarrier, p.rank, kStatusTimeoutBarrier);
+    flags_signal(p.peer_base, p.ctl, p.kind, p.epoch, p.rank, tid);
+    if (p.wait)
+      flags_wait(p.peer_base[p.rank], p.ctl, p.kind, p.epoch, tid, p.wait_budget_ns, p.status,
+                 kKernelBarrier, p.rank, kStatusTimeoutBarrier);
   }
 }
 void launch_device_barrier(const BarrierParams& p, cudaStream_t stream) {

@@ -102,6 +102,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   int* s_flag = reinterpret_cast<int*>(tmem_slot + 1);     // epilogue broadcast word
   __shared__ PushTargets s_tg;
   __shared__ int s_push_ok;
+  __shared__ char* s_remote_out[kMaxRanks];
+  __shared__ float* s_remote_dw[kMaxRanks];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_tiles = (p.mode == kVarlenM ? p.num_m_tiles : p.num_experts * p.num_m_tiles) * p.num_n_tiles;
@@ -123,6 +125,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   if (PUSH) {
     if ((pp.flags & 1) && blockIdx.x == 0 && warp == kGemmWarps && lane < pp.num_ranks)
       publish_record(pp.own, pp.peer_base, pp.ctl, pp.kind, pp.epoch, pp.rank, lane);
+  }
+  if ((EPI == kEpiScatter || EPI == kEpiDswiglu) && warp == 2 && lane < p.num_ranks) {
+    // Resolve buffers that every rank allocated at its own arena offset from the published records.
+    if (p.remote_out.enabled) {
+      const unsigned long long* rec = fetch_record(p.peer_base[p.rank], p.ctl, p.remote_out.kind, p.remote_out.epoch,
+                                                   lane, budget, p.status, kKernelGemm, p.rank);
+      s_remote_out[lane] = rec ? static_cast<char*>(p.peer_base[lane]) + rec[p.remote_out.field] : nullptr;
+    }
+    if (p.remote_dw.enabled) {
+      const unsigned long long* rec = fetch_record(p.peer_base[p.rank], p.ctl, p.remote_dw.kind, p.remote_dw.epoch,
+                                                   lane, budget, p.status, kKernelGemm, p.rank);
+      s_remote_dw[lane] = rec ? reinterpret_cast<float*>(static_cast<char*>(p.peer_base[lane]) + rec[p.remote_dw.field]) : nullptr;
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -322,9 +337,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         } else if (EPI == kEpiScatter) {
           if (tok >= 0) {
             __nv_bfloat16* dst;
-            if (p.scatter_remote) {
+            if (p.remote_out.enabled) {
               const int2 src = p.row_src[grow];
-              dst = static_cast<__nv_bfloat16*>(p.peer_out[src.x]) + static_cast<long long>(src.y) * p.N + n;
+              dst = reinterpret_cast<__nv_bfloat16*>(s_remote_out[src.x]) + static_cast<long long>(src.y) * p.N + n;
             } else {
               dst = static_cast<__nv_bfloat16*>(p.scatter_local) + static_cast<long long>(tok) * p.N + n;
             }
@@ -385,8 +400,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (EPI == kEpiDswiglu) {
         if (tok >= 0 && p.dl_dweight != nullptr) red_add_f32(p.dl_dweight + grow, dw_acc);
       }
-      if ((EPI == kEpiScatter && !p.scatter_remote && p.tile_stripes_done != nullptr) ||
-          (EPI == kEpiDswiglu && p.return_dweight)) {
+      if ((EPI == kEpiScatter && !p.remote_out.enabled && p.tile_stripes_done != nullptr) ||
+          (EPI == kEpiDswiglu && p.remote_dw.enabled)) {
         // Per-M-tile completion: the CTA that finishes the last N stripe of a tile does the
         // per-row bookkeeping once every stripe's writes are visible.
         __threadfence();
@@ -401,7 +416,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           } else {
             const int2 src = p.row_src[grow];
             const float v = *reinterpret_cast<volatile float*>(p.dl_dweight + grow);
-            p.peer_dw_out[src.x][static_cast<long long>(src.y) * p.num_topk + p.row_k_slot[grow]] = v;
+            s_remote_dw[src.x][static_cast<long long>(src.y) * p.num_topk + p.row_k_slot[grow]] = v;
           }
         }
       }
@@ -451,11 +466,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (p.tail.enabled) {
           // Every CTA's remote reductions were fenced at system scope before it counted itself.
           __threadfence_system();
-          for (int r = 0; r < p.tail.num_ranks; ++r)
-            flags_signal(p.tail.peer_base, p.tail.ctl, p.tail.kind, p.tail.epoch, p.tail.rank, r);
+          for (int r = 0; r < p.num_ranks; ++r)
+            flags_signal(p.peer_base, p.ctl, p.tail.kind, p.tail.epoch, p.rank, r);
           if (p.tail.wait)
-            for (int r = 0; r < p.tail.num_ranks; ++r)
-              if (!flags_wait(p.tail.peer_base[p.tail.rank], p.tail.ctl, p.tail.kind, p.tail.epoch, r,
+            for (int r = 0; r < p.num_ranks; ++r)
+              if (!flags_wait(p.peer_base[p.rank], p.ctl, p.tail.kind, p.tail.epoch, r,
                               p.wait_budget_ns, p.status, kKernelGemm, p.rank, kStatusTimeoutTail))
                 break;
         }

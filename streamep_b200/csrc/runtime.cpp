@@ -152,6 +152,7 @@ struct DispatchState {
   std::vector<int> recv_per_expert;
   std::optional<EventHandle> metadata_done_event;
   BufferRecord record{};
+  std::vector<at::Tensor> aux_keepalive;
 
   void release_o() { o = at::Tensor(); }
   void release_pool() { pool = at::Tensor(); }
@@ -181,9 +182,9 @@ struct GemmArgs {
   std::optional<at::Tensor> out0, out1, preact, row_weight, row_token, dl_dweight;
   std::optional<at::Tensor> scatter_local, row_src, row_k_slot;
   std::optional<at::Tensor> tile_stripes_done, k_remaining, done_per_token;
-  std::vector<int64_t> peer_out_offsets;            // remote scatter: arena offset of every rank's accumulator
-  std::vector<int64_t> peer_dw_offsets;             // remote dL/dweight return: arena offset of every rank's [T, K]
-  bool scatter_remote = false, return_dweight = false;
+  // remote scatter / remote dL/dweight return: (record kind, epoch, word) naming the buffer on every rank
+  std::vector<int> remote_out;
+  std::vector<int> remote_dw;
   int num_topk = 0;
   int64_t seq = 0;
   int num_m_tiles = -1;                             // VarlenM: total tiles (defaults to len(tile_id_to_expert))
@@ -284,6 +285,7 @@ class Runtime {
   int rank() const { return rank_; }
   int num_ranks() const { return num_ranks_; }
   int num_channels() const { return num_channels_; }
+  int64_t launch_count() const { return launches_; }
   int64_t arena_bytes_in_use() const { return static_cast<int64_t>(arena_->bytes_in_use()); }
   int64_t arena_high_water() const { return static_cast<int64_t>(arena_->high_water()); }
   int64_t arena_capacity() const { return static_cast<int64_t>(arena_->capacity()); }
@@ -407,7 +409,7 @@ class Runtime {
     p.recv_channel_prefix_matrix = st->recv_channel_prefix_matrix.data_ptr<int>();
     p.blocks_done = counters_ + 0;
     p.host = host_dev_; p.status = status_; p.wait_budget_ns = budget_ns_;
-    launch_dispatch_metadata(p, at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_dispatch_metadata(p, at::cuda::getCurrentCUDAStream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
 
@@ -485,7 +487,7 @@ class Runtime {
     f.k_local_remaining = st->k_local_remaining.data_ptr<int>();
     f.y_done_per_token = reinterpret_cast<long long*>(st->y_done_per_token.data_ptr<int64_t>());
     f.recv_src = reinterpret_cast<int2*>(st->recv_src.data_ptr<int>());
-    launch_fill_tile_metadata(f, at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_fill_tile_metadata(f, at::cuda::getCurrentCUDAStream());
     SEP_CUDA_CHECK(cudaGetLastError());
 
     BufferRecord& r = st->record;
@@ -494,6 +496,18 @@ class Runtime {
     r.k_local_remaining = sub_off[6]; r.arrival_count = sub_off[7]; r.recv_src = sub_off[8];
     st->push_epoch = ++epochs_[kKindDispatch];
     st->metadata_done_event = EventHandle(at::cuda::getCurrentCUDAStream());
+  }
+
+  // Extra words of the dispatch record: arena tensors of this rank that peers address by (rank, row),
+  // e.g. the [T, H] output accumulator the fused combine reduces into.
+  void dispatch_set_aux(const std::shared_ptr<DispatchState>& st, int i, const at::Tensor& t) {
+    SEP_ASSERT(i >= 0 && i < 5, "aux index out of range");
+    (&st->record.aux0)[i] = t.numel() ? symmetric_offset(t) : 0;
+    st->aux_keepalive.push_back(t);
+  }
+  void grads_set_aux(const std::shared_ptr<GradsState>& g, int i, const at::Tensor& t) {
+    SEP_ASSERT(i >= 0 && i < 5, "aux index out of range");
+    (&g->record.aux0)[i] = t.numel() ? symmetric_offset(t) : 0;
   }
 
   PushParams make_push_params(const DispatchState& st, const at::Tensor& rows, bool is_grads, const BufferRecord& rec,
@@ -522,7 +536,7 @@ class Runtime {
     PushParams p = make_push_params(*st, st->x, false, st->record, kKindDispatch, st->push_epoch, flags,
                                     st->pool_arrival_count.data_ptr<int>(), 2);
     if (flags & 2) ++gate_issued_[0];
-    launch_dispatch_push(p, num_blocks, at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_dispatch_push(p, num_blocks, at::cuda::getCurrentCUDAStream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
 
@@ -547,7 +561,7 @@ class Runtime {
     PushParams p = make_push_params(*st, dl_dy, true, g->record, kKindDispatchGrads, g->epoch, flags,
                                     g->bwd_dispatch_arrival_count.data_ptr<int>(), 4);
     if (flags & 2) ++gate_issued_[1];
-    launch_dispatch_push(p, num_blocks, at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_dispatch_push(p, num_blocks, at::cuda::getCurrentCUDAStream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
 
@@ -595,16 +609,16 @@ class Runtime {
     fill_peers(p.peer_base); p.ctl = ctl_; p.own = c->record;
     p.blocks_done = counters_ + (is_fwd ? 6 : 7);
     p.status = status_; p.wait_budget_ns = budget_ns_;
-    launch_combine_pull(p, num_blocks, at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_combine_pull(p, num_blocks, at::cuda::getCurrentCUDAStream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
 
   // ---- barrier ------------------------------------------------------------------------------------
   void barrier() {
     BarrierParams p{};
-    p.num_ranks = num_ranks_; p.rank = rank_; p.epoch = ++epochs_[kKindBarrier];
+    p.num_ranks = num_ranks_; p.rank = rank_; p.epoch = ++epochs_[kKindBarrier]; p.kind = kKindBarrier; p.wait = 1;
     fill_peers(p.peer_base); p.ctl = ctl_; p.status = status_; p.wait_budget_ns = budget_ns_;
-    launch_device_barrier(p, at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_device_barrier(p, at::cuda::getCurrentCUDAStream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
   // Emulated ranks run one after another on one device: a barrier there is "every rank bumped its
@@ -634,7 +648,7 @@ class Runtime {
       SEP_ASSERT(static_cast<int64_t>(p.num_m_tiles) * BM_ <= rows, "tile list longer than A");
       p.num_n_tiles = (N + BN - 1) / BN;
       p.tile_id_to_expert = a.tile_id_to_expert->data_ptr<int>();
-      if (rows == 0 || p.num_m_tiles == 0) return;
+      if (rows == 0) { launch_without_tiles(a); return; }
       ta = make_tmap(a.a.data_ptr(), K, rows, 1, K, rows * K, 64, BM_);
       if (a.b_mn_major) tb = make_tmap(a.b.data_ptr(), N, K, E, N, K * N, 64, 64);
       else tb = make_tmap(a.b.data_ptr(), K, N, E, K, N * K, 64, BN);
@@ -673,29 +687,29 @@ class Runtime {
     if (a.k_remaining.has_value()) p.k_remaining = a.k_remaining->data_ptr<int>();
     if (a.done_per_token.has_value()) p.done_per_token = reinterpret_cast<long long*>(a.done_per_token->data_ptr<int64_t>());
     p.seq = a.seq; p.num_topk = a.num_topk;
-    p.scatter_remote = a.scatter_remote ? 1 : 0; p.return_dweight = a.return_dweight ? 1 : 0;
+    p.num_ranks = num_ranks_; fill_peers(p.peer_base); p.ctl = ctl_;
+    auto set_ref = [](RemoteRef& r, const std::vector<int>& v) {
+      if (v.empty()) return;
+      SEP_ASSERT(v.size() == 3 && v[2] >= 0 && v[2] < kMailboxWords - 1, "remote reference must be (kind, epoch, word)");
+      r.enabled = 1; r.kind = v[0]; r.epoch = v[1]; r.field = v[2];
+    };
+    set_ref(p.remote_out, a.remote_out);
+    set_ref(p.remote_dw, a.remote_dw);
     if (a.epilogue == kEpiScatter || a.epilogue == kEpiDswiglu) SEP_ASSERT(p.row_token != nullptr, "this epilogue needs pool_recv_token");
     if (a.epilogue == kEpiScatter) {
-      if (a.scatter_remote) {
-        SEP_ASSERT(static_cast<int>(a.peer_out_offsets.size()) == num_ranks_ && p.row_src != nullptr, "remote scatter needs one accumulator offset per rank and pool_src");
-        for (int r = 0; r < num_ranks_; ++r) p.peer_out[r] = static_cast<char*>(peer_base_[r]) + a.peer_out_offsets[r];
-      } else {
-        SEP_ASSERT(p.scatter_local != nullptr, "local scatter needs a destination");
-      }
+      if (p.remote_out.enabled) SEP_ASSERT(p.row_src != nullptr, "remote scatter needs pool_src");
+      else SEP_ASSERT(p.scatter_local != nullptr, "local scatter needs a destination");
     }
     if (a.epilogue == kEpiDswiglu) {
       SEP_ASSERT(p.preact != nullptr && p.out0 != nullptr && p.out1 != nullptr, "dswiglu epilogue needs preact and both outputs");
-      if (a.return_dweight) {
-        SEP_ASSERT(static_cast<int>(a.peer_dw_offsets.size()) == num_ranks_ && p.row_src != nullptr && p.row_k_slot != nullptr &&
-                   p.tile_stripes_done != nullptr && p.dl_dweight != nullptr, "dL/dweight return needs offsets, pool_src, pool_k_slot, stripe counters and dl_dweight");
-        for (int r = 0; r < num_ranks_; ++r) p.peer_dw_out[r] = reinterpret_cast<float*>(static_cast<char*>(peer_base_[r]) + a.peer_dw_offsets[r]);
-      }
+      if (p.remote_dw.enabled)
+        SEP_ASSERT(p.row_src != nullptr && p.row_k_slot != nullptr && p.tile_stripes_done != nullptr && p.dl_dweight != nullptr,
+                   "dL/dweight return needs pool_src, pool_k_slot, stripe counters and dl_dweight");
     }
     if (a.epilogue == kEpiSwiglu || a.epilogue == kEpiStore) SEP_ASSERT(p.out0 != nullptr, "this epilogue needs out0");
     if (a.tail) {
       p.tail.enabled = 1; p.tail.kind = a.tail_kind; p.tail.epoch = ++epochs_[a.tail_kind];
-      p.tail.num_ranks = num_ranks_; p.tail.rank = rank_; p.tail.wait = a.tail_wait ? 1 : 0;
-      fill_peers(p.tail.peer_base); p.tail.ctl = ctl_;
+      p.tail.wait = a.tail_wait ? 1 : 0;
       p.tail.ctas_done = counters_ + (a.tail_kind == kKindGemmYTail ? 8 : 9);
     }
     int n_ctas = a.num_ctas > 0 ? a.num_ctas : num_sms();
@@ -715,27 +729,51 @@ class Runtime {
       ppp = &pp;
     }
     if (ppp == nullptr) n_ctas = static_cast<int>(std::min<int64_t>(n_ctas, std::max<int64_t>(total, 1)));
-    launch_grouped_gemm(p, &ta, &tb, ppp, n_ctas, at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_grouped_gemm(p, &ta, &tb, ppp, n_ctas, at::cuda::getCurrentCUDAStream());
+    SEP_CUDA_CHECK(cudaGetLastError());
+  }
+
+  // A rank that received no rows has nothing to multiply, but it still takes part in the collective
+  // halves of the fused kernels: its own rows must be pushed and its completion flags raised.
+  void launch_without_tiles(const GemmArgs& a) {
+    auto stream = at::cuda::getCurrentCUDAStream();
+    if (a.fused_push) {
+      PushParams pp = make_push_params(*a.fused_push, a.fused_push->x, false, a.fused_push->record, kKindDispatch,
+                                       a.fused_push->push_epoch, a.push_flags & 3, a.fused_push->pool_arrival_count.data_ptr<int>(), 2);
+      pp.started_flag = nullptr;
+      ++launches_; launch_dispatch_push(pp, num_sms(), stream);
+    } else if (a.fused_push_grads) {
+      PushParams pp = make_push_params(*a.fused_push_routing, a.fused_push_rows, true, a.fused_push_grads->record, kKindDispatchGrads,
+                                       a.fused_push_grads->epoch, a.push_flags & 3, a.fused_push_grads->bwd_dispatch_arrival_count.data_ptr<int>(), 4);
+      pp.started_flag = nullptr;
+      ++launches_; launch_dispatch_push(pp, num_sms(), stream);
+    }
+    if (a.tail) {
+      BarrierParams b{};
+      b.num_ranks = num_ranks_; b.rank = rank_; b.kind = a.tail_kind; b.epoch = ++epochs_[a.tail_kind]; b.wait = a.tail_wait ? 1 : 0;
+      fill_peers(b.peer_base); b.ctl = ctl_; b.status = status_; b.wait_budget_ns = budget_ns_;
+      ++launches_; launch_device_barrier(b, stream);
+    }
     SEP_CUDA_CHECK(cudaGetLastError());
   }
 
   // ---- small ops ---------------------------------------------------------------------------------------
   void tile_producer(const at::Tensor& count, const at::Tensor& target, double delay_us) {
-    launch_tile_producer(count.data_ptr<int>(), target.data_ptr<int>(), count.numel(), static_cast<long long>(delay_us * 1000.0),
+    ++launches_; launch_tile_producer(count.data_ptr<int>(), target.data_ptr<int>(), count.numel(), static_cast<long long>(delay_us * 1000.0),
                          at::cuda::getCurrentCUDAStream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
   at::Tensor pool_compress(const at::Tensor& pool, const at::Tensor& pool_recv_token, int64_t num_recv) {
     SEP_ASSERT(pool.is_contiguous() && pool.scalar_type() == at::kBFloat16 && pool.size(1) % 8 == 0, "pool must be contiguous bf16 with hidden % 8 == 0");
     auto out = at::empty({num_recv, pool.size(1)}, pool.options());
-    launch_pool_compress(pool.data_ptr(), out.data_ptr(), pool_recv_token.data_ptr<int>(), pool.size(0), pool.size(1), at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_pool_compress(pool.data_ptr(), out.data_ptr(), pool_recv_token.data_ptr<int>(), pool.size(0), pool.size(1), at::cuda::getCurrentCUDAStream());
     SEP_CUDA_CHECK(cudaGetLastError());
     return out;
   }
   at::Tensor pool_expand(const at::Tensor& recv, const at::Tensor& pool_recv_token, int64_t tk_padded) {
     SEP_ASSERT(recv.is_contiguous() && recv.scalar_type() == at::kBFloat16 && recv.size(1) % 8 == 0, "recv must be contiguous bf16 with hidden % 8 == 0");
     auto out = at::empty({tk_padded, recv.size(1)}, recv.options());
-    launch_pool_expand(recv.data_ptr(), out.data_ptr(), pool_recv_token.data_ptr<int>(), tk_padded, recv.size(1), at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_pool_expand(recv.data_ptr(), out.data_ptr(), pool_recv_token.data_ptr<int>(), tk_padded, recv.size(1), at::cuda::getCurrentCUDAStream());
     SEP_CUDA_CHECK(cudaGetLastError());
     return out;
   }
@@ -755,7 +793,7 @@ class Runtime {
     p.topk_idx = reinterpret_cast<long long*>(idx.data_ptr<int64_t>()); p.topk_weights = w.data_ptr<float>();
     p.is_token_in_rank = reinterpret_cast<unsigned char*>(in_rank.data_ptr<bool>());
     p.probs = want_probs ? probs.data_ptr<float>() : nullptr;
-    if (p.num_tokens > 0) launch_router(p, at::cuda::getCurrentCUDAStream());
+    if (p.num_tokens > 0) ++launches_, launch_router(p, at::cuda::getCurrentCUDAStream());
     SEP_CUDA_CHECK(cudaGetLastError());
     return {idx, w, in_rank, probs};
   }
@@ -795,6 +833,7 @@ class Runtime {
   unsigned long long budget_ns_ = 0;
   int64_t timeout_ms_ = 0;
   int epochs_[kNumKinds];
+  int64_t launches_ = 0;
   int gate_issued_[8];
   bool available_ = false, destroyed_ = false;
 };
@@ -855,7 +894,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       RO(recv_channel_prefix_matrix) RO(tile_id_to_expert) RO(pool_arrival_target)
       RO(pool) RO(pool_topk_weight) RO(pool_recv_token) RO(pool_k_slot) RO(pool_src) RO(recv_token_to_slots)
       RO(k_local_total) RO(k_local_remaining) RO(pool_arrival_count) RO(recv_src) RO(y_done_per_token) RO(o)
-      RO(total_tiles) RO(num_recv_tokens) RO(recv_per_expert) RO(metadata_done_event)
+      RO(total_tiles) RO(num_recv_tokens) RO(recv_per_expert) RO(metadata_done_event) RO(push_epoch) RO(meta_epoch)
 #undef RO
       .def("release_o", &DispatchState::release_o)
       .def("release_pool", &DispatchState::release_pool);
@@ -863,7 +902,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   py::class_<GradsState, std::shared_ptr<GradsState>>(m, "GradsState")
       .def_readonly("dl_do_pool", &GradsState::dl_do_pool)
       .def_readonly("bwd_dispatch_arrival_count", &GradsState::bwd_dispatch_arrival_count)
-      .def_readonly("started_event", &GradsState::started_event);
+      .def_readonly("started_event", &GradsState::started_event)
+      .def_readonly("epoch", &GradsState::epoch);
 
   py::class_<CombineState, std::shared_ptr<CombineState>>(m, "CombineState")
       .def_readonly("out", &CombineState::out)
@@ -875,8 +915,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       RW(mode) RW(epilogue) RW(block_n) RW(num_ctas) RW(a_mn_major) RW(b_mn_major) RW(a) RW(b)
       RW(tile_id_to_expert) RW(expert_pool_block_offset) RW(expert_frequency) RW(arrival_count) RW(arrival_target)
       RW(out0) RW(out1) RW(preact) RW(row_weight) RW(row_token) RW(dl_dweight) RW(scatter_local) RW(row_src) RW(row_k_slot)
-      RW(tile_stripes_done) RW(k_remaining) RW(done_per_token) RW(peer_out_offsets) RW(peer_dw_offsets)
-      RW(scatter_remote) RW(return_dweight) RW(num_topk) RW(seq) RW(num_m_tiles) RW(started_flag)
+      RW(tile_stripes_done) RW(k_remaining) RW(done_per_token) RW(remote_out) RW(remote_dw)
+      RW(num_topk) RW(seq) RW(num_m_tiles) RW(started_flag)
       RW(tail) RW(tail_kind) RW(tail_wait) RW(fused_push) RW(fused_push_grads) RW(fused_push_routing) RW(fused_push_rows)
       RW(push_flags);
 #undef RW
@@ -896,6 +936,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_property_readonly("rank", &Runtime::rank)
       .def_property_readonly("num_ranks", &Runtime::num_ranks)
       .def_property_readonly("num_channels", &Runtime::num_channels)
+      .def("launch_count", &Runtime::launch_count)
       .def("arena_bytes_in_use", &Runtime::arena_bytes_in_use)
       .def("arena_high_water", &Runtime::arena_high_water)
       .def("arena_capacity", &Runtime::arena_capacity)
@@ -913,6 +954,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("dispatch_allocate", &Runtime::dispatch_allocate)
       .def("dispatch_push", &Runtime::dispatch_push)
       .def("grads_begin", &Runtime::grads_begin)
+      .def("dispatch_set_aux", &Runtime::dispatch_set_aux)
+      .def("grads_set_aux", &Runtime::grads_set_aux)
       .def("grads_push", &Runtime::grads_push)
       .def("combine_begin", &Runtime::combine_begin)
       .def("combine_launch", &Runtime::combine_launch)

@@ -128,8 +128,7 @@ def _scatter_common(a, *, o, pool_recv_token, tile_stripes_done, k_local_remaini
                     remote_offsets, pool_src, tail_kind, tail_wait):
     a.row_token = pool_recv_token
     if remote_offsets is not None:
-        a.scatter_remote = True
-        a.peer_out_offsets = list(remote_offsets)
+        a.remote_out = [int(v) for v in remote_offsets]
         a.row_src = pool_src
         a.tail, a.tail_kind, a.tail_wait = True, tail_kind, tail_wait
     else:
@@ -154,9 +153,10 @@ def streaming_moe_y(postact_a: torch.Tensor, w2: torch.Tensor, tile_id_to_expert
 
     * ``o[pool_recv_token[slot]]`` on this rank (then per-token completion stamps
       ``y_done_per_token[r] = combine_seq`` once all of r's local slots are in), or
-    * the SOURCE rank's output row over NVLink when ``remote_out_offsets`` gives
-      the arena offset of every rank's ``[T, H]`` accumulator (fused combine); the
-      kernel then ends with a cross-rank completion handshake.
+    * the SOURCE rank's output row over NVLink when ``remote_out_offsets`` names
+      ``(record kind, epoch, word)`` of the record in which every rank published the
+      arena offset of its ``[T, H]`` accumulator (fused combine); the kernel then
+      ends with a cross-rank completion handshake.
     """
     a = _args()
     N = w2.shape[1]
@@ -215,7 +215,7 @@ def streaming_moe_y_bwd(dL_do_pool: torch.Tensor, w2: torch.Tensor, preact_a: to
                         pool_src: Optional[torch.Tensor] = None, pool_k_slot: Optional[torch.Tensor] = None,
                         num_topk: int = 0, tile_n_stripes_done: Optional[torch.Tensor] = None,
                         fused_dispatch_grads=None, fused_routing=None, fused_rows: Optional[torch.Tensor] = None,
-                        push_flags: int = 3,
+                        push_flags: int = 3, num_tiles: Optional[int] = None,
                         tile_n: Optional[int] = None, num_sms: Optional[int] = None, buffer=None):
     """``g = dL_do_pool[TKp, H] @ w2[e]`` (NN GEMM, K = H) followed by the SwiGLU
     backward on the saved ``preact_a``:
@@ -225,8 +225,9 @@ def streaming_moe_y_bwd(dL_do_pool: torch.Tensor, w2: torch.Tensor, preact_a: to
     * ``postact_a_for_dW2[slot, i] = w * postact[slot, i]``,
     * padding rows (``pool_recv_token < 0``) come out exactly zero.
 
-    ``dL_dweight`` must be zero on entry.  With ``remote_dw_offsets`` the final
-    per-slot value is also stored into the source rank's ``[T, K]`` matrix.
+    ``dL_dweight`` must be zero on entry.  With ``remote_dw_offsets`` (a ``(record
+    kind, epoch, word)`` triple, see :func:`streaming_moe_y`) the final per-slot
+    value is also stored into the source rank's ``[T, K]`` matrix.
     """
     rows, H = dL_do_pool.shape
     E, H2, I = w2.shape
@@ -243,11 +244,12 @@ def streaming_moe_y_bwd(dL_do_pool: torch.Tensor, w2: torch.Tensor, preact_a: to
     a.a, a.b, a.tile_id_to_expert = dL_do_pool, w2, tile_id_to_expert
     a.preact, a.out0, a.out1 = preact_a, dL_dswiglu_in, postact_a_for_dW2
     a.row_weight, a.row_token, a.dl_dweight = pool_topk_weight, pool_recv_token, dL_dweight
+    if num_tiles is not None:
+        a.num_m_tiles = num_tiles
     if arrival_count is not None:
         a.arrival_count, a.arrival_target = arrival_count, arrival_target
     if remote_dw_offsets is not None:
-        a.return_dweight = True
-        a.peer_dw_offsets = list(remote_dw_offsets)
+        a.remote_dw = [int(v) for v in remote_dw_offsets]
         a.row_src, a.row_k_slot, a.num_topk = pool_src, pool_k_slot, num_topk
         a.tile_stripes_done = tile_n_stripes_done
     if fused_dispatch_grads is not None:
