@@ -20,6 +20,7 @@
 #include <cuda.h>
 
 #include "comm_common.cuh"
+#include "no_alloc.h"
 
 namespace sep {
 
@@ -540,3 +541,111 @@ void launch_grouped_gemm(const GemmParams& p, const void* tmap_a, const void* tm
 }
 
 }  // namespace sep
+
+// =============================================================================================
+// Allocation-free entry point (declared and documented in no_alloc.h).
+// =============================================================================================
+namespace {
+
+// Scratch of the no-alloc entry point: per-M-tile "N stripes finished" counters.  In host code this
+// name is only a handle for cudaGetSymbolAddress; the device address is resolved once per device.
+static __device__ __align__(256) int g_noalloc_stripes_done[kNoAllocMaxTiles];
+
+constexpr int kNoAllocMaxDevices = 64;
+int* g_noalloc_scratch_ptr[kNoAllocMaxDevices] = {};
+thread_local char g_noalloc_error[256] = "";
+
+int noalloc_fail(int code, const char* what, cudaError_t e = cudaSuccess) {
+  if (e != cudaSuccess) snprintf(g_noalloc_error, sizeof(g_noalloc_error), "%s: %s", what, cudaGetErrorString(e));
+  else snprintf(g_noalloc_error, sizeof(g_noalloc_error), "%s", what);
+  return code;
+}
+
+using NoAllocEncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+bool noalloc_tmap(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t b0, uint32_t b1) {
+  static NoAllocEncodeFn encode = nullptr;
+  if (encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || fn == nullptr)
+      return false;
+    encode = reinterpret_cast<NoAllocEncodeFn>(fn);
+  }
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+extern "C" const char* streamep_noalloc_last_error(void) { return g_noalloc_error; }
+
+extern "C" int streamep_gemm_y_scatter_noalloc(const void* postact, const void* w2, const int* tile_id_to_expert,
+                                               const float* pool_topk_weight, const int* pool_recv_token, void* o,
+                                               int* k_local_remaining, long long* y_done_per_token, int total_tiles,
+                                               int hidden, int ffn, int num_local_experts, long long seq, void* stream_v) {
+  using namespace sep;
+  g_noalloc_error[0] = 0;
+  if (total_tiles < 0 || total_tiles > kNoAllocMaxTiles)
+    return noalloc_fail(-1, "total_tiles exceeds kNoAllocMaxTiles (32768): split the call or use the regular entry point");
+  if (total_tiles == 0) return 0;
+  if (!postact || !w2 || !tile_id_to_expert || !pool_topk_weight || !pool_recv_token || !o || !k_local_remaining || !y_done_per_token)
+    return noalloc_fail(-2, "null pointer argument");
+  if (hidden <= 0 || ffn <= 0 || hidden % 8 != 0 || ffn % 8 != 0 || num_local_experts <= 0)
+    return noalloc_fail(-2, "hidden and ffn must be positive multiples of 8, num_local_experts positive");
+  if (reinterpret_cast<uintptr_t>(postact) % 16 != 0 || reinterpret_cast<uintptr_t>(w2) % 16 != 0 || reinterpret_cast<uintptr_t>(o) % 16 != 0)
+    return noalloc_fail(-2, "postact, w2 and o must be 16-byte aligned");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return noalloc_fail(-3, "cudaGetDevice", e);
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return noalloc_fail(-2, "device ordinal out of range");
+  if (g_noalloc_scratch_ptr[dev] == nullptr) {
+    // One-time set-up for this device (with it current): the device address behind the symbol.
+    int* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_stripes_done);
+    if (e != cudaSuccess || ptr == nullptr) return noalloc_fail(-3, "cudaGetSymbolAddress(scratch)", e);
+    g_noalloc_scratch_ptr[dev] = ptr;
+  }
+  int* scratch = g_noalloc_scratch_ptr[dev];
+  // The array keeps the previous call's counts: clear the part this call uses.
+  e = cudaMemsetAsync(scratch, 0, sizeof(int) * static_cast<size_t>(total_tiles), stream);
+  if (e != cudaSuccess) return noalloc_fail(-3, "cudaMemsetAsync(scratch)", e);
+
+  const int block_n = (hidden % 256 == 0) ? 256 : ((hidden % 128 == 0) ? 128 : (hidden > 128 ? 256 : 128));
+  const long long rows = static_cast<long long>(total_tiles) * BM;
+  CUtensorMap ta, tb;
+  if (!noalloc_tmap(&ta, postact, ffn, rows, 1, 64, BM) || !noalloc_tmap(&tb, w2, ffn, hidden, num_local_experts, 64, block_n))
+    return noalloc_fail(-3, "cuTensorMapEncodeTiled failed");
+
+  GemmParams p{};
+  p.mode = kVarlenM; p.epilogue = kEpiScatter; p.block_n = block_n;
+  p.N = hidden; p.K = ffn; p.num_experts = num_local_experts; p.total_rows = static_cast<int>(rows);
+  p.num_m_tiles = total_tiles; p.num_n_tiles = (hidden + block_n - 1) / block_n;
+  p.tile_id_to_expert = tile_id_to_expert;
+  p.row_weight = pool_topk_weight; p.row_token = pool_recv_token;
+  p.scatter_local = o;
+  p.tile_stripes_done = scratch; p.k_remaining = k_local_remaining; p.done_per_token = y_done_per_token; p.seq = seq;
+  p.num_ranks = 1; p.rank = 0;
+  p.status = nullptr;                       // waits stay bounded by the budget below
+  p.wait_budget_ns = 2000000000ull;
+  int sms = 0;
+  e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return noalloc_fail(-3, "cudaDeviceGetAttribute", e);
+  const long long total = static_cast<long long>(p.num_m_tiles) * p.num_n_tiles;
+  const int ctas = static_cast<int>(total < sms ? total : sms);
+  PushParams none{};
+  if (block_n == 256) launch_instance<256, false, false, kEpiScatter, false>(p, ta, tb, none, ctas, stream);
+  else launch_instance<128, false, false, kEpiScatter, false>(p, ta, tb, none, ctas, stream);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return noalloc_fail(-3, "kernel launch", e);
+  return 0;
+}
