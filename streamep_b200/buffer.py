@@ -187,6 +187,27 @@ class Buffer:
     def set_timeout_ms(self, ms: int) -> None:
         self.runtime.set_timeout_ms(int(ms))
 
+    def recover(self) -> None:
+        """Collective host-side recovery after a failed collective (a rank that did not
+        join, a wait that ran out).  Every rank of the group must call it: the device is
+        drained, the status block cleared, and the per-kind epoch counters - which went
+        out of step when only some ranks launched the failed operation - are re-agreed
+        as the maximum over the group.  Tensors of the failed operation must not be used."""
+        import torch.distributed as dist
+
+        torch.cuda.synchronize()
+        self.runtime.poll_status(True)
+        mine = self.runtime.get_epochs()
+        if self._local is not None:
+            every = [b.runtime.get_epochs() for b in self._local[0].buffers]
+        else:
+            every = [None] * self.group_size
+            dist.all_gather_object(every, mine, self.group)
+        agreed = [max(col) + 2 for col in zip(*every)]
+        self.runtime.set_epochs(agreed)
+        if self._local is None and self.group_size > 1:
+            dist.barrier(self.group)
+
     # ------------------------------------------------------------------ symmetric memory
     def alloc_symmetric(self, shape: Sequence[int], dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
         """A tensor in the peer-mapped arena.  Gates and rows that peers read while they
@@ -342,14 +363,14 @@ class Buffer:
         cfg = self.get_dispatch_config(self.group_size) if config is None else config
         if not self._emulated:
             self.runtime.dispatch_metadata(st, 3)
-            self.runtime.dispatch_allocate(st)
+            self._allocate(st)
             if launch_push:
                 self.runtime.dispatch_push(st, 7, self._blocks(cfg))
         else:
             self.runtime.dispatch_metadata(st, 1)
             self._phase()
             self.runtime.dispatch_metadata(st, 2)
-            self.runtime.dispatch_allocate(st)
+            self._allocate(st)
             if launch_push:
                 self.runtime.dispatch_push(st, 1, 1)
                 self._phase()
@@ -358,6 +379,15 @@ class Buffer:
                 self.runtime.dispatch_push(st, 4, 8)
         handle = self._make_handle(st, is_token_in_rank, seq, tile_m)
         return st.pool, handle, st.metadata_done_event
+
+    def _allocate(self, st) -> None:
+        """Host poll for the receive sizes + allocation of everything peers write into."""
+        try:
+            self.runtime.dispatch_allocate(st)
+        except RuntimeError as e:
+            if "timed out" in str(e) or "metadata failed" in str(e):
+                raise StreamEPTimeout(str(e)) from None
+            raise
 
     # ------------------------------------------------------------------ dispatch_grads
     def dispatch_grads(self, handle: StreamingHandle, dL_dy: torch.Tensor, *,

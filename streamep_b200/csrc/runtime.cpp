@@ -624,6 +624,11 @@ class Runtime {
   // Emulated ranks run one after another on one device: a barrier there is "every rank bumped its
   // epoch and stored its flags", with nobody waiting.
   int next_epoch(int kind) { return ++epochs_[kind]; }
+  std::vector<int> get_epochs() const { return std::vector<int>(epochs_, epochs_ + kNumKinds); }
+  void set_epochs(const std::vector<int>& e) {
+    SEP_ASSERT(static_cast<int>(e.size()) == kNumKinds, "one epoch per operation kind expected");
+    for (int k = 0; k < kNumKinds; ++k) epochs_[k] = e[k];
+  }
 
   // ---- grouped GEMM ---------------------------------------------------------------------------------
   void grouped_gemm(const GemmArgs& a) {
@@ -961,6 +966,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("combine_launch", &Runtime::combine_launch)
       .def("barrier", &Runtime::barrier)
       .def("next_epoch", &Runtime::next_epoch)
+      .def("get_epochs", &Runtime::get_epochs)
+      .def("set_epochs", &Runtime::set_epochs)
       .def("grouped_gemm", &Runtime::grouped_gemm)
       .def("tile_producer", &Runtime::tile_producer)
       .def("pool_compress", &Runtime::pool_compress)
