@@ -27,9 +27,9 @@ namespace sep {
 constexpr int BM = 128;          // rows per tile == pool tile_m
 constexpr int BK = 64;           // bf16 elements per k-block: one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kGemmWarps = 6;    // 0: TMA producer, 1: MMA issuer + TMEM owner, 2..5: epilogue
-constexpr int kPushWarps = 8;    // extra warps of the fused variant
-constexpr int kEpiThreads = 128;
+constexpr int kGemmWarps = 10;   // 0: TMA producer, 1: MMA issuer + TMEM owner, 2..9: epilogue
+constexpr int kPushWarps = 6;    // extra warps of the fused variant
+constexpr int kEpiThreads = 256; // two threads per accumulator row: each takes half of the tile's columns
 
 template <int BN> struct GemmCfg {
   static constexpr int kABytes = BM * BK * 2;                 // 16 KB
@@ -83,7 +83,7 @@ __device__ __forceinline__ int atom_add_acq_rel_gpu(int* p, int v) {
   asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
   return old;
 }
-__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 template <int BN, bool A_MN, bool B_MN, int EPI, bool PUSH>
 __global__ void __launch_bounds__((kGemmWarps + (PUSH ? kPushWarps : 0)) * 32, 1)
@@ -248,10 +248,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     if (!ok) report_failure(p.status, kStatusTimeoutPipeline, kKernelGemm, 1, p.rank, 0, 0, 0);
   } else if (warp < kGemmWarps) {
-    // ------------------------------------------------------------------ epilogue (4 warps, one row per thread)
+    // ------------------------------------------------------------------ epilogue (8 warps: a warp reads the 32 TMEM
+    // lanes of its quarter; warps 2..5 take the left half of the tile's columns, warps 6..9 the right half)
     const int quarter = warp & 3;                 // TMEM lanes this warp may read
     const int row = quarter * 32 + lane;
     const int epi_tid = (warp - 2) * 32 + lane;
+    const int half = (warp - 2) >> 2;
+    constexpr int kChunksPerHalf = BN / 64;
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
     for (int lin = blockIdx.x; lin < total_tiles; lin += gridDim.x) {
       const TileCoord t = decode_tile(p, lin);
@@ -282,10 +285,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (p.row_weight != nullptr && tok >= 0) w = p.row_weight[grow];
       }
       float dw_acc = 0.f;
+      int2 src = make_int2(0, 0);
+      if ((EPI == kEpiScatter && p.remote_out.enabled) || (EPI == kEpiDswiglu && p.remote_dw.enabled)) {
+        if (tok >= 0) src = p.row_src[grow];
+      }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * kChunksPerHalf; c < (half + 1) * kChunksPerHalf; ++c) {
         const int n = n0 + c * 32;
         if (n >= p.N) break;
+        uint4 pq[8];
+        if (EPI == kEpiDswiglu) {
+          // issue the whole row segment of preact before touching the accumulator: 8 loads in flight
+          if (tok >= 0) {
+            const char* pre = reinterpret_cast<const char*>(static_cast<const __nv_bfloat16*>(p.preact) + grow * p.ld_preact + 2 * n);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (n + j * 4 < p.N) pq[j] = ld_nc_v4(pre + j * 16);
+          }
+        }
         uint32_t r[32];
         if (!empty) {
           tmem_ld_32x32(taddr + c * 32, r);
@@ -339,7 +356,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (tok >= 0) {
             __nv_bfloat16* dst;
             if (p.remote_out.enabled) {
-              const int2 src = p.row_src[grow];
               dst = reinterpret_cast<__nv_bfloat16*>(s_remote_out[src.x]) + static_cast<long long>(src.y) * p.N + n;
             } else {
               dst = static_cast<__nv_bfloat16*>(p.scatter_local) + static_cast<long long>(tok) * p.N + n;
@@ -358,11 +374,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           __nv_bfloat16* din = static_cast<__nv_bfloat16*>(p.out0) + grow * p.ld0 + 2 * n;
           __nv_bfloat16* pw = static_cast<__nv_bfloat16*>(p.out1) + grow * p.ld1 + n;
           if (tok >= 0) {
-            const uint4* pre = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.preact) + grow * p.ld_preact + 2 * n);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {       // 8 output columns per step
               if (n + q * 8 >= p.N) break;
-              const uint4 p0 = pre[q * 2], p1 = pre[q * 2 + 1];
+              const uint4 p0 = pq[q * 2], p1 = pq[q * 2 + 1];
               const uint32_t pv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
               uint32_t o_in[8]; float post[8];
 #pragma unroll
@@ -411,11 +426,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         epi_bar_sync();
         const bool last = (*s_flag != 0);
         epi_bar_sync();
-        if (last && tok >= 0) {
+        if (last && tok >= 0 && half == 0) {
           if (EPI == kEpiScatter) {
             if (atom_add_acq_rel_gpu(p.k_remaining + tok, -1) == 1) st_release_gpu(p.done_per_token + tok, p.seq);
           } else {
-            const int2 src = p.row_src[grow];
             const float v = *reinterpret_cast<volatile float*>(p.dl_dweight + grow);
             s_remote_dw[src.x][static_cast<long long>(src.y) * p.num_topk + p.row_k_slot[grow]] = v;
           }

@@ -47,17 +47,17 @@ def _rt(buffer):
 
 
 def pick_block_n(n: int, requested: Optional[int] = None) -> int:
-    """Tile width of the output: 256 (one full-width UMMA) when it divides N,
-    else 128 when that divides N, else 256 with a masked last tile."""
+    """Tile width of the output.  256 (one full-width UMMA per k-step) unless the masked part of
+    the last tile would waste more than 15 % of the work, in which case 128 is used."""
     if requested is not None:
         if requested not in (128, 256):
             raise ValueError(f"tile_n must be 128 or 256 on sm_100a (got {requested})")
         return requested
-    if n % 256 == 0:
-        return 256
-    if n % 128 == 0:
+    if n <= 128:
         return 128
-    return 256 if n > 128 else 128
+    waste256 = (-(-n // 256) * 256) / n
+    waste128 = (-(-n // 128) * 128) / n
+    return 256 if waste256 <= 1.15 * waste128 else 128
 
 
 def _args():
