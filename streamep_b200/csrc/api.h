@@ -66,7 +66,7 @@ struct MetadataParams {
   const long long* topk_idx;     // [T, K] int64, -1 = skip
   int num_tokens, num_topk, num_experts, num_ranks, rank, num_channels, tile_m;
   int epoch;                     // monotonic per-buffer collective counter
-  int phase_mask;                // bit0: count + exchange + signal; bit1: wait + synthesize
+  int phase_mask;                // bit0: count + exchange + signal; bit1: wait + synthesize; bit2: materialise (own launch)
   // symmetric memory
   void* peer_base[kMaxRanks];    // arena bases (own entry included)
   ControlLayout ctl;
@@ -80,6 +80,9 @@ struct MetadataParams {
   int* channel_prefix_matrix;    // [R, C]
   int* send_base;                // [C, E] scratch: base slot at the owner for (channel, expert), src = this rank
   int* send_token_base;          // [C, R] scratch: first recv-token id at dst for (channel, dst)
+  int* send_order_base;          // [C, E] scratch: first position in `send_list` of this rank's (channel, expert) pairs
+  int* send_list;                // [T * K] pair ids (t * K + k) in push order: (local expert, rotated dst rank, channel, t, k)
+  int* num_send;                 // [1] number of valid pairs == used length of send_list
   int* peer_total_tiles;         // [R]
   int* peer_num_recv;            // [R]
   // receiver-side outputs (local)
@@ -124,12 +127,14 @@ struct PushParams {
   const float* topk_weights;     // [T, K] (forward only)
   const int* pair_slot;          // [T, K]
   const int* send_recv_token;    // [T, R]
+  const int* send_list;          // [num_send] pair ids in push order
+  const int* num_send;           // [1]
   int num_tokens, hidden, num_topk, num_experts, num_ranks, rank, tile_m;
   int is_grads;                  // 1: rows only (no per-slot / per-token scalars)
   int kind;                      // kKindDispatch or kKindDispatchGrads
   int epoch;
   int flags;                     // bit0 publish own record, bit1 push, bit2 tail wait for own tiles
-  int tokens_per_chunk;
+  int pairs_per_chunk;           // pairs one warp ships between two counter releases (<= 32)
   void* peer_base[kMaxRanks];
   ControlLayout ctl;
   BufferRecord own;              // offsets of this rank's freshly allocated buffers (grads: only `pool`

@@ -67,10 +67,13 @@ __device__ __forceinline__ bool flags_wait(void* own_base, const ControlLayout& 
 }
 
 // ---------------------------------------------------------------------------------------------
-// Row push.  One warp ships `tokens_per_chunk` consecutive tokens: each token row is read once and
-// written into the pool slot of every (token, k) pair at the owning rank, followed by the per-slot
-// and per-recv-token scalars, and finally one release-add per touched (rank, tile) counter.
-// `dst` holds per-rank absolute pointers resolved from the peers' records (shared memory).
+// Row push.  Pairs are shipped in the order of the send list: local expert index first, then the
+// destination rank rotated by the sender's rank, then channel and token.  Every rank therefore fills
+// local expert 0 of all owners first, which is the order in which the owners' GEMM kernels consume
+// tiles, and at any time the senders are spread over all destinations.  A warp copies the row of
+// each pair of its chunk into the pair's pool slot at the owning rank, writes the per-slot and
+// per-recv-token scalars, and finally release-adds every (rank, tile) counter the chunk touched.
+// `tg` holds per-rank absolute pointers resolved from the peers' records (shared memory).
 // ---------------------------------------------------------------------------------------------
 struct PushTargets {
   char* pool[kMaxRanks];
@@ -100,85 +103,70 @@ __device__ __forceinline__ void resolve_push_targets(PushTargets& tg, int p, voi
   tg.recv_src[p] = reinterpret_cast<int2*>(b + rec[9]);
 }
 
-__device__ __forceinline__ void push_chunk(const PushParams& p, const PushTargets& tg, int tok_begin,
-                                           int tok_end, int lane) {
+// One warp ships the pairs at positions [pos_begin, pos_end) of the send list (at most 32).  Lane j
+// owns pair j of the chunk for the scalar work; the row copies are done by the whole warp, one pair
+// after another.
+__device__ __forceinline__ void push_chunk(const PushParams& p, const PushTargets& tg, int pos_begin,
+                                           int pos_end, int lane) {
   const int K = p.num_topk, R = p.num_ranks;
   const int e_local = p.num_experts / R;
   const size_t row_bytes = static_cast<size_t>(p.hidden) * 2;
   const int vec_per_row = p.hidden / 8;   // 16-byte vectors
+  const int n = pos_end - pos_begin;
 
-  for (int t = tok_begin; t < tok_end; ++t) {
-    // lane k (< K) owns pair (t, k)
-    int slot = -1, dst = -1;
-    if (lane < K) {
-      long long e = p.topk_idx[static_cast<size_t>(t) * K + lane];
-      slot = p.pair_slot[static_cast<size_t>(t) * K + lane];
-      if (e >= 0 && slot >= 0) dst = static_cast<int>(e / e_local); else slot = -1;
+  int t = -1, k = 0, slot = -1, dst = -1;
+  if (lane < n) {
+    const int pair = p.send_list[pos_begin + lane];
+    t = pair / K; k = pair - t * K;
+    const long long e = p.topk_idx[pair];
+    slot = p.pair_slot[pair];
+    dst = static_cast<int>(e / e_local);
+  }
+  for (int j = 0; j < n; ++j) {
+    const int tj = __shfl_sync(0xffffffffu, t, j);
+    const int sj = __shfl_sync(0xffffffffu, slot, j);
+    const int dj = __shfl_sync(0xffffffffu, dst, j);
+    const char* src_row = static_cast<const char*>(p.x) + static_cast<size_t>(tj) * row_bytes;
+    char* dst_row = tg.pool[dj] + static_cast<size_t>(sj) * row_bytes;
+    int v = lane;
+    for (; v + 96 < vec_per_row; v += 128) {
+      uint4 a0 = ld_nc_v4(src_row + static_cast<size_t>(v) * 16);
+      uint4 a1 = ld_nc_v4(src_row + static_cast<size_t>(v + 32) * 16);
+      uint4 a2 = ld_nc_v4(src_row + static_cast<size_t>(v + 64) * 16);
+      uint4 a3 = ld_nc_v4(src_row + static_cast<size_t>(v + 96) * 16);
+      st_na_v4(dst_row + static_cast<size_t>(v) * 16, a0);
+      st_na_v4(dst_row + static_cast<size_t>(v + 32) * 16, a1);
+      st_na_v4(dst_row + static_cast<size_t>(v + 64) * 16, a2);
+      st_na_v4(dst_row + static_cast<size_t>(v + 96) * 16, a3);
     }
-    // row copy: every 16-byte vector is loaded once and stored to each pair's slot
-    const char* src_row = static_cast<const char*>(p.x) + static_cast<size_t>(t) * row_bytes;
-    for (int k = 0; k < K; ++k) {
-      const int s = __shfl_sync(0xffffffffu, slot, k);
-      const int d = __shfl_sync(0xffffffffu, dst, k);
-      if (s < 0) continue;
-      char* dst_row = tg.pool[d] + static_cast<size_t>(s) * row_bytes;
-      int v = lane;
-      for (; v + 96 < vec_per_row; v += 128) {
-        uint4 a0 = ld_nc_v4(src_row + static_cast<size_t>(v) * 16);
-        uint4 a1 = ld_nc_v4(src_row + static_cast<size_t>(v + 32) * 16);
-        uint4 a2 = ld_nc_v4(src_row + static_cast<size_t>(v + 64) * 16);
-        uint4 a3 = ld_nc_v4(src_row + static_cast<size_t>(v + 96) * 16);
-        st_na_v4(dst_row + static_cast<size_t>(v) * 16, a0);
-        st_na_v4(dst_row + static_cast<size_t>(v + 32) * 16, a1);
-        st_na_v4(dst_row + static_cast<size_t>(v + 64) * 16, a2);
-        st_na_v4(dst_row + static_cast<size_t>(v + 96) * 16, a3);
-      }
-      for (; v < vec_per_row; v += 32)
-        st_na_v4(dst_row + static_cast<size_t>(v) * 16, ld_nc_v4(src_row + static_cast<size_t>(v) * 16));
+    for (; v < vec_per_row; v += 32)
+      st_na_v4(dst_row + static_cast<size_t>(v) * 16, ld_nc_v4(src_row + static_cast<size_t>(v) * 16));
+  }
+  if (!p.is_grads && lane < n) {
+    const int r = p.send_recv_token[static_cast<size_t>(t) * R + dst];
+    tg.pool_topk_weight[dst][slot] = p.topk_weights[static_cast<size_t>(t) * K + k];
+    tg.pool_recv_token[dst][slot] = r;
+    tg.pool_k_slot[dst][slot] = k;
+    tg.pool_src[dst][slot] = make_int2(p.rank, t);
+    tg.recv_token_to_slots[dst][static_cast<size_t>(r) * K + k] = slot;   // other k of this recv token stay -1
+    // per-recv-token scalars: written by the first pair of this token that goes to `dst`
+    int cnt = 0; bool first = true;
+    for (int kk = 0; kk < K; ++kk) {
+      const long long e2 = p.topk_idx[static_cast<size_t>(t) * K + kk];
+      if (e2 >= 0 && static_cast<int>(e2 / e_local) == dst) { ++cnt; if (kk < k) first = false; }
     }
-    if (!p.is_grads) {
-      if (slot >= 0) {
-        const int r = p.send_recv_token[static_cast<size_t>(t) * R + dst];
-        tg.pool_topk_weight[dst][slot] = p.topk_weights[static_cast<size_t>(t) * K + lane];
-        tg.pool_recv_token[dst][slot] = r;
-        tg.pool_k_slot[dst][slot] = lane;
-        tg.pool_src[dst][slot] = make_int2(p.rank, t);
-      }
-      // per-recv-token scalars at every destination rank of this token
-      for (int d = 0; d < R; ++d) {
-        const int r = p.send_recv_token[static_cast<size_t>(t) * R + d];
-        if (r < 0) continue;
-        const unsigned mine = __ballot_sync(0xffffffffu, slot >= 0 && dst == d);
-        if (lane < K) tg.recv_token_to_slots[d][static_cast<size_t>(r) * K + lane] = (dst == d) ? slot : -1;
-        if (lane == 0) {
-          const int cnt = __popc(mine);
-          tg.k_local_total[d][r] = cnt;
-          tg.k_local_remaining[d][r] = cnt;
-          tg.recv_src[d][r] = make_int2(p.rank, t);
-        }
-      }
+    if (first) {
+      tg.k_local_total[dst][r] = cnt;
+      tg.k_local_remaining[dst][r] = cnt;
+      tg.recv_src[dst][r] = make_int2(p.rank, t);
     }
   }
   // Release the chunk: one add per distinct (rank, tile) the chunk touched.
   __syncwarp();
-  const int n_pairs = (tok_end - tok_begin) * K;
-  for (int base = 0; base < n_pairs; base += 32) {
-    const int i = base + lane;
-    int key = -1 - lane;   // unique per lane when there is nothing to count
-    int d = -1, tile = -1;
-    if (i < n_pairs) {
-      const size_t idx = static_cast<size_t>(tok_begin) * K + i;
-      const long long e = p.topk_idx[idx];
-      const int s = p.pair_slot[idx];
-      if (e >= 0 && s >= 0) {
-        d = static_cast<int>(e / e_local);
-        tile = s / p.tile_m;
-        key = (d << 24) | tile;
-      }
-    }
-    const unsigned peers = __match_any_sync(0xffffffffu, key);
-    if (d >= 0 && (__ffs(peers) - 1) == lane) red_release_sys_add(tg.arrival_count[d] + tile, __popc(peers));
-  }
+  const int key = (lane < n) ? ((dst << 24) | (slot / p.tile_m)) : (-1 - lane);
+  const unsigned peers = __match_any_sync(0xffffffffu, key);
+  if (lane < n && (__ffs(peers) - 1) == lane)
+    red_release_sys_add(tg.arrival_count[dst] + slot / p.tile_m, __popc(peers));
 }
 
 }  // namespace sep

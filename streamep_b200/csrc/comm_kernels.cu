@@ -62,6 +62,28 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
   const int per = (T + C - 1) / C;
   void* own = p.peer_base[p.rank];
 
+  if (p.phase_mask == 4) {
+    // ---------------------------------------------------------------- materialise (own launch, any grid)
+    const size_t gid = static_cast<size_t>(blockIdx.x) * blockDim.x + tid, gsz = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = gid; i < static_cast<size_t>(T) * K; i += gsz) {
+      const int t = static_cast<int>(i / K);
+      const long long e = p.topk_idx[i];
+      int slot = -1;
+      if (e >= 0 && e < E) {
+        const int c = t / per;
+        const int rk = p.pair_rank[i];
+        slot = p.send_base[static_cast<size_t>(c) * E + e] + rk;
+        p.send_list[p.send_order_base[static_cast<size_t>(c) * E + e] + rk] = static_cast<int>(i);
+      }
+      p.pair_slot[i] = slot;
+    }
+    for (size_t i = gid; i < static_cast<size_t>(T) * R; i += gsz) {
+      const int t = static_cast<int>(i / R), d = static_cast<int>(i - static_cast<size_t>(t) * R);
+      const int rk = p.token_rank_in_channel[i];
+      p.send_recv_token[i] = rk < 0 ? -1 : p.send_token_base[(t / per) * R + d] + rk;
+    }
+    return;
+  }
   if (p.phase_mask & 1) {
     const int c = blockIdx.x;
     const int lo = min(per * c, T), hi = min(lo + per, T);
@@ -102,7 +124,11 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
         }
         const unsigned m = __ballot_sync(0xffffffffu, hit);
         if (t < hi) {
-          p.token_rank_in_channel[static_cast<size_t>(t) * R + d] = hit ? run + __popc(m & ((1u << lane) - 1u)) : -1;
+          // position in the (channel, dst) stream; a token that is not sent records where the next
+          // sent one will sit, encoded as -(position) - 1
+          const int pos = run + __popc(m & ((1u << lane) - 1u));
+          p.token_rank_in_channel[static_cast<size_t>(t) * R + d] = hit ? pos : -1;
+          p.send_head[static_cast<size_t>(t) * R + d] = hit ? pos : -pos - 1;
           p.is_token_in_rank[static_cast<size_t>(t) * R + d] = hit ? 1 : 0;
         }
         run += __popc(m);
@@ -252,36 +278,56 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
       p.recv_channel_prefix_matrix[s * C + c] = rc;
     }
   }
+  // 6. push order of this rank's pairs: experts sorted by (local index, destination rank rotated by
+  //    this rank), channels in order inside an expert.  s_off is reused as the per-expert base.
   __syncthreads();
-  // 6. materialise destination slots and recv-token ids for this rank's pairs / tokens
-  for (size_t i = tid; i < static_cast<size_t>(T) * K; i += blockDim.x) {
-    const int t = static_cast<int>(i / K);
-    const long long e = p.topk_idx[i];
-    int slot = -1;
-    if (e >= 0 && e < E) slot = p.send_base[static_cast<size_t>(t / per) * E + e] + p.pair_rank[i];
-    p.pair_slot[i] = slot;
+  for (int e = tid; e < E; e += blockDim.x) {
+    int cnt = 0;
+    for (int c = 0; c < C; ++c) cnt += ctl_inbox_counts(own, p.ctl, parity, p.rank, c)[e];
+    const int d = e / EL, el = e - d * EL;
+    s_hist[el * R + ((d - p.rank + R) % R)] = cnt;     // keyed by push order
   }
-  for (size_t i = tid; i < static_cast<size_t>(T) * R; i += blockDim.x) {
-    const int t = static_cast<int>(i / R), d = static_cast<int>(i - static_cast<size_t>(t) * R);
-    const int rk = p.token_rank_in_channel[i];
-    p.send_recv_token[i] = rk < 0 ? -1 : p.send_token_base[(t / per) * R + d] + rk;
+  __syncthreads();
+  if (warp == 0) {
+    int carry = 0;
+    for (int base = 0; base < E; base += 32) {
+      const int i = base + lane;
+      const int v = (i < E) ? s_hist[i] : 0;
+      int total;
+      const int excl = warp_excl_scan(v, lane, total);
+      if (i < E) s_off[i] = carry + excl;
+      carry += total;
+    }
+    if (lane == 0) *p.num_send = carry;
   }
-  // send_head: position in the (channel, dst) stream; gaps hold -(next valid position) - 1
-  for (int i = tid; i < C * R; i += blockDim.x) {
-    const int c = i / R, d = i - c * R;
-    const int lo = min(per * c, T), hi = min(lo + per, T);
-    int nxt = ctl_inbox_tokens(own, p.ctl, parity, p.rank, c)[d];
-    for (int t = hi - 1; t >= lo; --t) {
-      const int rk = p.token_rank_in_channel[static_cast<size_t>(t) * R + d];
-      if (rk >= 0) { nxt = rk; p.send_head[static_cast<size_t>(t) * R + d] = rk; }
-      else p.send_head[static_cast<size_t>(t) * R + d] = -nxt - 1;
+  __syncthreads();
+  for (int e = tid; e < E; e += blockDim.x) {
+    const int d = e / EL, el = e - d * EL;
+    int run = s_off[el * R + ((d - p.rank + R) % R)];
+    for (int c = 0; c < C; ++c) {
+      p.send_order_base[static_cast<size_t>(c) * E + e] = run;
+      run += ctl_inbox_counts(own, p.ctl, parity, p.rank, c)[e];
     }
   }
 }
 
 void launch_dispatch_metadata(const MetadataParams& p, cudaStream_t stream) {
-  const int grid = (p.phase_mask & 1) ? p.num_channels : 1;
-  dispatch_metadata_kernel<<<grid, kMetaThreads, 0, stream>>>(p);
+  if (p.phase_mask & 3) {
+    MetadataParams q = p;
+    q.phase_mask = p.phase_mask & 3;
+    const int grid = (q.phase_mask & 1) ? p.num_channels : 1;
+    dispatch_metadata_kernel<<<grid, kMetaThreads, 0, stream>>>(q);
+  }
+  if (p.phase_mask & 2) {   // destination slots, recv-token ids and the send list, spread over many blocks
+    MetadataParams q = p;
+    q.phase_mask = 4;
+    const long long work = static_cast<long long>(p.num_tokens) * max(p.num_topk, p.num_ranks);
+    long long blocks = (work + 1023) / 1024;
+    if (blocks < 1) blocks = 1;
+    if (blocks > 148) blocks = 148;
+    const int grid = static_cast<int>(blocks);
+    dispatch_metadata_kernel<<<grid, kMetaThreads, 0, stream>>>(q);
+  }
 }
 
 // =============================================================================================
@@ -347,15 +393,16 @@ __global__ void __launch_bounds__(kPushThreads, 1) dispatch_push_kernel(const Pu
     }
     __syncthreads();
     if (s_ok) {
-      const int tpc = p.tokens_per_chunk;
-      const int num_chunks = (p.num_tokens + tpc - 1) / tpc;
+      const int ppc = p.pairs_per_chunk;
+      const int num_send = *p.num_send;
+      const int num_chunks = (num_send + ppc - 1) / ppc;
       for (;;) {
         int chunk = 0;
         if (lane == 0) chunk = atomicAdd(p.work_counter, 1);
         chunk = __shfl_sync(0xffffffffu, chunk, 0);
         if (chunk >= num_chunks) break;
-        const int t0 = chunk * tpc;
-        push_chunk(p, s_tg, t0, min(t0 + tpc, p.num_tokens), lane);
+        const int p0 = chunk * ppc;
+        push_chunk(p, s_tg, p0, min(p0 + ppc, num_send), lane);
       }
     }
   }

@@ -449,15 +449,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
       asm volatile("bar.sync 2, %0;" :: "r"(kPushWarps * 32) : "memory");
       if (s_push_ok) {
-        const int tpc = pp.tokens_per_chunk;
-        const int num_chunks = (pp.num_tokens + tpc - 1) / tpc;
+        const int ppc = pp.pairs_per_chunk;
+        const int num_send = *pp.num_send;
+        const int num_chunks = (num_send + ppc - 1) / ppc;
         for (;;) {
           int chunk = 0;
           if (lane == 0) chunk = atomicAdd(pp.work_counter, 1);
           chunk = __shfl_sync(0xffffffffu, chunk, 0);
           if (chunk >= num_chunks) break;
-          const int t0 = chunk * tpc;
-          push_chunk(pp, s_tg, t0, min(t0 + tpc, pp.num_tokens), lane);
+          const int p0 = chunk * ppc;
+          push_chunk(pp, s_tg, p0, min(p0 + ppc, num_send), lane);
         }
       }
     }

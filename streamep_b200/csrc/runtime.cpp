@@ -140,7 +140,8 @@ struct DispatchState {
   // sender side (regular device memory)
   at::Tensor sender_slab;
   at::Tensor pair_rank, pair_slot, token_rank_in_channel, send_recv_token, send_head, is_token_in_rank,
-      channel_prefix_matrix, send_base, send_token_base, peer_total_tiles, peer_num_recv;
+      channel_prefix_matrix, send_base, send_token_base, peer_total_tiles, peer_num_recv, send_order_base, send_list,
+      num_send;
   // receiver side metadata (regular device memory)
   at::Tensor expert_frequency, expert_pool_block_offset, base_pool, seen_per_substream, rank_prefix_matrix,
       recv_channel_prefix_matrix, tile_id_to_expert, pool_arrival_target;
@@ -365,8 +366,8 @@ class Runtime {
     st->meta_epoch = ++epochs_[kKindMetadata];
     const int64_t T = st->num_tokens, K = st->num_topk, R = num_ranks_, C = num_channels_, E = num_experts, EL = E / R;
     // One int32 slab for all small tensors (each torch::empty costs microseconds on the host).
-    const int64_t n_i32 = T * K * 2 + T * R * 3 + (T * R + 3) / 4 + R * C + C * E + C * R + 2 * R + EL + (EL + 1) +
-                          2 * C * R * EL + R * R + R * C + 64;
+    const int64_t n_i32 = T * K * 3 + T * R * 3 + (T * R + 3) / 4 + R * C + 2 * C * E + C * R + 2 * R + EL + (EL + 1) +
+                          2 * C * R * EL + R * R + R * C + 96;
     st->sender_slab = at::empty({n_i32}, x.options().dtype(at::kInt));
     int64_t off = 0;
     auto take = [&](std::vector<int64_t> shape) {
@@ -380,6 +381,7 @@ class Runtime {
     st->is_token_in_rank = take({(T * R + 3) / 4}).view(at::kBool).narrow(0, 0, T * R).view({T, R});
     st->channel_prefix_matrix = take({R, C}); st->send_base = take({C, E}); st->send_token_base = take({C, R});
     st->peer_total_tiles = take({R}); st->peer_num_recv = take({R});
+    st->send_order_base = take({C, E}); st->send_list = take({T * K}); st->num_send = take({1});
     st->expert_frequency = take({EL}); st->expert_pool_block_offset = take({EL + 1});
     st->base_pool = take({C, R, EL}); st->seen_per_substream = take({C, R, EL});
     st->rank_prefix_matrix = take({R, R}); st->recv_channel_prefix_matrix = take({R, C});
@@ -401,6 +403,8 @@ class Runtime {
     p.is_token_in_rank = reinterpret_cast<unsigned char*>(st->is_token_in_rank.data_ptr<bool>());
     p.channel_prefix_matrix = st->channel_prefix_matrix.data_ptr<int>();
     p.send_base = st->send_base.data_ptr<int>(); p.send_token_base = st->send_token_base.data_ptr<int>();
+    p.send_order_base = st->send_order_base.data_ptr<int>(); p.send_list = st->send_list.data_ptr<int>();
+    p.num_send = st->num_send.data_ptr<int>();
     p.peer_total_tiles = st->peer_total_tiles.data_ptr<int>(); p.peer_num_recv = st->peer_num_recv.data_ptr<int>();
     p.expert_frequency = st->expert_frequency.data_ptr<int>();
     p.expert_pool_block_offset = st->expert_pool_block_offset.data_ptr<int>();
@@ -518,10 +522,11 @@ class Runtime {
     p.topk_weights = st.topk_weights.data_ptr<float>();
     p.pair_slot = st.pair_slot.data_ptr<int>();
     p.send_recv_token = st.send_recv_token.data_ptr<int>();
+    p.send_list = st.send_list.data_ptr<int>(); p.num_send = st.num_send.data_ptr<int>();
     p.num_tokens = st.num_tokens; p.hidden = st.hidden; p.num_topk = st.num_topk; p.num_experts = st.num_experts;
     p.num_ranks = num_ranks_; p.rank = rank_; p.tile_m = st.tile_m;
     p.is_grads = is_grads ? 1 : 0; p.kind = kind; p.epoch = epoch; p.flags = flags;
-    p.tokens_per_chunk = std::max(1, std::min(8, 64 / std::max(1, st.num_topk)));
+    p.pairs_per_chunk = 16;
     fill_peers(p.peer_base); p.ctl = ctl_; p.own = rec;
     p.own_arrival_count = own_count; p.own_arrival_target = st.pool_arrival_target.data_ptr<int>();
     p.own_total_tiles = st.total_tiles;
@@ -895,6 +900,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       RO(x) RO(topk_idx) RO(topk_weights) RO(num_tokens) RO(hidden) RO(num_topk) RO(num_experts) RO(tile_m) RO(seq)
       RO(pair_rank) RO(pair_slot) RO(token_rank_in_channel) RO(send_recv_token) RO(send_head) RO(is_token_in_rank)
       RO(channel_prefix_matrix) RO(send_base) RO(send_token_base) RO(peer_total_tiles) RO(peer_num_recv)
+      RO(send_order_base) RO(send_list) RO(num_send)
       RO(expert_frequency) RO(expert_pool_block_offset) RO(base_pool) RO(seen_per_substream) RO(rank_prefix_matrix)
       RO(recv_channel_prefix_matrix) RO(tile_id_to_expert) RO(pool_arrival_target)
       RO(pool) RO(pool_topk_weight) RO(pool_recv_token) RO(pool_k_slot) RO(pool_src) RO(recv_token_to_slots)

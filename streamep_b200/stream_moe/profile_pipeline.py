@@ -26,14 +26,14 @@ LOGICAL = [  # substring of the kernel name -> logical name (template args: BN, 
     ("fill_tile_metadata_kernel", "tile fill"),
     ("dispatch_push_kernel", "dispatch / dispatch_grads (stand-alone push)"),
     ("combine_pull_kernel", "combine / combine_grads (stand-alone pull)"),
-    ("0, 0, 1, 1>", "dispatch (+) GEMM-A SwiGLU (fused)"),
-    ("0, 0, 1, 0>", "GEMM-A SwiGLU"),
-    ("0, 0, 2, 0>", "GEMM-Y (+ combine when remote)"),
-    ("0, 1, 3, 1>", "dispatch_grads (+) GEMM-Y_bwd dSwiGLU (fused)"),
-    ("0, 1, 3, 0>", "GEMM-Y_bwd dSwiGLU"),
-    ("0, 1, 2, 0>", "GEMM-A_bwd (+ combine_grads when remote)"),
-    ("1, 1, 0, 0>", "dW grouped GEMM"),
-    ("0, 0, 0, 0>", "preact recompute GEMM"),
+    ("false, false, 1, true>", "dispatch (+) GEMM-A SwiGLU (fused)"),
+    ("false, false, 1, false>", "GEMM-A SwiGLU"),
+    ("false, false, 2, false>", "GEMM-Y (+ combine when remote)"),
+    ("false, true, 3, true>", "dispatch_grads (+) GEMM-Y_bwd dSwiGLU (fused)"),
+    ("false, true, 3, false>", "GEMM-Y_bwd dSwiGLU"),
+    ("false, true, 2, false>", "GEMM-A_bwd (+ combine_grads when remote)"),
+    ("true, true, 0, false>", "dW grouped GEMM"),
+    ("false, false, 0, false>", "preact recompute GEMM"),
     ("pool_rows_kernel", "pool compress / expand"),
     ("router_kernel", "router"),
     ("device_barrier_kernel", "barrier / tail handshake"),
@@ -41,9 +41,13 @@ LOGICAL = [  # substring of the kernel name -> logical name (template args: BN, 
 
 
 def classify(name: str) -> str:
+    name = name.replace(", 0, 0,", ", false, false,").replace(", 0, 1,", ", false, true,").replace(", 1, 1,", ", true, true,")
     for key, label in LOGICAL:
         if key in name:
             return label
+    for epi, push, label in ((1, 1, 4), (1, 0, 5), (2, 0, 6), (3, 1, 7), (3, 0, 8)):
+        if name.endswith(f"{epi}, {push}>") or f", {epi}, {push}>(" in name:
+            return LOGICAL[label][1]
     if "Memset" in name or "memset" in name or "FillFunctor" in name:
         return "memset / fill (torch)"
     return "other: " + name[:60]
