@@ -12,11 +12,11 @@ number of GPUs grows.  ``--config scaling`` runs the Mixtral-style sweep shape (
 hidden 4096, 8 experts in total, top-2, ffn 14336, 3 layers back to back); ``--config wide`` the
 dispatch-heavy shape (4096 tokens/rank, hidden 7168, 32 experts/rank, top-8, ffn 2048).
 
-Timing: W untimed warm-up steps, then exactly K steps between CUDA events on the launching stream,
-bracketed by a barrier and a device synchronize; a buffer larger than L2 is rewritten between steps
-(outside the event pairs of a step are not possible without gaps, so the flush is part of the
-measured loop and counted: it costs the same in every run).  The reported value is the max over
-ranks.  ``e2e`` repeats the measurement through the public module API with, every step, the
+Timing: W (>= 3) untimed warm-up steps, then exactly K steps, the whole region bracketed by a
+barrier and a device synchronize on both sides.  Each step sits between its own pair of CUDA events
+on the launching stream and a 256 MiB buffer (larger than the 126 MB L2) is rewritten between
+steps, outside the event pairs; ``ms_per_step`` is the mean of the K event intervals and the
+reported value is the max over ranks.  ``e2e`` repeats the measurement through the public module API with, every step, the
 host-to-device copy of that step's inputs from pinned memory and a device-to-host read of the loss.
 """
 from __future__ import annotations
@@ -24,9 +24,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import subprocess
 import sys
-import threading
 import time
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
@@ -38,59 +36,6 @@ CONFIGS = {
     "wide":    dict(tokens=4096, hidden=7168, experts_per_rank=32, experts_total=None, topk=8, ffn=2048, layers=1),
     "tiny":    dict(tokens=512, hidden=256, experts_per_rank=4, experts_total=None, topk=2, ffn=128, layers=1),
 }
-
-
-class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, gpu_index: int):
-        self.gpu_index = gpu_index
-        self.proc = None
-        self.lines = []
-        self.thread = None
-
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
-            return
-
-        def pump():
-            for line in self.proc.stdout:
-                self.lines.append(line.strip())
-        self.thread = threading.Thread(target=pump, daemon=True)
-        self.thread.start()
-
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, power, reasons = [], [], [], set()
-        for ln in self.lines:
-            parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1])); mx.append(float(parts[2])); power.append(float(parts[3]))
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
 def reference_arm(args):
@@ -193,8 +138,8 @@ def main():
     barrier()
     if buffer is not None:
         buffer.check_status()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    from streamep_b200.utils.clocks import ClockSampler
+    sampler = ClockSampler(local_rank).start()
     l0 = launches()
     barrier()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
