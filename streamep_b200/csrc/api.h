@@ -201,6 +201,12 @@ void launch_pool_compress(const void* pool, void* recv, const int* pool_recv_tok
 void launch_pool_expand(const void* recv, void* pool, const int* pool_recv_token, int tk_padded,
                         int hidden, cudaStream_t stream);
 
+// out[t, :] += sum over the pairs (t, k) owned by OTHER ranks of rows[t * K + k, :], accumulated in fp32.
+// Second half of the fused combine: expert ranks store one bf16 row per remote (token, k) pair into the
+// source rank's `rows`; pairs owned by the source rank itself were already reduced into `out`.
+void launch_combine_reduce(void* out, const void* rows, const long long* topk_idx, int num_tokens, int hidden,
+                           int num_topk, int num_experts, int num_ranks, int rank, cudaStream_t stream);
+
 struct RouterParams {
   const void* x;        // [T, H] bf16
   const void* w_gate;   // [E, H] bf16
@@ -261,7 +267,8 @@ struct GemmParams {
   // scatter targets
   void* scatter_local;           // [T_recv, N] bf16 (local variant)
   const int2* row_src;           // per-slot (src_rank, src_token) (remote variant)
-  RemoteRef remote_out;          // remote variant: each source rank's [T, N] bf16 accumulator
+  RemoteRef remote_out;          // remote variant: each source rank's [T * K, N] bf16 rows, one per (token, k);
+                                 // rows whose source is this rank are red.added into scatter_local instead
   // remote return of per-slot scalars (dswiglu, fused backward): final dl_dweight -> source [T, K] fp32
   RemoteRef remote_dw;
   const int* row_k_slot;
@@ -282,8 +289,10 @@ struct GemmParams {
 };
 
 // tmap_a / tmap_b: 128-byte CUtensorMap blobs (3-D, bf16, 128-byte swizzle) built by the host.
-void launch_grouped_gemm(const GemmParams& p, const void* tmap_a, const void* tmap_b,
-                         const PushParams* fused_push, int num_ctas, cudaStream_t stream);
+// tmap_o0 / tmap_o1: output maps for the TMA-store epilogues (store, swiglu, dswiglu); box 32 rows x one
+// staging row (32, 64 or 128 bytes) with the matching swizzle.  Null for the scatter epilogue.
+void launch_grouped_gemm(const GemmParams& p, const void* tmap_a, const void* tmap_b, const void* tmap_o0,
+                         const void* tmap_o1, const PushParams* fused_push, int num_ctas, cudaStream_t stream);
 size_t grouped_gemm_smem_bytes(int block_n);
 
 }  // namespace sep

@@ -600,6 +600,49 @@ void launch_pool_expand(const void* recv, void* pool, const int* pool_recv_token
 }
 
 // =============================================================================================
+// Second half of the fused combine: fp32 reduction of the rows that remote expert ranks stored
+// =============================================================================================
+__global__ void combine_reduce_kernel(char* out, const char* rows, const long long* topk_idx, int num_tokens,
+                                      int hidden, int K, int e_local, int rank) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t row_bytes = static_cast<size_t>(hidden) * 2;
+  const int vecs = hidden / 8;
+  for (int t = blockIdx.x * warps_per_block + warp; t < num_tokens; t += gridDim.x * warps_per_block) {
+    unsigned remote = 0;
+    for (int k = 0; k < K; ++k) {
+      const long long e = topk_idx[static_cast<size_t>(t) * K + k];
+      if (e >= 0 && static_cast<int>(e / e_local) != rank) remote |= 1u << k;
+    }
+    if (remote == 0) continue;
+    for (int v = lane; v < vecs; v += 32) {
+      char* o = out + static_cast<size_t>(t) * row_bytes + static_cast<size_t>(v) * 16;
+      const uint4 q0 = *reinterpret_cast<const uint4*>(o);
+      float acc[8];
+      { const float2 a = unpack_bf16x2(q0.x), b = unpack_bf16x2(q0.y), c = unpack_bf16x2(q0.z), d = unpack_bf16x2(q0.w);
+        acc[0] = a.x; acc[1] = a.y; acc[2] = b.x; acc[3] = b.y; acc[4] = c.x; acc[5] = c.y; acc[6] = d.x; acc[7] = d.y; }
+      for (int k = 0; k < K; ++k) {
+        if (!((remote >> k) & 1u)) continue;
+        const uint4 q = ld_nc_v4(rows + (static_cast<size_t>(t) * K + k) * row_bytes + static_cast<size_t>(v) * 16);
+        const float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), c = unpack_bf16x2(q.z), d = unpack_bf16x2(q.w);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+      }
+      uint4 r;
+      r.x = pack_bf16x2(acc[0], acc[1]); r.y = pack_bf16x2(acc[2], acc[3]);
+      r.z = pack_bf16x2(acc[4], acc[5]); r.w = pack_bf16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(o) = r;
+    }
+  }
+}
+void launch_combine_reduce(void* out, const void* rows, const long long* topk_idx, int num_tokens, int hidden,
+                           int num_topk, int num_experts, int num_ranks, int rank, cudaStream_t stream) {
+  if (num_tokens == 0 || num_ranks == 1) return;
+  const int grid = min((num_tokens + 7) / 8, 148 * 8);
+  combine_reduce_kernel<<<grid, 256, 0, stream>>>(static_cast<char*>(out), static_cast<const char*>(rows), topk_idx,
+                                                  num_tokens, hidden, num_topk, num_experts / num_ranks, rank);
+}
+
+// =============================================================================================
 // Router: logits = x @ w_gate^T, softmax, top-k, renormalise, rank bitmap.  One warp per token.
 // The reference has no router; its harnesses build routing with torch ops
 // (stream_ep/stream_moe/profile_pipeline.py:102-139).

@@ -37,8 +37,9 @@ template <int BN> struct GemmCfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (BN == 256) ? 4 : 6;
   static constexpr int kTmemCols = 2 * BN;                    // two accumulator buffers
-  static constexpr int kBarrierBytes = 1024;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kEpiStageBytes = 4096;                 // per epilogue warp: 32 rows x 128 bytes
+  static constexpr int kSmemBytes = kStages * kStageBytes + 8 * kEpiStageBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
 size_t grouped_gemm_smem_bytes(int block_n) {
@@ -88,13 +89,15 @@ __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;"
 template <int BN, bool A_MN, bool B_MN, int EPI, bool PUSH>
 __global__ void __launch_bounds__((kGemmWarps + (PUSH ? kPushWarps : 0)) * 32, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_o0, const __grid_constant__ CUtensorMap tmap_o1,
                     const GemmParams p, const PushParams pp) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ unsigned char smem_dyn[];
   // 128-byte swizzle atoms are 1024 bytes: align the operand ring accordingly.
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   unsigned char* stage_base = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  unsigned char* epi_stage = smem + Cfg::kStages * Cfg::kStageBytes;      // 8 x 4 KB, 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + 8 * Cfg::kEpiStageBytes);
   uint64_t* full_bar = bars;                               // [kStages]
   uint64_t* empty_bar = bars + Cfg::kStages;               // [kStages]
   uint64_t* tmem_full = bars + 2 * Cfg::kStages;           // [2]
@@ -249,16 +252,28 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     if (!ok) report_failure(p.status, kStatusTimeoutPipeline, kKernelGemm, 1, p.rank, 0, 0, 0);
   } else if (warp < kGemmWarps) {
     // ------------------------------------------------------------------ epilogue (8 warps: a warp reads the 32 TMEM
-    // lanes of its quarter; warps 2..5 take the left half of the tile's columns, warps 6..9 the right half)
+    // lanes of its quarter; warps 2..5 take the left half of the tile's columns, warps 6..9 the right half).
+    // Results go through a per-warp 4 KB swizzled staging tile so that global memory only ever sees
+    // full contiguous row segments: TMA stores for dense outputs, warp-coalesced red.add / st for scatters.
     const int quarter = warp & 3;                 // TMEM lanes this warp may read
     const int row = quarter * 32 + lane;
     const int epi_tid = (warp - 2) * 32 + lane;
     const int half = (warp - 2) >> 2;
     constexpr int kChunksPerHalf = BN / 64;
+    const uint32_t stg = smem_u32(epi_stage + (warp - 2) * Cfg::kEpiStageBytes);
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
     for (int lin = blockIdx.x; lin < total_tiles; lin += gridDim.x) {
       const TileCoord t = decode_tile(p, lin);
       const bool empty = (t.k_blocks == 0);
+      if (EPI == kEpiDswiglu) {
+        // While the tensor cores still work on this tile, pull this thread's segment of preact towards L2.
+        const long long prow = static_cast<long long>(t.row0) + row;
+        const int pn = t.n_tile * BN + half * (BN / 2);
+        const char* pre = reinterpret_cast<const char*>(static_cast<const __nv_bfloat16*>(p.preact) + prow * p.ld_preact + 2 * pn);
+#pragma unroll
+        for (int j = 0; j < BN / 64; ++j)
+          if (pn + j * 32 < p.N) prefetch_l2(pre + j * 128);
+      }
       if (!empty && ok) {
         if (!mbar_wait(&tmem_full[acc], acc_phase, budget, p.status)) {
           report_failure(p.status, kStatusTimeoutPipeline, kKernelGemm, 2, p.rank, lin, acc, 0);
@@ -269,26 +284,30 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (!ok) break;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
       const int n0 = t.n_tile * BN;
-      // row bookkeeping
-      long long grow;       // global output row
-      bool row_ok = true;
-      if (p.mode == kVarlenM) {
-        grow = static_cast<long long>(t.row0) + row;
-      } else {
-        const int m = t.m_tile * BM + row;
-        row_ok = m < p.M_out;
-        grow = m;
-      }
+      // first output row of this warp (TMA y coordinate) and this thread's global row
+      const int warp_row0 = (p.mode == kVarlenM ? t.row0 : t.m_tile * BM) + quarter * 32;
+      const int zc = (p.mode == kVarlenK) ? t.expert : 0;
+      const long long grow = static_cast<long long>(p.mode == kVarlenM ? t.row0 : t.m_tile * BM) + row;
       int tok = 0; float w = 1.f;
       if (EPI == kEpiScatter || EPI == kEpiDswiglu) {
         tok = p.row_token[grow];
         if (p.row_weight != nullptr && tok >= 0) w = p.row_weight[grow];
       }
-      float dw_acc = 0.f;
-      int2 src = make_int2(0, 0);
-      if ((EPI == kEpiScatter && p.remote_out.enabled) || (EPI == kEpiDswiglu && p.remote_dw.enabled)) {
-        if (tok >= 0) src = p.row_src[grow];
+      // scatter: where this row goes and how (0 skip, 1 bf16x2 red.add, 2 plain store)
+      char* dst_row = nullptr; int op = 0;
+      if (EPI == kEpiScatter && tok >= 0) {
+        if (p.remote_out.enabled) {
+          const int2 src = p.row_src[grow];
+          if (src.x == p.rank) {
+            dst_row = static_cast<char*>(p.scatter_local) + static_cast<long long>(src.y) * p.N * 2; op = 1;
+          } else {   // the source rank's per-(token, k) row: written once, reduced there in fp32
+            dst_row = s_remote_out[src.x] + (static_cast<long long>(src.y) * p.num_topk + p.row_k_slot[grow]) * p.N * 2; op = 2;
+          }
+        } else {
+          dst_row = static_cast<char*>(p.scatter_local) + static_cast<long long>(tok) * p.N * 2; op = 1;
+        }
       }
+      float dw_acc = 0.f;
 #pragma unroll 1
       for (int c = half * kChunksPerHalf; c < (half + 1) * kChunksPerHalf; ++c) {
         const int n = n0 + c * 32;
@@ -312,100 +331,117 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           for (int i = 0; i < 32; ++i) r[i] = 0;
         }
         if (EPI == kEpiStore) {
-          if (row_ok) {
-            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out0) +
-                                 static_cast<long long>(t.expert) * p.out_expert_stride + grow * p.ld0 + n;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              if (n + q * 8 < p.N)
-                st_global_v4(dst + q * 8,
-                             pack_bf16x2(__uint_as_float(r[q * 8 + 0]), __uint_as_float(r[q * 8 + 1])),
-                             pack_bf16x2(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3])),
-                             pack_bf16x2(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5])),
-                             pack_bf16x2(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7])));
-            }
-          }
+          for (int q = 0; q < 4; ++q)
+            st_shared_v4(stg + stage_off<64>(lane, q),
+                         pack_bf16x2(__uint_as_float(r[q * 8 + 0]), __uint_as_float(r[q * 8 + 1])),
+                         pack_bf16x2(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3])),
+                         pack_bf16x2(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5])),
+                         pack_bf16x2(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7])));
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) { tma_store_3d(&tmap_o0, epi_stage + (warp - 2) * Cfg::kEpiStageBytes, n, warp_row0, zc); bulk_commit(); bulk_wait_read(); }
+          __syncwarp();
         } else if (EPI == kEpiSwiglu) {
-          // columns (2i, 2i+1) = (gate_i, up_i)
+          // columns (2i, 2i+1) = (gate_i, up_i); preact tile at +0 (64-byte rows), postact tile at +2048 (32-byte rows)
           if (p.out1 != nullptr) {
-            __nv_bfloat16* pre = static_cast<__nv_bfloat16*>(p.out1) + grow * p.ld1 + n;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              if (n + q * 8 < p.N)
-                st_global_v4(pre + q * 8,
-                             pack_bf16x2(__uint_as_float(r[q * 8 + 0]), __uint_as_float(r[q * 8 + 1])),
-                             pack_bf16x2(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3])),
-                             pack_bf16x2(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5])),
-                             pack_bf16x2(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7])));
-            }
+            for (int q = 0; q < 4; ++q)
+              st_shared_v4(stg + stage_off<64>(lane, q),
+                           pack_bf16x2(__uint_as_float(r[q * 8 + 0]), __uint_as_float(r[q * 8 + 1])),
+                           pack_bf16x2(__uint_as_float(r[q * 8 + 2]), __uint_as_float(r[q * 8 + 3])),
+                           pack_bf16x2(__uint_as_float(r[q * 8 + 4]), __uint_as_float(r[q * 8 + 5])),
+                           pack_bf16x2(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7])));
           }
           float a[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float g = __uint_as_float(r[2 * i]), u = __uint_as_float(r[2 * i + 1]);
-            a[i] = g / (1.f + __expf(-g)) * u;
+            a[i] = g * fast_sigmoid(g) * u;
           }
-          __nv_bfloat16* post = static_cast<__nv_bfloat16*>(p.out0) + grow * p.ld0 + n / 2;
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            if (n + q * 16 < p.N)
-              st_global_v4(post + q * 8, pack_bf16x2(a[q * 8 + 0], a[q * 8 + 1]), pack_bf16x2(a[q * 8 + 2], a[q * 8 + 3]),
-                           pack_bf16x2(a[q * 8 + 4], a[q * 8 + 5]), pack_bf16x2(a[q * 8 + 6], a[q * 8 + 7]));
+          for (int q = 0; q < 2; ++q)
+            st_shared_v4(stg + 2048 + stage_off<32>(lane, q), pack_bf16x2(a[q * 8 + 0], a[q * 8 + 1]),
+                         pack_bf16x2(a[q * 8 + 2], a[q * 8 + 3]), pack_bf16x2(a[q * 8 + 4], a[q * 8 + 5]),
+                         pack_bf16x2(a[q * 8 + 6], a[q * 8 + 7]));
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            unsigned char* sb = epi_stage + (warp - 2) * Cfg::kEpiStageBytes;
+            if (p.out1 != nullptr) tma_store_3d(&tmap_o1, sb, n, warp_row0, 0);
+            tma_store_3d(&tmap_o0, sb + 2048, n / 2, warp_row0, 0);
+            bulk_commit(); bulk_wait_read();
           }
+          __syncwarp();
         } else if (EPI == kEpiScatter) {
-          if (tok >= 0) {
-            __nv_bfloat16* dst;
-            if (p.remote_out.enabled) {
-              dst = reinterpret_cast<__nv_bfloat16*>(s_remote_out[src.x]) + static_cast<long long>(src.y) * p.N + n;
-            } else {
-              dst = static_cast<__nv_bfloat16*>(p.scatter_local) + static_cast<long long>(tok) * p.N + n;
-            }
+          // stage the weighted bf16 row segment (64 bytes), then let 4 lanes handle one row so that
+          // every global access is a contiguous 64-byte piece of a destination row
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              if (n + q * 8 < p.N)
-                red_add_bf16x2_v4(dst + q * 8,
-                                  pack_bf16x2(w * __uint_as_float(r[q * 8 + 0]), w * __uint_as_float(r[q * 8 + 1])),
-                                  pack_bf16x2(w * __uint_as_float(r[q * 8 + 2]), w * __uint_as_float(r[q * 8 + 3])),
-                                  pack_bf16x2(w * __uint_as_float(r[q * 8 + 4]), w * __uint_as_float(r[q * 8 + 5])),
-                                  pack_bf16x2(w * __uint_as_float(r[q * 8 + 6]), w * __uint_as_float(r[q * 8 + 7])));
+          for (int q = 0; q < 4; ++q)
+            st_shared_v4(stg + stage_off<64>(lane, q),
+                         pack_bf16x2(w * __uint_as_float(r[q * 8 + 0]), w * __uint_as_float(r[q * 8 + 1])),
+                         pack_bf16x2(w * __uint_as_float(r[q * 8 + 2]), w * __uint_as_float(r[q * 8 + 3])),
+                         pack_bf16x2(w * __uint_as_float(r[q * 8 + 4]), w * __uint_as_float(r[q * 8 + 5])),
+                         pack_bf16x2(w * __uint_as_float(r[q * 8 + 6]), w * __uint_as_float(r[q * 8 + 7])));
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int rr = i * 8 + (lane >> 2), piece = lane & 3;
+            const uint4 v = ld_shared_v4(stg + stage_off<64>(rr, piece));
+            char* ptr = reinterpret_cast<char*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(dst_row), rr));
+            const int o = __shfl_sync(0xffffffffu, op, rr);
+            const int col = n + piece * 8;
+            if (o != 0 && col < p.N) {
+              if (o == 1) red_add_bf16x2_v4(ptr + static_cast<long long>(col) * 2, v.x, v.y, v.z, v.w);
+              else st_na_v4(ptr + static_cast<long long>(col) * 2, v);
             }
           }
+          __syncwarp();
         } else {   // kEpiDswiglu: r = g[row, n..n+32) = dL/d(postact) before the topk weight
-          __nv_bfloat16* din = static_cast<__nv_bfloat16*>(p.out0) + grow * p.ld0 + 2 * n;
-          __nv_bfloat16* pw = static_cast<__nv_bfloat16*>(p.out1) + grow * p.ld1 + n;
+          uint32_t o_in[32], o_pw[16];
           if (tok >= 0) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {       // 8 output columns per step
-              if (n + q * 8 >= p.N) break;
               const uint4 p0 = pq[q * 2], p1 = pq[q * 2 + 1];
               const uint32_t pv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-              uint32_t o_in[8]; float post[8];
+              float post[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
-                const float2 gu = unpack_bf16x2(pv[i]);
+                const bool in = (n + q * 8 + i) < p.N;
+                const float2 gu = in ? unpack_bf16x2(pv[i]) : make_float2(0.f, 0.f);
                 const float g = __uint_as_float(r[q * 8 + i]);
-                const float sig = 1.f / (1.f + __expf(-gu.x));
+                const float sig = fast_sigmoid(gu.x);
                 const float silu = gu.x * sig;
                 post[i] = silu * gu.y;
-                dw_acc += post[i] * g;
+                dw_acc += in ? post[i] * g : 0.f;
                 const float dgate = w * g * gu.y * sig * (1.f + gu.x * (1.f - sig));
                 const float dup = w * g * silu;
-                o_in[i] = pack_bf16x2(dgate, dup);
+                o_in[q * 8 + i] = pack_bf16x2(dgate, dup);
               }
-              st_global_v4(din + q * 16, o_in[0], o_in[1], o_in[2], o_in[3]);
-              st_global_v4(din + q * 16 + 8, o_in[4], o_in[5], o_in[6], o_in[7]);
-              st_global_v4(pw + q * 8, pack_bf16x2(w * post[0], w * post[1]), pack_bf16x2(w * post[2], w * post[3]),
-                           pack_bf16x2(w * post[4], w * post[5]), pack_bf16x2(w * post[6], w * post[7]));
+#pragma unroll
+              for (int i = 0; i < 4; ++i) o_pw[q * 4 + i] = pack_bf16x2(w * post[2 * i], w * post[2 * i + 1]);
             }
           } else {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              if (n + q * 8 >= p.N) break;
-              st_global_v4(din + q * 16, 0, 0, 0, 0);
-              st_global_v4(din + q * 16 + 8, 0, 0, 0, 0);
-              st_global_v4(pw + q * 8, 0, 0, 0, 0);
-            }
+            for (int i = 0; i < 32; ++i) o_in[i] = 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o_pw[i] = 0;
           }
+          unsigned char* sb = epi_stage + (warp - 2) * Cfg::kEpiStageBytes;
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            st_shared_v4(stg + stage_off<128>(lane, q), o_in[q * 4 + 0], o_in[q * 4 + 1], o_in[q * 4 + 2], o_in[q * 4 + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) { tma_store_3d(&tmap_o0, sb, 2 * n, warp_row0, 0); bulk_commit(); bulk_wait_read(); }
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            st_shared_v4(stg + stage_off<64>(lane, q), o_pw[q * 4 + 0], o_pw[q * 4 + 1], o_pw[q * 4 + 2], o_pw[q * 4 + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) { tma_store_3d(&tmap_o1, sb, n, warp_row0, 0); bulk_commit(); bulk_wait_read(); }
+          __syncwarp();
         }
       }
       if (!empty) {
@@ -430,12 +466,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (EPI == kEpiScatter) {
             if (atom_add_acq_rel_gpu(p.k_remaining + tok, -1) == 1) st_release_gpu(p.done_per_token + tok, p.seq);
           } else {
+            const int2 src = p.row_src[grow];
             const float v = *reinterpret_cast<volatile float*>(p.dl_dweight + grow);
             s_remote_dw[src.x][static_cast<long long>(src.y) * p.num_topk + p.row_k_slot[grow]] = v;
           }
         }
       }
     }
+    if (lane == 0) bulk_wait_all();     // every bulk store this warp issued has been performed
     if (p.tail.enabled) __threadfence_system();
   } else if (PUSH) {
     // ------------------------------------------------------------------ dispatch push warps
@@ -499,8 +537,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 // Host dispatch over the template instances
 // ---------------------------------------------------------------------------------------------
 template <int BN, bool A_MN, bool B_MN, int EPI, bool PUSH>
-static void launch_instance(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& tb,
-                            const PushParams& pp, int num_ctas, cudaStream_t stream) {
+static void launch_instance(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to0,
+                            const CUtensorMap& to1, const PushParams& pp, int num_ctas, cudaStream_t stream) {
   auto kernel = grouped_gemm_kernel<BN, A_MN, B_MN, EPI, PUSH>;
   static bool configured = false;
   const int smem = GemmCfg<BN>::kSmemBytes;
@@ -509,47 +547,49 @@ static void launch_instance(const GemmParams& p, const CUtensorMap& ta, const CU
     configured = true;
   }
   const int threads = (kGemmWarps + (PUSH ? kPushWarps : 0)) * 32;
-  kernel<<<num_ctas, threads, smem, stream>>>(ta, tb, p, pp);
+  kernel<<<num_ctas, threads, smem, stream>>>(ta, tb, to0, to1, p, pp);
 }
 
 template <int BN, bool PUSH>
-static bool dispatch_layout(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& tb,
-                            const PushParams& pp, int n, cudaStream_t s) {
+static bool dispatch_layout(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to0,
+                            const CUtensorMap& to1, const PushParams& pp, int n, cudaStream_t s) {
   if (p.mode == kVarlenM && !p.a_mn_major && !p.b_mn_major) {
-    if (p.epilogue == kEpiSwiglu) { launch_instance<BN, false, false, kEpiSwiglu, PUSH>(p, ta, tb, pp, n, s); return true; }
+    if (p.epilogue == kEpiSwiglu) { launch_instance<BN, false, false, kEpiSwiglu, PUSH>(p, ta, tb, to0, to1, pp, n, s); return true; }
     if (PUSH) return false;
     if constexpr (!PUSH) {
-      if (p.epilogue == kEpiStore) { launch_instance<BN, false, false, kEpiStore, false>(p, ta, tb, pp, n, s); return true; }
-      if (p.epilogue == kEpiScatter) { launch_instance<BN, false, false, kEpiScatter, false>(p, ta, tb, pp, n, s); return true; }
+      if (p.epilogue == kEpiStore) { launch_instance<BN, false, false, kEpiStore, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
+      if (p.epilogue == kEpiScatter) { launch_instance<BN, false, false, kEpiScatter, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
     }
   }
   if (p.mode == kVarlenM && !p.a_mn_major && p.b_mn_major) {
-    if (p.epilogue == kEpiDswiglu) { launch_instance<BN, false, true, kEpiDswiglu, PUSH>(p, ta, tb, pp, n, s); return true; }
+    if (p.epilogue == kEpiDswiglu) { launch_instance<BN, false, true, kEpiDswiglu, PUSH>(p, ta, tb, to0, to1, pp, n, s); return true; }
     if constexpr (!PUSH) {
-      if (p.epilogue == kEpiScatter) { launch_instance<BN, false, true, kEpiScatter, false>(p, ta, tb, pp, n, s); return true; }
-      if (p.epilogue == kEpiStore) { launch_instance<BN, false, true, kEpiStore, false>(p, ta, tb, pp, n, s); return true; }
+      if (p.epilogue == kEpiScatter) { launch_instance<BN, false, true, kEpiScatter, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
+      if (p.epilogue == kEpiStore) { launch_instance<BN, false, true, kEpiStore, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
     }
   }
   if constexpr (!PUSH) {
     if (p.mode == kVarlenK && p.a_mn_major && p.b_mn_major && p.epilogue == kEpiStore) {
-      launch_instance<BN, true, true, kEpiStore, false>(p, ta, tb, pp, n, s); return true;
+      launch_instance<BN, true, true, kEpiStore, false>(p, ta, tb, to0, to1, pp, n, s); return true;
     }
   }
   return false;
 }
 
-void launch_grouped_gemm(const GemmParams& p, const void* tmap_a, const void* tmap_b, const PushParams* fused_push,
-                         int num_ctas, cudaStream_t stream) {
+void launch_grouped_gemm(const GemmParams& p, const void* tmap_a, const void* tmap_b, const void* tmap_o0,
+                         const void* tmap_o1, const PushParams* fused_push, int num_ctas, cudaStream_t stream) {
   const CUtensorMap& ta = *static_cast<const CUtensorMap*>(tmap_a);
   const CUtensorMap& tb = *static_cast<const CUtensorMap*>(tmap_b);
+  const CUtensorMap& to0 = *static_cast<const CUtensorMap*>(tmap_o0 ? tmap_o0 : tmap_a);
+  const CUtensorMap& to1 = *static_cast<const CUtensorMap*>(tmap_o1 ? tmap_o1 : tmap_a);
   bool ok;
   if (fused_push != nullptr) {
-    ok = (p.block_n == 256) ? dispatch_layout<256, true>(p, ta, tb, *fused_push, num_ctas, stream)
-                            : dispatch_layout<128, true>(p, ta, tb, *fused_push, num_ctas, stream);
+    ok = (p.block_n == 256) ? dispatch_layout<256, true>(p, ta, tb, to0, to1, *fused_push, num_ctas, stream)
+                            : dispatch_layout<128, true>(p, ta, tb, to0, to1, *fused_push, num_ctas, stream);
   } else {
     PushParams none{};
-    ok = (p.block_n == 256) ? dispatch_layout<256, false>(p, ta, tb, none, num_ctas, stream)
-                            : dispatch_layout<128, false>(p, ta, tb, none, num_ctas, stream);
+    ok = (p.block_n == 256) ? dispatch_layout<256, false>(p, ta, tb, to0, to1, none, num_ctas, stream)
+                            : dispatch_layout<128, false>(p, ta, tb, to0, to1, none, num_ctas, stream);
   }
   if (!ok) fprintf(stderr, "streamep_b200: unsupported grouped GEMM configuration (mode=%d epi=%d a_mn=%d b_mn=%d)\n",
                    p.mode, p.epilogue, p.a_mn_major, p.b_mn_major);
@@ -658,8 +698,8 @@ extern "C" int streamep_gemm_y_scatter_noalloc(const void* postact, const void* 
   const long long total = static_cast<long long>(p.num_m_tiles) * p.num_n_tiles;
   const int ctas = static_cast<int>(total < sms ? total : sms);
   PushParams none{};
-  if (block_n == 256) launch_instance<256, false, false, kEpiScatter, false>(p, ta, tb, none, ctas, stream);
-  else launch_instance<128, false, false, kEpiScatter, false>(p, ta, tb, none, ctas, stream);
+  if (block_n == 256) launch_instance<256, false, false, kEpiScatter, false>(p, ta, tb, ta, ta, none, ctas, stream);
+  else launch_instance<128, false, false, kEpiScatter, false>(p, ta, tb, ta, ta, none, ctas, stream);
   e = cudaGetLastError();
   if (e != cudaSuccess) return noalloc_fail(-3, "kernel launch", e);
   return 0;

@@ -107,6 +107,12 @@ __device__ __forceinline__ void st_na_v4(void* p, uint4 v) {
                :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" :: "l"(p));
+}
+// sigmoid through one ex2 and one approximate reciprocal (the results are rounded to bf16 anyway)
+__device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -192,6 +198,34 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, ui
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       :: "r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
+// Bulk tensor store shared -> global (clipped at the tensor's bounds), tracked by bulk async-groups.
+__device__ __forceinline__ void tma_store_3d(const void* tmap, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               :: "l"(tmap), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the source shared memory of all committed groups has been read (it may be overwritten)
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all committed groups are complete (their global writes are performed)
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" :: "r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+// Byte offset of 16-byte chunk `j` of row `r` in a staging tile with RB-byte rows (32, 64 or 128),
+// using the XOR swizzle that TMA applies for that row width (CU_TENSOR_MAP_SWIZZLE_32B/64B/128B).
+// Rows of one quarter-warp land in distinct banks, and a TMA store reads the tile back unswizzled.
+template <int RB>
+__device__ __forceinline__ uint32_t stage_off(int r, int j) {
+  const uint32_t a = static_cast<uint32_t>(r) * RB + static_cast<uint32_t>(j) * 16;
+  return a ^ (((a >> 7) & (RB / 16 - 1)) << 4);
 }
 
 // ----------------------------------------------------------------------------------------------

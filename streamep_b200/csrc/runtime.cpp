@@ -69,7 +69,8 @@ static Fn driver_fn(const char* name) {
 
 // 3-D bf16 tensor map, 128-byte swizzle, OOB reads return zero.  dims/box are innermost-first.
 static CUtensorMap make_tmap(const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_elems,
-                             uint64_t stride2_elems, uint32_t b0, uint32_t b1) {
+                             uint64_t stride2_elems, uint32_t b0, uint32_t b1,
+                             CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   static EncodeTiledFn encode = driver_fn<EncodeTiledFn>("cuTensorMapEncodeTiled");
   CUtensorMap m;
   cuuint64_t dims[3] = {d0, d1, d2};
@@ -79,7 +80,7 @@ static CUtensorMap make_tmap(const void* base, uint64_t d0, uint64_t d1, uint64_
   SEP_ASSERT(reinterpret_cast<uintptr_t>(base) % 16 == 0, "TMA base address must be 16-byte aligned");
   SEP_ASSERT(strides[0] % 16 == 0 && strides[1] % 16 == 0, "TMA row pitch must be a multiple of 16 bytes");
   CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) throw std::runtime_error("streamep_b200: cuTensorMapEncodeTiled failed with code " + std::to_string(r));
   return m;
@@ -644,7 +645,8 @@ class Runtime {
     p.mode = a.mode; p.epilogue = a.epilogue; p.block_n = a.block_n;
     p.a_mn_major = a.a_mn_major; p.b_mn_major = a.b_mn_major;
     p.rank = rank_; p.status = status_; p.wait_budget_ns = budget_ns_;
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, to0, to1;
+    bool have_o0 = false, have_o1 = false;
     const int BN = a.block_n;
     if (a.mode == kVarlenM) {
       // A: [rows, K] row-major; B: weights [E, N, K] (K-major) or [E, K, N] (MN-major)
@@ -707,8 +709,9 @@ class Runtime {
     set_ref(p.remote_dw, a.remote_dw);
     if (a.epilogue == kEpiScatter || a.epilogue == kEpiDswiglu) SEP_ASSERT(p.row_token != nullptr, "this epilogue needs pool_recv_token");
     if (a.epilogue == kEpiScatter) {
-      if (p.remote_out.enabled) SEP_ASSERT(p.row_src != nullptr, "remote scatter needs pool_src");
-      else SEP_ASSERT(p.scatter_local != nullptr, "local scatter needs a destination");
+      SEP_ASSERT(a.scatter_local.has_value(), "scatter needs a local destination");   // may be empty (a rank without tokens)
+      if (p.remote_out.enabled)
+        SEP_ASSERT(p.row_src != nullptr && p.row_k_slot != nullptr && p.num_topk > 0, "remote scatter needs pool_src, pool_k_slot and num_topk");
     }
     if (a.epilogue == kEpiDswiglu) {
       SEP_ASSERT(p.preact != nullptr && p.out0 != nullptr && p.out1 != nullptr, "dswiglu epilogue needs preact and both outputs");
@@ -721,6 +724,25 @@ class Runtime {
       p.tail.enabled = 1; p.tail.kind = a.tail_kind; p.tail.epoch = ++epochs_[a.tail_kind];
       p.tail.wait = a.tail_wait ? 1 : 0;
       p.tail.ctas_done = counters_ + (a.tail_kind == kKindGemmYTail ? 8 : 9);
+    }
+    // Output maps of the TMA-store epilogues: one box = 32 rows x one staging row.
+    auto out_map = [&](const at::Tensor& t, int64_t cols, int64_t rows, int64_t experts, uint32_t box_cols, CUtensorMapSwizzle sw) {
+      SEP_ASSERT(t.scalar_type() == at::kBFloat16 && t.stride(-1) == 1, "GEMM outputs must be bf16 with contiguous rows");
+      const int64_t ld = t.dim() >= 2 ? t.stride(-2) : cols;
+      SEP_ASSERT(ld % 8 == 0 && cols % 8 == 0, "GEMM output rows must be multiples of 16 bytes");
+      return make_tmap(t.data_ptr(), cols, rows, experts, ld, experts > 1 ? t.stride(0) : rows * ld, box_cols, 32, sw);
+    };
+    if (a.epilogue == kEpiStore) {
+      if (a.mode == kVarlenM) to0 = out_map(*a.out0, p.N, p.total_rows, 1, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+      else to0 = out_map(*a.out0, p.N, p.M_out, p.num_experts, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+      have_o0 = true;
+    } else if (a.epilogue == kEpiSwiglu) {
+      SEP_ASSERT(p.N % 16 == 0, "SwiGLU epilogue needs an output width that is a multiple of 16");
+      to0 = out_map(*a.out0, p.N / 2, p.total_rows, 1, 16, CU_TENSOR_MAP_SWIZZLE_32B); have_o0 = true;
+      if (a.out1.has_value()) { to1 = out_map(*a.out1, p.N, p.total_rows, 1, 32, CU_TENSOR_MAP_SWIZZLE_64B); have_o1 = true; }
+    } else if (a.epilogue == kEpiDswiglu) {
+      to0 = out_map(*a.out0, 2 * static_cast<int64_t>(p.N), p.total_rows, 1, 64, CU_TENSOR_MAP_SWIZZLE_128B); have_o0 = true;
+      to1 = out_map(*a.out1, p.N, p.total_rows, 1, 32, CU_TENSOR_MAP_SWIZZLE_64B); have_o1 = true;
     }
     int n_ctas = a.num_ctas > 0 ? a.num_ctas : num_sms();
     const int64_t total = static_cast<int64_t>(a.mode == kVarlenM ? p.num_m_tiles : p.num_experts * p.num_m_tiles) * p.num_n_tiles;
@@ -739,7 +761,9 @@ class Runtime {
       ppp = &pp;
     }
     if (ppp == nullptr) n_ctas = static_cast<int>(std::min<int64_t>(n_ctas, std::max<int64_t>(total, 1)));
-    ++launches_; launch_grouped_gemm(p, &ta, &tb, ppp, n_ctas, at::cuda::getCurrentCUDAStream());
+    ++launches_;
+    launch_grouped_gemm(p, &ta, &tb, have_o0 ? &to0 : nullptr, have_o1 ? &to1 : nullptr, ppp, n_ctas,
+                        at::cuda::getCurrentCUDAStream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
 
@@ -771,6 +795,15 @@ class Runtime {
   void tile_producer(const at::Tensor& count, const at::Tensor& target, double delay_us) {
     ++launches_; launch_tile_producer(count.data_ptr<int>(), target.data_ptr<int>(), count.numel(), static_cast<long long>(delay_us * 1000.0),
                          at::cuda::getCurrentCUDAStream());
+    SEP_CUDA_CHECK(cudaGetLastError());
+  }
+  void combine_reduce(const at::Tensor& out, const at::Tensor& rows, const at::Tensor& topk_idx, int num_experts) {
+    SEP_ASSERT(out.is_contiguous() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.size(1) % 8 == 0, "out must be contiguous [T, H] bf16");
+    SEP_ASSERT(topk_idx.scalar_type() == at::kLong && topk_idx.is_contiguous() && topk_idx.size(0) == out.size(0), "topk_idx must be contiguous [T, K] int64");
+    if (out.size(0) == 0 || num_ranks_ == 1) return;
+    SEP_ASSERT(rows.numel() == out.size(0) * topk_idx.size(1) * out.size(1), "rows must be [T * K, H]");
+    ++launches_; launch_combine_reduce(out.data_ptr(), rows.data_ptr(), reinterpret_cast<const long long*>(topk_idx.data_ptr<int64_t>()),
+                          out.size(0), out.size(1), topk_idx.size(1), num_experts, num_ranks_, rank_, at::cuda::getCurrentCUDAStream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
   at::Tensor pool_compress(const at::Tensor& pool, const at::Tensor& pool_recv_token, int64_t num_recv) {
@@ -976,6 +1009,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_epochs", &Runtime::set_epochs)
       .def("grouped_gemm", &Runtime::grouped_gemm)
       .def("tile_producer", &Runtime::tile_producer)
+      .def("combine_reduce", &Runtime::combine_reduce)
       .def("pool_compress", &Runtime::pool_compress)
       .def("pool_expand", &Runtime::pool_expand)
       .def("router", &Runtime::router);

@@ -125,14 +125,14 @@ def grouped_gemm_preact(pool: torch.Tensor, w1: torch.Tensor, tile_id_to_expert:
 
 
 def _scatter_common(a, *, o, pool_recv_token, tile_stripes_done, k_local_remaining, done_per_token, seq,
-                    remote_offsets, pool_src, tail_kind, tail_wait):
+                    remote_offsets, pool_src, pool_k_slot, num_topk, tail_kind, tail_wait):
     a.row_token = pool_recv_token
+    a.scatter_local = o
     if remote_offsets is not None:
         a.remote_out = [int(v) for v in remote_offsets]
-        a.row_src = pool_src
+        a.row_src, a.row_k_slot, a.num_topk = pool_src, pool_k_slot, int(num_topk)
         a.tail, a.tail_kind, a.tail_wait = True, tail_kind, tail_wait
     else:
-        a.scatter_local = o
         if tile_stripes_done is not None:
             a.tile_stripes_done = tile_stripes_done
             a.k_remaining = k_local_remaining
@@ -146,6 +146,7 @@ def streaming_moe_y(postact_a: torch.Tensor, w2: torch.Tensor, tile_id_to_expert
                     k_local_remaining: Optional[torch.Tensor] = None,
                     y_done_per_token: Optional[torch.Tensor] = None, combine_seq: int = 0,
                     remote_out_offsets: Optional[Sequence[int]] = None, pool_src: Optional[torch.Tensor] = None,
+                    pool_k_slot: Optional[torch.Tensor] = None, num_topk: int = 0,
                     tail_wait: bool = True, started_flag: bool = False,
                     tile_n: Optional[int] = None, num_sms: Optional[int] = None, buffer=None):
     """``y = postact @ w2[e]^T`` scaled by the slot's top-k weight and reduced
@@ -153,10 +154,14 @@ def streaming_moe_y(postact_a: torch.Tensor, w2: torch.Tensor, tile_id_to_expert
 
     * ``o[pool_recv_token[slot]]`` on this rank (then per-token completion stamps
       ``y_done_per_token[r] = combine_seq`` once all of r's local slots are in), or
-    * the SOURCE rank's output row over NVLink when ``remote_out_offsets`` names
+    * with ``remote_out_offsets`` (fused combine): rows whose source token lives on
+      this rank are red.added into ``o`` (here ``[T, H]``, indexed by source token);
+      rows of other ranks' tokens are STORED, one contiguous bf16 row per (token, k),
+      into that rank's ``[T * K, H]`` landing buffer over NVLink.  The triple names
       ``(record kind, epoch, word)`` of the record in which every rank published the
-      arena offset of its ``[T, H]`` accumulator (fused combine); the kernel then
-      ends with a cross-rank completion handshake.
+      arena offset of its landing buffer.  The kernel ends with a cross-rank
+      completion handshake; ``combine_reduce`` then folds the landed rows into ``o``
+      in fp32.
     """
     a = _args()
     N = w2.shape[1]
@@ -167,8 +172,8 @@ def streaming_moe_y(postact_a: torch.Tensor, w2: torch.Tensor, tile_id_to_expert
         a.started_flag = GATE_KERNEL_Y
     _scatter_common(a, o=o, pool_recv_token=pool_recv_token, tile_stripes_done=tile_n_stripes_done,
                     k_local_remaining=k_local_remaining, done_per_token=y_done_per_token, seq=combine_seq,
-                    remote_offsets=remote_out_offsets, pool_src=pool_src, tail_kind=KIND_GEMM_Y_TAIL,
-                    tail_wait=tail_wait)
+                    remote_offsets=remote_out_offsets, pool_src=pool_src, pool_k_slot=pool_k_slot, num_topk=num_topk,
+                    tail_kind=KIND_GEMM_Y_TAIL, tail_wait=tail_wait)
     if num_sms:
         a.num_ctas = num_sms
     _rt(buffer).grouped_gemm(a)
@@ -181,6 +186,7 @@ def streaming_moe_a_bwd(dL_dswiglu_in: torch.Tensor, w1: torch.Tensor, tile_id_t
                         bwd_k_local_remaining: Optional[torch.Tensor] = None,
                         bwd_a_done_per_token: Optional[torch.Tensor] = None, dispatch_seq: int = 0,
                         remote_out_offsets: Optional[Sequence[int]] = None, pool_src: Optional[torch.Tensor] = None,
+                        pool_k_slot: Optional[torch.Tensor] = None, num_topk: int = 0,
                         tail_wait: bool = True, started_flag: bool = False,
                         tile_n: Optional[int] = None, num_sms: Optional[int] = None, buffer=None):
     """``dpool = dL_dswiglu_in[TKp, 2I] @ w1[e]`` (NN GEMM, K = 2I) reduced into
@@ -196,8 +202,8 @@ def streaming_moe_a_bwd(dL_dswiglu_in: torch.Tensor, w1: torch.Tensor, tile_id_t
         a.started_flag = GATE_KERNEL_A_BWD
     _scatter_common(a, o=dL_dx_per_r, pool_recv_token=pool_recv_token, tile_stripes_done=tile_n_stripes_done,
                     k_local_remaining=bwd_k_local_remaining, done_per_token=bwd_a_done_per_token,
-                    seq=dispatch_seq, remote_offsets=remote_out_offsets, pool_src=pool_src,
-                    tail_kind=KIND_GEMM_A_BWD_TAIL, tail_wait=tail_wait)
+                    seq=dispatch_seq, remote_offsets=remote_out_offsets, pool_src=pool_src, pool_k_slot=pool_k_slot,
+                    num_topk=num_topk, tail_kind=KIND_GEMM_A_BWD_TAIL, tail_wait=tail_wait)
     if num_sms:
         a.num_ctas = num_sms
     _rt(buffer).grouped_gemm(a)
@@ -308,3 +314,10 @@ def router_topk(x: torch.Tensor, w_gate: torch.Tensor, top_k: int, num_ranks: in
     idx, w, in_rank, probs = _rt(buffer).router(x.contiguous(), w_gate.contiguous(), top_k, num_ranks,
                                                 renormalize, return_probs)
     return (idx, w, in_rank, probs) if return_probs else (idx, w, in_rank)
+
+
+def combine_reduce(out: torch.Tensor, landed_rows: torch.Tensor, topk_idx: torch.Tensor, num_experts: int, buffer=None):
+    """``out[t] += sum_k landed_rows[t * K + k]`` over the pairs owned by other ranks, in fp32
+    (second half of the fused combine; a no-op for a single rank)."""
+    _rt(buffer).combine_reduce(out, landed_rows, topk_idx.contiguous(), int(num_experts))
+    return out

@@ -16,8 +16,10 @@ default on):
               dispatch (+) GEMM-A/SwiGLU   one persistent kernel: push warps store this rank's
                                            token rows into the owners' pool slots over NVLink
                                            while tcgen05 warps consume 128-row tiles as they land
-              GEMM-Y (+) combine           epilogue scales by the top-k weight and red.adds bf16x2
-                                           straight into the SOURCE rank's output row
+              GEMM-Y (+) combine           epilogue scales by the top-k weight and sends every row to
+                                           the SOURCE rank: contiguous bf16 row stores over NVLink
+                                           into a per-(token, k) landing buffer (bf16x2 red.add for
+                                           rows of this rank's own tokens), then an fp32 reduce
     backward  dispatch_grads (+) GEMM-Y_bwd/dSwiGLU (+ dL/dweight returned to the source)
               GEMM-A_bwd (+) combine_grads (remote red.add into the source's dL/dx)
               dW2, dW1 grouped GEMMs (true-length varlen-K)
@@ -106,15 +108,18 @@ def moe_forward(ctx, streams, buffer, x, topk_idx, topk_weights, is_token_in_ran
     if fused:
         with torch.cuda.stream(comp):
             _nvtx_push(f"fwd_dispatch_{_NVTX_FWD}")
-            out = buffer.alloc_symmetric([T, H], torch.bfloat16, zero=True)
+            # rows that other ranks compute for this rank's tokens land here, one per (token, k)
+            K = topk_idx.shape[1]
+            landing = buffer.alloc_symmetric([T * K if buffer.group_size > 1 else 0, H], torch.bfloat16)
             _, handle, _ = buffer.dispatch(x, topk_idx, topk_weights, is_token_in_rank, num_experts,
                                            tile_m=cfg.tile_m, launch_push=False)
             st = handle._dispatch_out
-            rt.dispatch_set_aux(st, 0, out)
+            rt.dispatch_set_aux(st, 0, landing)
             _nvtx_pop()
         TKp = handle.TK_padded
         postact = torch.empty(TKp, I, dtype=x.dtype, device=x.device)
         preact = torch.empty(TKp, two_i, dtype=x.dtype, device=x.device) if level == 0 else None
+        out = torch.zeros(T, H, dtype=x.dtype, device=x.device)
         comp.wait_stream(caller)
         with torch.cuda.stream(comp):
             _nvtx_push(f"fwd_compute_{_NVTX_FWD}")
@@ -122,10 +127,13 @@ def moe_forward(ctx, streams, buffer, x, topk_idx, topk_weights, is_token_in_ran
             _nvtx_pop()
             _nvtx_push(f"fwd_combine_{_NVTX_FWD}")
             gg.streaming_moe_y(postact, w2c, handle.tile_id_to_expert, handle.pool_topk_weight,
-                               handle.pool_recv_token, remote_out_offsets=(KIND_DISPATCH, st.push_epoch, AUX0),
-                               pool_src=handle.pool_src, tail_wait=not buffer._emulated, tile_n=cfg.tile_n_y,
-                               num_sms=cfg.num_sms_y, buffer=buffer)
+                               handle.pool_recv_token, o=out, remote_out_offsets=(KIND_DISPATCH, st.push_epoch, AUX0),
+                               pool_src=handle.pool_src, pool_k_slot=handle.pool_k_slot, num_topk=K,
+                               tail_wait=not buffer._emulated, tile_n=cfg.tile_n_y, num_sms=cfg.num_sms_y, buffer=buffer)
             buffer._phase()
+            gg.combine_reduce(out, landing, st.topk_idx, num_experts, buffer=buffer)
+            buffer._phase()     # (emulated ranks) nobody reuses a landing buffer before every reduce is enqueued
+            del landing
             _nvtx_pop()
             saved_pool = _maybe_compress(buffer, handle, level)
     else:
@@ -251,11 +259,12 @@ def moe_backward(ctx, dL_dy):
 
     if fused:
         with torch.cuda.stream(comp):
-            dx = buffer.alloc_symmetric([T, H], torch.bfloat16, zero=True)
+            dx = torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
+            landing = buffer.alloc_symmetric([T * K if buffer.group_size > 1 else 0, H], torch.bfloat16)
             dwt = buffer.alloc_symmetric([T, K], torch.float32, zero=True)
             dl_do_pool, bwd_count, _ = buffer.dispatch_grads(handle, dL_dy, launch_push=False)
             g = handle._grads_state
-            rt.grads_set_aux(g, 0, dx)
+            rt.grads_set_aux(g, 0, landing)
             rt.grads_set_aux(g, 1, dwt)
             pool, preact = rebuild_inputs()
             ykw = dict(dL_dswiglu_in=dswiglu_in, postact_a_for_dW2=postact_dw2, dL_dweight=dl_dweight,
@@ -274,10 +283,14 @@ def moe_backward(ctx, dL_dy):
                 buffer._phase()
                 gg.streaming_moe_y_bwd(*yargs, push_flags=0, **ykw)
             gg.streaming_moe_a_bwd(dswiglu_in, sv.w1, handle.tile_id_to_expert, handle.pool_recv_token,
-                                   remote_out_offsets=(KIND_DISPATCH_GRADS, g.epoch, AUX0), pool_src=handle.pool_src,
+                                   dL_dx_per_r=dx, remote_out_offsets=(KIND_DISPATCH_GRADS, g.epoch, AUX0),
+                                   pool_src=handle.pool_src, pool_k_slot=handle.pool_k_slot, num_topk=K,
                                    tail_wait=not buffer._emulated, tile_n=cfg.tile_n_a_bwd,
                                    num_sms=cfg.num_sms_a_bwd, buffer=buffer)
             buffer._phase()
+            gg.combine_reduce(dx, landing, st.topk_idx, st.num_experts, buffer=buffer)
+            buffer._phase()
+            del landing
             _launch_dw(buffer, handle, cfg, dl_do_pool, postact_dw2, dswiglu_in, pool, dW1, dW2)
         dL_dx, dL_dw = dx, dwt
     else:
