@@ -65,6 +65,10 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
   if (p.phase_mask == 4) {
     // ---------------------------------------------------------------- materialise (own launch, any grid)
     const size_t gid = static_cast<size_t>(blockIdx.x) * blockDim.x + tid, gsz = static_cast<size_t>(gridDim.x) * blockDim.x;
+    // The synthesize launch before this one gave up (a peer never arrived): the base tables were
+    // never written, so there is nothing valid to materialise.
+    const int num_send = *reinterpret_cast<const volatile int*>(p.num_send);
+    if (num_send < 0) return;
     for (size_t i = gid; i < static_cast<size_t>(T) * K; i += gsz) {
       const int t = static_cast<int>(i / K);
       const long long e = p.topk_idx[i];
@@ -73,7 +77,9 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
         const int c = t / per;
         const int rk = p.pair_rank[i];
         slot = p.send_base[static_cast<size_t>(c) * E + e] + rk;
-        p.send_list[p.send_order_base[static_cast<size_t>(c) * E + e] + rk] = static_cast<int>(i);
+        const int pos = p.send_order_base[static_cast<size_t>(c) * E + e] + rk;
+        if (pos >= 0 && pos < num_send) p.send_list[pos] = static_cast<int>(i);
+        else report_failure(p.status, kStatusBadIndex, kKernelMetadata, 4, p.rank, static_cast<int>(i), num_send, pos);
       }
       p.pair_slot[i] = slot;
     }
@@ -171,7 +177,8 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
   }
   __syncthreads();
   if (!s_ok) {
-    if (tid == 0) {   // unblock the host poll with an error marker
+    if (tid == 0) {   // unblock the host poll with an error marker; the materialise launch must do nothing
+      *p.num_send = -1;
       p.host->total_tiles = -1;
       p.host->num_recv_tokens = -1;
       __threadfence_system();
@@ -648,48 +655,78 @@ void launch_combine_reduce(void* out, const void* rows, const long long* topk_id
 // (stream_ep/stream_moe/profile_pipeline.py:102-139).
 // =============================================================================================
 constexpr int kRouterMaxExpertsPerLane = 16;   // up to 512 experts
+constexpr int kRouterTokens = 64;              // tokens per CTA
+constexpr int kRouterKChunk = 32;              // hidden elements per shared-memory step
 
-__global__ void router_kernel(const RouterParams p) {
+// One CTA routes 64 tokens: a register-tiled fp32 GEMM (4 tokens x 4 experts per thread, operands staged
+// k-major in shared memory) produces the logits of 64 experts at a time into shared memory; then each
+// warp finishes 8 tokens: softmax over all experts, top-k by repeated arg-max, renormalise, rank bitmap.
+__global__ void __launch_bounds__(256) router_kernel(const RouterParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int warps_per_block = blockDim.x >> 5;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* xs = reinterpret_cast<float*>(smem_raw);                 // [kRouterKChunk][64 tokens]
+  float* ws = xs + kRouterKChunk * kRouterTokens;                 // [kRouterKChunk][64 experts]
+  float* logits = ws + kRouterKChunk * 64;                        // [64 tokens][E_pad]
   const int E = p.num_experts, H = p.hidden, K = p.num_topk;
+  const int e_pad = (E + 63) / 64 * 64 + 1;                       // +1: rows start in different banks
   const int e_local = E / p.num_ranks;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int ty = tid >> 4, tx = tid & 15;                          // 16 x 16 threads, 4 x 4 outputs each
   const __nv_bfloat16* xg = static_cast<const __nv_bfloat16*>(p.x);
   const __nv_bfloat16* wg = static_cast<const __nv_bfloat16*>(p.w_gate);
-  __nv_bfloat16* s_x = reinterpret_cast<__nv_bfloat16*>(smem_raw) + static_cast<size_t>(warp) * H;
+  const int t0 = blockIdx.x * kRouterTokens;
+  const int ld_row = tid & 63, ld_kc = (tid >> 6) * 8;             // loader: row 0..63, 8 consecutive k
 
-  for (int t = blockIdx.x * warps_per_block + warp; t < p.num_tokens; t += gridDim.x * warps_per_block) {
-    for (int v = lane; v < H / 8; v += 32)
-      reinterpret_cast<uint4*>(s_x)[v] = ld_nc_v4(xg + static_cast<size_t>(t) * H + v * 8);
-    __syncwarp();
-    float logit[kRouterMaxExpertsPerLane];
+  for (int e0 = 0; e0 < E; e0 += 64) {
+    float acc[4][4];
 #pragma unroll
-    for (int j = 0; j < kRouterMaxExpertsPerLane; ++j) logit[j] = -INFINITY;
-    // expert e is owned by lane e % 32; every lane reduces its own rows of w_gate
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < H; k0 += kRouterKChunk) {
+      uint4 xv = make_uint4(0, 0, 0, 0), wv = make_uint4(0, 0, 0, 0);
+      const int kk = k0 + ld_kc;
+      if (t0 + ld_row < p.num_tokens && kk < H) xv = ld_nc_v4(xg + static_cast<size_t>(t0 + ld_row) * H + kk);
+      if (e0 + ld_row < E && kk < H) wv = __ldg(reinterpret_cast<const uint4*>(wg + static_cast<size_t>(e0 + ld_row) * H + kk));
+      __syncthreads();   // previous step's tiles are no longer read
+      const uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w}, wu[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 a = unpack_bf16x2(xu[j]), b = unpack_bf16x2(wu[j]);
+        xs[(ld_kc + 2 * j) * kRouterTokens + ld_row] = a.x;
+        xs[(ld_kc + 2 * j + 1) * kRouterTokens + ld_row] = a.y;
+        ws[(ld_kc + 2 * j) * 64 + ld_row] = b.x;
+        ws[(ld_kc + 2 * j + 1) * 64 + ld_row] = b.y;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < kRouterKChunk; ++k) {
+        const float4 a = *reinterpret_cast<const float4*>(xs + k * kRouterTokens + ty * 4);
+        const float4 b = *reinterpret_cast<const float4*>(ws + k * 64 + tx * 4);
+        const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) logits[(ty * 4 + i) * e_pad + e0 + tx * 4 + j] = acc[i][j];
+  }
+  __syncthreads();
+
+  for (int tt = warp; tt < kRouterTokens; tt += 8) {
+    const int t = t0 + tt;
+    if (t >= p.num_tokens) break;
+    float logit[kRouterMaxExpertsPerLane];
+    float mx = -INFINITY;
 #pragma unroll
     for (int j = 0; j < kRouterMaxExpertsPerLane; ++j) {
       const int e = j * 32 + lane;
-      if (e < E) {
-        float acc = 0.f;
-        const uint4* wrow = reinterpret_cast<const uint4*>(wg + static_cast<size_t>(e) * H);
-        for (int v = 0; v < H / 8; ++v) {
-          const uint4 q = __ldg(wrow + v);
-          const uint4 xv = reinterpret_cast<const uint4*>(s_x)[v];
-          const float2 a0 = unpack_bf16x2(q.x), b0 = unpack_bf16x2(xv.x);
-          const float2 a1 = unpack_bf16x2(q.y), b1 = unpack_bf16x2(xv.y);
-          const float2 a2 = unpack_bf16x2(q.z), b2 = unpack_bf16x2(xv.z);
-          const float2 a3 = unpack_bf16x2(q.w), b3 = unpack_bf16x2(xv.w);
-          acc += a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y +
-                 a2.x * b2.x + a2.y * b2.y + a3.x * b3.x + a3.y * b3.y;
-        }
-        logit[j] = acc;
-      }
+      logit[j] = (e < E) ? logits[tt * e_pad + e] : -INFINITY;
+      mx = fmaxf(mx, logit[j]);
     }
-    // softmax over all experts
-    float mx = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < kRouterMaxExpertsPerLane; ++j) mx = fmaxf(mx, logit[j]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     float sum = 0.f;
@@ -708,9 +745,9 @@ __global__ void router_kernel(const RouterParams p) {
       const int e = j * 32 + lane;
       if (p.probs != nullptr && e < E) p.probs[static_cast<size_t>(t) * E + e] = logit[j];
     }
-    // top-k by repeated arg-max (ties -> lowest expert id, as torch.topk on distinct values)
-    float wsum = 0.f;
-    float my_w = 0.f; int my_e = -1;
+    // top-k by repeated arg-max (ties -> lowest expert id)
+    float wsum = 0.f, my_w = 0.f;
+    int my_e = -1;
     unsigned rank_mask = 0;
     for (int k = 0; k < K; ++k) {
       float best = -1.f; int best_e = 0x7fffffff;
@@ -738,17 +775,16 @@ __global__ void router_kernel(const RouterParams p) {
     }
     if (lane < p.num_ranks && p.is_token_in_rank != nullptr)
       p.is_token_in_rank[static_cast<size_t>(t) * p.num_ranks + lane] = (rank_mask >> lane) & 1u;
-    __syncwarp();
   }
 }
 
 void launch_router(const RouterParams& p, cudaStream_t stream) {
-  const int warps = 4;
-  const size_t smem = static_cast<size_t>(warps) * p.hidden * 2;
-  const int grid = min((p.num_tokens + warps - 1) / warps, 148 * 4);
+  const int e_pad = (p.num_experts + 63) / 64 * 64 + 1;
+  const size_t smem = sizeof(float) * (kRouterKChunk * kRouterTokens + kRouterKChunk * 64 + static_cast<size_t>(kRouterTokens) * e_pad);
+  const int grid = (p.num_tokens + kRouterTokens - 1) / kRouterTokens;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  router_kernel<<<grid, warps * 32, smem, stream>>>(p);
+  router_kernel<<<grid, 256, smem, stream>>>(p);
 }
 
 }  // namespace sep

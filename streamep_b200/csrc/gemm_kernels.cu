@@ -401,25 +401,32 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           uint32_t o_in[32], o_pw[16];
           if (tok >= 0) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {       // 8 output columns per step
-              const uint4 p0 = pq[q * 2], p1 = pq[q * 2 + 1];
-              const uint32_t pv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-              float post[8];
+            for (int q = 0; q < 4; ++q) {       // 8 output columns per step; N is a multiple of 8
+              if (n + q * 8 < p.N) {
+                const uint4 p0 = pq[q * 2], p1 = pq[q * 2 + 1];
+                const uint32_t pv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+                float post[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const bool in = (n + q * 8 + i) < p.N;
-                const float2 gu = in ? unpack_bf16x2(pv[i]) : make_float2(0.f, 0.f);
-                const float g = __uint_as_float(r[q * 8 + i]);
-                const float sig = fast_sigmoid(gu.x);
-                const float silu = gu.x * sig;
-                post[i] = silu * gu.y;
-                dw_acc += in ? post[i] * g : 0.f;
-                const float dgate = w * g * gu.y * sig * (1.f + gu.x * (1.f - sig));
-                const float dup = w * g * silu;
-                o_in[q * 8 + i] = pack_bf16x2(dgate, dup);
+                for (int i = 0; i < 8; ++i) {
+                  const float2 gu = unpack_bf16x2(pv[i]);          // (gate, up)
+                  const float g = __uint_as_float(r[q * 8 + i]);
+                  const float sig = fast_sigmoid(gu.x);
+                  const float silu = gu.x * sig;
+                  post[i] = silu * gu.y;
+                  dw_acc = fmaf(post[i], g, dw_acc);
+                  const float wg = w * g;
+                  // d silu / d gate = sig + silu * (1 - sig)
+                  const float dsilu = sig + fmaf(-sig, silu, silu);
+                  o_in[q * 8 + i] = pack_bf16x2(wg * gu.y * dsilu, wg * silu);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o_pw[q * 4 + i] = pack_bf16x2(w * post[2 * i], w * post[2 * i + 1]);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o_in[q * 8 + i] = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o_pw[q * 4 + i] = 0;
               }
-#pragma unroll
-              for (int i = 0; i < 4; ++i) o_pw[q * 4 + i] = pack_bf16x2(w * post[2 * i], w * post[2 * i + 1]);
             }
           } else {
 #pragma unroll

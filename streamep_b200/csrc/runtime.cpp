@@ -791,6 +791,40 @@ class Runtime {
     SEP_CUDA_CHECK(cudaGetLastError());
   }
 
+  // ---- whole fused forward after the metadata launch, in one native call ----------------------------------
+  // The host must read the receive sizes before it can size the pool, so the GPU has nothing queued while
+  // the host works between that read and the first GEMM launch.  Doing every step of that stretch here
+  // (allocation, fill, three launches) instead of ~25 Python-level calls keeps the idle gap short.
+  // Returns {out, postact, preact (may be undefined)}.
+  std::vector<at::Tensor> fused_forward(const std::shared_ptr<DispatchState>& st, const at::Tensor& w1, const at::Tensor& w2,
+                                        const at::Tensor& landing, bool store_preact, int tile_n_a, int tile_n_y,
+                                        int num_sms_a, int num_sms_y) {
+    dispatch_allocate(st);
+    dispatch_set_aux(st, 0, landing);
+    const int64_t TKp = static_cast<int64_t>(st->total_tiles) * st->tile_m, I = w2.size(2), H = w2.size(1);
+    auto opts = st->x.options();
+    at::Tensor postact = at::empty({TKp, I}, opts);
+    at::Tensor preact = store_preact ? at::empty({TKp, 2 * I}, opts) : at::Tensor();
+    at::Tensor out = at::zeros({static_cast<int64_t>(st->num_tokens), H}, opts);
+    GemmArgs a;
+    a.mode = kVarlenM; a.epilogue = kEpiSwiglu; a.block_n = tile_n_a; a.num_ctas = num_sms_a;
+    a.a = st->pool; a.b = w1; a.tile_id_to_expert = st->tile_id_to_expert;
+    a.out0 = postact; if (store_preact) a.out1 = preact;
+    a.arrival_count = st->pool_arrival_count; a.arrival_target = st->pool_arrival_target;
+    a.fused_push = st; a.push_flags = 3;
+    grouped_gemm(a);
+    GemmArgs y;
+    y.mode = kVarlenM; y.epilogue = kEpiScatter; y.block_n = tile_n_y; y.num_ctas = num_sms_y;
+    y.a = postact; y.b = w2; y.tile_id_to_expert = st->tile_id_to_expert;
+    y.row_weight = st->pool_topk_weight; y.row_token = st->pool_recv_token; y.scatter_local = out;
+    y.remote_out = {kKindDispatch, st->push_epoch, 10};
+    y.row_src = st->pool_src; y.row_k_slot = st->pool_k_slot; y.num_topk = st->num_topk;
+    y.tail = true; y.tail_kind = kKindGemmYTail; y.tail_wait = true;
+    grouped_gemm(y);
+    combine_reduce(out, landing, st->topk_idx, st->num_experts);
+    return {out, postact, preact};
+  }
+
   // ---- small ops ---------------------------------------------------------------------------------------
   void tile_producer(const at::Tensor& count, const at::Tensor& target, double delay_us) {
     ++launches_; launch_tile_producer(count.data_ptr<int>(), target.data_ptr<int>(), count.numel(), static_cast<long long>(delay_us * 1000.0),
@@ -1008,6 +1042,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("get_epochs", &Runtime::get_epochs)
       .def("set_epochs", &Runtime::set_epochs)
       .def("grouped_gemm", &Runtime::grouped_gemm)
+      .def("fused_forward", &Runtime::fused_forward)
       .def("tile_producer", &Runtime::tile_producer)
       .def("combine_reduce", &Runtime::combine_reduce)
       .def("pool_compress", &Runtime::pool_compress)

@@ -105,7 +105,29 @@ def moe_forward(ctx, streams, buffer, x, topk_idx, topk_weights, is_token_in_ran
 
     comm.wait_stream(caller)
     comp.wait_stream(caller)
-    if fused:
+    if fused and not buffer._emulated:
+        # Production path: everything after the metadata launch happens in one native call (see
+        # Runtime::fused_forward) so that the GPU idles as briefly as possible after the host read.
+        with torch.cuda.stream(comp):
+            _nvtx_push(f"fwd_fused_{_NVTX_FWD}")
+            K = topk_idx.shape[1]
+            landing = buffer.alloc_symmetric([T * K if buffer.group_size > 1 else 0, H], torch.bfloat16)
+            st, seq = buffer._dispatch_begin(x, topk_idx, topk_weights, num_experts, cfg.tile_m, None)
+            rt.dispatch_metadata(st, 3)
+            try:
+                out, postact, preact = rt.fused_forward(st, w1c, w2c, landing, level == 0, cfg.tile_n_a, cfg.tile_n_y,
+                                                        cfg.num_sms_a or 0, cfg.num_sms_y or 0)
+            except RuntimeError as e:
+                if "timed out" in str(e) or "metadata failed" in str(e):
+                    from ..errors import StreamEPTimeout
+                    raise StreamEPTimeout(str(e)) from None
+                raise
+            handle = buffer._make_handle(st, is_token_in_rank, seq, cfg.tile_m)
+            TKp = handle.TK_padded
+            del landing
+            saved_pool = _maybe_compress(buffer, handle, level)
+            _nvtx_pop()
+    elif fused:
         with torch.cuda.stream(comp):
             _nvtx_push(f"fwd_dispatch_{_NVTX_FWD}")
             # rows that other ranks compute for this rank's tokens land here, one per (token, k)

@@ -1,0 +1,1 @@
+"""Host utilities: NVLink check, failure detection, clock sampling, timing."""
