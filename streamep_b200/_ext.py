@@ -74,7 +74,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             name=_NAME,
             sources=_sources(),
             extra_cflags=["-O3", "-std=c++17"],
-            extra_cuda_cflags=NVCC_FLAGS,
+            extra_cuda_cflags=NVCC_FLAGS + os.environ.get("STREAMEP_EXTRA_NVCC_FLAGS", "").split(),
             extra_ldflags=["-l:libstdc++.so.6"],
             build_directory=str(_BUILD_DIR),
             verbose=verbose,

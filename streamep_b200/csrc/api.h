@@ -286,6 +286,8 @@ struct GemmParams {
   int rank;
   StatusBlock* status;
   unsigned long long wait_budget_ns;
+  int dbg_flags;                 // experiment switches of -DSEP_EPI_TIMING builds
+  long long* dbg_cycles;         // optional [num_ctas, 8]: epilogue phase cycle counters (builds with -DSEP_EPI_TIMING)
 };
 
 // tmap_a / tmap_b: 128-byte CUtensorMap blobs (3-D, bf16, 128-byte swizzle) built by the host.

@@ -28,7 +28,8 @@ constexpr int BM = 128;          // rows per tile == pool tile_m
 constexpr int BK = 64;           // bf16 elements per k-block: one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kGemmWarps = 10;   // 0: TMA producer, 1: MMA issuer + TMEM owner, 2..9: epilogue
-constexpr int kPushWarps = 6;    // extra warps of the fused variant
+// extra warps of the fused variants; the dSwiGLU epilogue keeps two preact segments in registers, so it gets fewer
+constexpr int push_warps(int epi) { return epi == kEpiDswiglu ? 4 : 6; }
 constexpr int kEpiThreads = 256; // two threads per accumulator row: each takes half of the tile's columns
 
 template <int BN> struct GemmCfg {
@@ -87,7 +88,7 @@ __device__ __forceinline__ int atom_add_acq_rel_gpu(int* p, int v) {
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 template <int BN, bool A_MN, bool B_MN, int EPI, bool PUSH>
-__global__ void __launch_bounds__((kGemmWarps + (PUSH ? kPushWarps : 0)) * 32, 1)
+__global__ void __launch_bounds__((kGemmWarps + (PUSH ? push_warps(EPI) : 0)) * 32, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_o0, const __grid_constant__ CUtensorMap tmap_o1,
                     const GemmParams p, const PushParams pp) {
@@ -239,6 +240,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                      : umma_smem_desc(a_addr + j * (UMMA_K * 2), 16, 1024);
             const uint64_t db = B_MN ? umma_smem_desc(b_addr + j * (UMMA_K * 128), BK * 128, 1024)
                                      : umma_smem_desc(b_addr + j * (UMMA_K * 2), 16, 1024);
+#ifdef SEP_EPI_TIMING
+            if (!(p.dbg_flags & 16))
+#endif
             umma_bf16_ss(tmem_d, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);                       // frees the smem stage when the MMAs retire
@@ -262,32 +266,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     constexpr int kChunksPerHalf = BN / 64;
     const uint32_t stg = smem_u32(epi_stage + (warp - 2) * Cfg::kEpiStageBytes);
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
+#ifdef SEP_EPI_TIMING
+    long long dbg_t[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define SEP_T(i, expr) { const long long c0__ = clock64(); expr; dbg_t[i] += clock64() - c0__; }
+    const long long dbg_start = clock64();
+#else
+#define SEP_T(i, expr) { expr; }
+#endif
     for (int lin = blockIdx.x; lin < total_tiles; lin += gridDim.x) {
       const TileCoord t = decode_tile(p, lin);
       const bool empty = (t.k_blocks == 0);
-      if (EPI == kEpiDswiglu) {
-        // While the tensor cores still work on this tile, pull this thread's segment of preact towards L2.
-        const long long prow = static_cast<long long>(t.row0) + row;
-        const int pn = t.n_tile * BN + half * (BN / 2);
-        const char* pre = reinterpret_cast<const char*>(static_cast<const __nv_bfloat16*>(p.preact) + prow * p.ld_preact + 2 * pn);
-#pragma unroll
-        for (int j = 0; j < BN / 64; ++j)
-          if (pn + j * 32 < p.N) prefetch_l2(pre + j * 128);
-      }
-      if (!empty && ok) {
-        if (!mbar_wait(&tmem_full[acc], acc_phase, budget, p.status)) {
-          report_failure(p.status, kStatusTimeoutPipeline, kKernelGemm, 2, p.rank, lin, acc, 0);
-          ok = false;
-        }
-        tc_fence_after_sync();
-      }
-      if (!ok) break;
-      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#ifdef SEP_EPI_TIMING
+      const long long dbg_tile0 = clock64();
+#endif
+      // Everything that does not need the accumulator is fetched while the tensor cores still work on this tile.
       const int n0 = t.n_tile * BN;
-      // first output row of this warp (TMA y coordinate) and this thread's global row
-      const int warp_row0 = (p.mode == kVarlenM ? t.row0 : t.m_tile * BM) + quarter * 32;
+      const int warp_row0 = (p.mode == kVarlenM ? t.row0 : t.m_tile * BM) + quarter * 32;   // TMA y coordinate
       const int zc = (p.mode == kVarlenK) ? t.expert : 0;
       const long long grow = static_cast<long long>(p.mode == kVarlenM ? t.row0 : t.m_tile * BM) + row;
+      const int c_begin = half * kChunksPerHalf;
       int tok = 0; float w = 1.f;
       if (EPI == kEpiScatter || EPI == kEpiDswiglu) {
         tok = p.row_token[grow];
@@ -307,28 +304,75 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           dst_row = static_cast<char*>(p.scatter_local) + static_cast<long long>(tok) * p.N * 2; op = 1;
         }
       }
+      // dSwiGLU reads preact[row, 2n .. 2n+64) per chunk.  A thread-per-row read would touch 32 different lines
+      // per instruction, which the load/store unit handles one line at a time; instead 8 lanes fetch one
+      // row's 128 bytes (4 full lines per instruction) and the rows are handed to their threads through the
+      // staging tile.  pqc = the next chunk in that fetch layout, pq = this thread's row segment.
+      uint4 pq[8], pqc[8];
+      const char* pre_base = nullptr;
+      if (EPI == kEpiDswiglu) {
+        pre_base = reinterpret_cast<const char*>(static_cast<const __nv_bfloat16*>(p.preact) +
+                                                 static_cast<long long>(warp_row0 + (lane >> 3)) * p.ld_preact) + (lane & 7) * 16;
+        const int nf = n0 + c_begin * 32;
+        if (nf < p.N) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            pqc[i] = (2 * nf + (lane & 7) * 8 < 2 * p.N)
+                         ? ld_nc_v4(pre_base + static_cast<long long>(i) * 4 * p.ld_preact * 2 + static_cast<long long>(nf) * 4)
+                         : make_uint4(0, 0, 0, 0);
+        }
+      }
+#ifdef SEP_EPI_TIMING
+      dbg_t[0] += clock64() - dbg_tile0;                 // pre-accumulator bookkeeping
+      const long long dbg_w0 = clock64();
+#endif
+      if (!empty && ok) {
+        if (!mbar_wait(&tmem_full[acc], acc_phase, budget, p.status)) {
+          report_failure(p.status, kStatusTimeoutPipeline, kKernelGemm, 2, p.rank, lin, acc, 0);
+          ok = false;
+        }
+        tc_fence_after_sync();
+      }
+      if (!ok) break;
+#ifdef SEP_EPI_TIMING
+      dbg_t[1] += clock64() - dbg_w0;                    // waiting for the accumulator
+      const long long dbg_e0 = clock64();
+#endif
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
       float dw_acc = 0.f;
 #pragma unroll 1
-      for (int c = half * kChunksPerHalf; c < (half + 1) * kChunksPerHalf; ++c) {
+      for (int c = c_begin; c < c_begin + kChunksPerHalf; ++c) {
         const int n = n0 + c * 32;
         if (n >= p.N) break;
-        uint4 pq[8];
         if (EPI == kEpiDswiglu) {
-          // issue the whole row segment of preact before touching the accumulator: 8 loads in flight
-          if (tok >= 0) {
-            const char* pre = reinterpret_cast<const char*>(static_cast<const __nv_bfloat16*>(p.preact) + grow * p.ld_preact + 2 * n);
+          // hand this chunk's preact rows to their threads, then request the next chunk (software pipeline)
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (n + j * 4 < p.N) pq[j] = ld_nc_v4(pre + j * 16);
+          for (int i = 0; i < 8; ++i)
+            st_shared_v4(stg + stage_off<128>(i * 4 + (lane >> 3), lane & 7), pqc[i].x, pqc[i].y, pqc[i].z, pqc[i].w);
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) pq[j] = ld_shared_v4(stg + stage_off<128>(lane, j));
+          __syncwarp();
+          const int nn = n + 32;
+#ifdef SEP_EPI_TIMING
+          if (!(p.dbg_flags & 64))
+#endif
+          if (c + 1 < c_begin + kChunksPerHalf && nn < p.N) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              pqc[i] = (2 * nn + (lane & 7) * 8 < 2 * p.N)
+                           ? ld_nc_v4(pre_base + static_cast<long long>(i) * 4 * p.ld_preact * 2 + static_cast<long long>(nn) * 4)
+                           : make_uint4(0, 0, 0, 0);
           }
         }
-        uint32_t r[32];
-        if (!empty) {
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-        } else {
+        uint32_t r[EPI == kEpiDswiglu ? 1 : 32];   // the dSwiGLU epilogue reads the accumulator 16 columns at a time
+        if (EPI != kEpiDswiglu) {
+          if (!empty) {
+            SEP_T(2, tmem_ld_32x32(taddr + c * 32, reinterpret_cast<uint32_t(&)[32]>(r)); tmem_ld_wait();)
+          } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0;
+            for (int i = 0; i < (EPI == kEpiDswiglu ? 1 : 32); ++i) r[i] = 0;
+          }
         }
         if (EPI == kEpiStore) {
 #pragma unroll
@@ -398,59 +442,108 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
           __syncwarp();
         } else {   // kEpiDswiglu: r = g[row, n..n+32) = dL/d(postact) before the topk weight
-          uint32_t o_in[32], o_pw[16];
-          if (tok >= 0) {
+          uint32_t o_pw[16];
+          unsigned char* sb = epi_stage + (warp - 2) * Cfg::kEpiStageBytes;
+#ifdef SEP_EPI_TIMING
+          const long long dbg_c0 = clock64();
+#endif
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {       // 8 output columns per step; N is a multiple of 8
-              if (n + q * 8 < p.N) {
-                const uint4 p0 = pq[q * 2], p1 = pq[q * 2 + 1];
-                const uint32_t pv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-                float post[8];
+          uint32_t rh[16];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const float2 gu = unpack_bf16x2(pv[i]);          // (gate, up)
-                  const float g = __uint_as_float(r[q * 8 + i]);
-                  const float sig = fast_sigmoid(gu.x);
-                  const float silu = gu.x * sig;
-                  post[i] = silu * gu.y;
-                  dw_acc = fmaf(post[i], g, dw_acc);
-                  const float wg = w * g;
-                  // d silu / d gate = sig + silu * (1 - sig)
-                  const float dsilu = sig + fmaf(-sig, silu, silu);
-                  o_in[q * 8 + i] = pack_bf16x2(wg * gu.y * dsilu, wg * silu);
-                }
+          for (int q = 0; q < 4; ++q) {       // 8 output columns per step; N is a multiple of 8
+            if ((q & 1) == 0) {
+              if (!empty) { tmem_ld_32x16(taddr + c * 32 + q * 8, rh); tmem_ld_wait(); }
+              else {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) o_pw[q * 4 + i] = pack_bf16x2(w * post[2 * i], w * post[2 * i + 1]);
-              } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) o_in[q * 8 + i] = 0;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) o_pw[q * 4 + i] = 0;
+                for (int i = 0; i < 16; ++i) rh[i] = 0;
               }
             }
-          } else {
+            uint32_t o_in[8];
+#ifdef SEP_EPI_TIMING
+            if ((p.dbg_flags & 32)) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o_in[i] = 0;
+              for (int i = 0; i < 8; ++i) o_in[i] = 0;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o_pw[i] = 0;
+              for (int i = 0; i < 4; ++i) o_pw[q * 4 + i] = 0;
+            } else
+#endif
+            if (tok >= 0 && n + q * 8 < p.N) {
+              const uint4 p0 = pq[q * 2], p1 = pq[q * 2 + 1];
+              const uint32_t pv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+              float post[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+#ifdef SEP_EPI_TIMING
+                const float2 gu = (p.dbg_flags & 4) ? make_float2(0.5f, 0.25f) : unpack_bf16x2(pv[i]);
+                const float g = (p.dbg_flags & 8) ? 1.5f : __uint_as_float(rh[(q & 1) * 8 + i]);
+                const float sig = (p.dbg_flags & 1) ? gu.x * 0.25f + 0.5f : fast_sigmoid(gu.x);
+#else
+                const float2 gu = unpack_bf16x2(pv[i]);          // (gate, up)
+                const float g = __uint_as_float(rh[(q & 1) * 8 + i]);
+                const float sig = fast_sigmoid(gu.x);
+#endif
+                const float silu = gu.x * sig;
+                post[i] = silu * gu.y;
+                dw_acc = fmaf(post[i], g, dw_acc);
+                const float wg = w * g;
+                const float dsilu = sig + fmaf(-sig, silu, silu);   // d silu / d gate = sig + silu * (1 - sig)
+                o_in[i] = pack_bf16x2(wg * gu.y * dsilu, wg * silu);
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i) o_pw[q * 4 + i] = pack_bf16x2(w * post[2 * i], w * post[2 * i + 1]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o_in[i] = 0;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) o_pw[q * 4 + i] = 0;
+            }
+#ifdef SEP_EPI_TIMING
+            if (!(p.dbg_flags & 2) || o_in[0] == 0x12345u) {
+#endif
+            st_shared_v4(stg + stage_off<128>(lane, 2 * q), o_in[0], o_in[1], o_in[2], o_in[3]);
+            st_shared_v4(stg + stage_off<128>(lane, 2 * q + 1), o_in[4], o_in[5], o_in[6], o_in[7]);
+#ifdef SEP_EPI_TIMING
+            }
+#endif
           }
-          unsigned char* sb = epi_stage + (warp - 2) * Cfg::kEpiStageBytes;
-#pragma unroll
-          for (int q = 0; q < 8; ++q)
-            st_shared_v4(stg + stage_off<128>(lane, q), o_in[q * 4 + 0], o_in[q * 4 + 1], o_in[q * 4 + 2], o_in[q * 4 + 3]);
-          fence_proxy_async_smem();
+#ifdef SEP_EPI_TIMING
+          dbg_t[0] += clock64() - dbg_c0;                 // (reused slot) compute + st.shared
+#endif
+          // Both outputs leave through the staging tile with plain coalesced stores (8 resp. 4 lanes per
+          // 128- resp. 64-byte row segment).  No proxy fence here on purpose: a fence would wait for the
+          // preact loads of the next chunk that are still in flight.
           __syncwarp();
-          if (lane == 0) { tma_store_3d(&tmap_o0, sb, 2 * n, warp_row0, 0); bulk_commit(); bulk_wait_read(); }
+          {
+            char* din_base = reinterpret_cast<char*>(static_cast<__nv_bfloat16*>(p.out0) + static_cast<long long>(warp_row0) * p.ld0 + 2 * n);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + (lane >> 3), piece = lane & 7;
+              const uint4 v = ld_shared_v4(stg + stage_off<128>(rr, piece));
+              if (2 * n + piece * 8 < 2 * p.N)
+                st_global_v4(din_base + static_cast<long long>(rr) * p.ld0 * 2 + piece * 16, v.x, v.y, v.z, v.w);
+            }
+          }
           __syncwarp();
 #pragma unroll
           for (int q = 0; q < 4; ++q)
             st_shared_v4(stg + stage_off<64>(lane, q), o_pw[q * 4 + 0], o_pw[q * 4 + 1], o_pw[q * 4 + 2], o_pw[q * 4 + 3]);
-          fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) { tma_store_3d(&tmap_o1, sb, n, warp_row0, 0); bulk_commit(); bulk_wait_read(); }
+          {
+            char* pw_base = reinterpret_cast<char*>(static_cast<__nv_bfloat16*>(p.out1) + static_cast<long long>(warp_row0) * p.ld1 + n);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int rr = i * 8 + (lane >> 2), piece = lane & 3;
+              const uint4 v = ld_shared_v4(stg + stage_off<64>(rr, piece));
+              if (n + piece * 8 < p.N)
+                st_global_v4(pw_base + static_cast<long long>(rr) * p.ld1 * 2 + piece * 16, v.x, v.y, v.z, v.w);
+            }
+          }
           __syncwarp();
         }
       }
+#ifdef SEP_EPI_TIMING
+      dbg_t[3] += clock64() - dbg_e0;                    // whole column loop of this tile
+#endif
       if (!empty) {
         tc_fence_before_sync();
         mbar_arrive(&tmem_empty[acc]);
@@ -481,6 +574,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
     }
     if (lane == 0) bulk_wait_all();     // every bulk store this warp issued has been performed
+#ifdef SEP_EPI_TIMING
+    if (p.dbg_cycles != nullptr && warp == 2 && lane == 0) {
+      dbg_t[7] = clock64() - dbg_start;
+      for (int i = 0; i < 8; ++i) p.dbg_cycles[blockIdx.x * 8 + i] = dbg_t[i];
+    }
+#endif
     if (p.tail.enabled) __threadfence_system();
   } else if (PUSH) {
     // ------------------------------------------------------------------ dispatch push warps
@@ -492,7 +591,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (rec == nullptr) s_push_ok = 0;
         else resolve_push_targets(s_tg, lane, pp.peer_base[lane], rec);
       }
-      asm volatile("bar.sync 2, %0;" :: "r"(kPushWarps * 32) : "memory");
+      asm volatile("bar.sync 2, %0;" :: "r"(push_warps(EPI) * 32) : "memory");
       if (s_push_ok) {
         const int ppc = pp.pairs_per_chunk;
         const int num_send = *pp.num_send;
@@ -553,7 +652,7 @@ static void launch_instance(const GemmParams& p, const CUtensorMap& ta, const CU
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     configured = true;
   }
-  const int threads = (kGemmWarps + (PUSH ? kPushWarps : 0)) * 32;
+  const int threads = (kGemmWarps + (PUSH ? push_warps(EPI) : 0)) * 32;
   kernel<<<num_ctas, threads, smem, stream>>>(ta, tb, to0, to1, p, pp);
 }
 

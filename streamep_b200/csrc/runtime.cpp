@@ -184,6 +184,8 @@ struct GemmArgs {
   std::optional<at::Tensor> out0, out1, preact, row_weight, row_token, dl_dweight;
   std::optional<at::Tensor> scatter_local, row_src, row_k_slot;
   std::optional<at::Tensor> tile_stripes_done, k_remaining, done_per_token;
+  int dbg_flags = 0;
+  std::optional<at::Tensor> dbg_cycles;             // int64 [num_ctas, 8], only filled by -DSEP_EPI_TIMING builds
   // remote scatter / remote dL/dweight return: (record kind, epoch, word) naming the buffer on every rank
   std::vector<int> remote_out;
   std::vector<int> remote_dw;
@@ -699,6 +701,8 @@ class Runtime {
     if (a.k_remaining.has_value()) p.k_remaining = a.k_remaining->data_ptr<int>();
     if (a.done_per_token.has_value()) p.done_per_token = reinterpret_cast<long long*>(a.done_per_token->data_ptr<int64_t>());
     p.seq = a.seq; p.num_topk = a.num_topk;
+    p.dbg_flags = a.dbg_flags;
+    if (a.dbg_cycles.has_value()) p.dbg_cycles = reinterpret_cast<long long*>(a.dbg_cycles->data_ptr<int64_t>());
     p.num_ranks = num_ranks_; fill_peers(p.peer_base); p.ctl = ctl_;
     auto set_ref = [](RemoteRef& r, const std::vector<int>& v) {
       if (v.empty()) return;
@@ -993,7 +997,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       RW(mode) RW(epilogue) RW(block_n) RW(num_ctas) RW(a_mn_major) RW(b_mn_major) RW(a) RW(b)
       RW(tile_id_to_expert) RW(expert_pool_block_offset) RW(expert_frequency) RW(arrival_count) RW(arrival_target)
       RW(out0) RW(out1) RW(preact) RW(row_weight) RW(row_token) RW(dl_dweight) RW(scatter_local) RW(row_src) RW(row_k_slot)
-      RW(tile_stripes_done) RW(k_remaining) RW(done_per_token) RW(remote_out) RW(remote_dw)
+      RW(tile_stripes_done) RW(k_remaining) RW(done_per_token) RW(dbg_cycles) RW(dbg_flags) RW(remote_out) RW(remote_dw)
       RW(num_topk) RW(seq) RW(num_m_tiles) RW(started_flag)
       RW(tail) RW(tail_kind) RW(tail_wait) RW(fused_push) RW(fused_push_grads) RW(fused_push_routing) RW(fused_push_rows)
       RW(push_flags);
