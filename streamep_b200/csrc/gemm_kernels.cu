@@ -54,11 +54,25 @@ struct TileCoord {
   int k_tail;      // VarlenK: valid rows in the last block (0 = full)
 };
 
+// Tile order.  Consecutive linear indices (= CTAs working at the same time) walk a band of kBandM row tiles
+// column by column: a wave of 148 tiles then shares kBandM A tiles and ~148/kBandM B tiles instead of one A
+// tile and 148 B tiles, which keeps weight traffic out of HBM when one expert's weights exceed the L2.
+// Bands follow the pool order (expert-major), i.e. the order in which dispatch completes tiles.
+constexpr int kBandM = 8;
+
+__device__ __forceinline__ void band_decode(int lin, int num_m, int num_n, int& m_tile, int& n_tile) {
+  const int band = lin / (kBandM * num_n);
+  const int rem = lin - band * (kBandM * num_n);
+  const int m0 = band * kBandM;
+  const int gm = min(kBandM, num_m - m0);
+  n_tile = rem / gm;
+  m_tile = m0 + (rem - n_tile * gm);
+}
+
 __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int lin) {
   TileCoord t;
   if (p.mode == kVarlenM) {
-    t.m_tile = lin / p.num_n_tiles;
-    t.n_tile = lin - t.m_tile * p.num_n_tiles;
+    band_decode(lin, p.num_m_tiles, p.num_n_tiles, t.m_tile, t.n_tile);
     t.expert = p.tile_id_to_expert[t.m_tile];
     t.row0 = t.m_tile * BM;
     t.k_blocks = (p.K + BK - 1) / BK;
@@ -66,9 +80,7 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int lin) {
   } else {
     const int per_e = p.num_m_tiles * p.num_n_tiles;
     t.expert = lin / per_e;
-    const int rem = lin - t.expert * per_e;
-    t.m_tile = rem / p.num_n_tiles;
-    t.n_tile = rem - t.m_tile * p.num_n_tiles;
+    band_decode(lin - t.expert * per_e, p.num_m_tiles, p.num_n_tiles, t.m_tile, t.n_tile);
     t.row0 = p.expert_pool_block_offset[t.expert] * BM;
     const int len = p.expert_frequency[t.expert];
     t.k_blocks = (len + BK - 1) / BK;
