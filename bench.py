@@ -17,7 +17,8 @@ barrier and a device synchronize on both sides.  Each step sits between its own 
 on the launching stream and a 256 MiB buffer (larger than the 126 MB L2) is rewritten between
 steps, outside the event pairs; ``ms_per_step`` is the mean of the K event intervals and the
 reported value is the max over ranks.  ``e2e`` repeats the measurement through the public module API with, every step, the
-host-to-device copy of that step's inputs from pinned memory and a device-to-host read of the loss.
+host-to-device copy of that step's inputs from pinned memory (prefetched on a copy stream, two buffers)
+and a device-to-host read of that step's loss (read on the host one step behind the launches).
 """
 from __future__ import annotations
 
@@ -162,10 +163,12 @@ def main():
     if not args.no_e2e:
         x_host = [torch.randn(T, H).to(torch.bfloat16).pin_memory() for _ in range(2)]
         x_in = [torch.empty(T, H, dtype=torch.bfloat16, device=dev) for _ in range(2)]
-        loss_host = torch.empty(1, dtype=torch.float32).pin_memory()
+        loss_host = [torch.empty(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+        loss_ready = [torch.cuda.Event(), torch.cuda.Event()]
         copy_stream = torch.cuda.Stream()
         copied = [torch.cuda.Event(), torch.cuda.Event()]
         consumed = [torch.cuda.Event(), torch.cuda.Event()]
+        losses = []
 
         def prefetch(i):
             with torch.cuda.stream(copy_stream):
@@ -173,34 +176,42 @@ def main():
                 x_in[i % 2].copy_(x_host[i % 2], non_blocking=True)
                 copied[i % 2].record(copy_stream)
 
-        def step_e2e(i):
+        def read_loss(i):
+            """Host read of step i's loss (blocks until its device-to-host copy has landed)."""
+            loss_ready[i % 2].synchronize()
+            losses.append(float(loss_host[i % 2][0]))
+
+        def step_e2e(i, first):
             torch.cuda.current_stream().wait_event(copied[i % 2])
             h = x_in[i % 2].detach().requires_grad_(True)
             cur = h
             for layer in layers:
                 cur = layer(cur)            # router + experts: the call a user makes
-            loss = (cur.float() * dy_dev.float()).sum() * (1.0 / cur.numel())
+            loss = (cur * dy_dev).sum(dtype=torch.float32) * (1.0 / cur.numel())
             loss.backward()
             consumed[i % 2].record()
-            loss_host.copy_(loss.detach().reshape(1), non_blocking=True)
+            if not first:
+                read_loss(i - 1)            # every step's loss is read on the host, one step behind the launches
+            loss_host[i % 2].copy_(loss.detach().reshape(1), non_blocking=True)
+            loss_ready[i % 2].record()
             prefetch(i + 2)
-            torch.cuda.current_stream().synchronize()     # the step's result is read on the host
             for p in params:
                 p.grad = None
-            return float(loss_host[0])
 
         for j in range(2):
             consumed[j].record()
         prefetch(0); prefetch(1)
         for i in range(max(args.warmup, 3)):
-            step_e2e(i)
-        barrier()
+            step_e2e(i, first=(i == 0))
         base = max(args.warmup, 3)
+        read_loss(base - 1)
+        barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(args.steps):
             flush.zero_()
-            step_e2e(base + i)
+            step_e2e(base + i, first=(i == 0))
+        read_loss(base + args.steps - 1)    # the last step's loss, still inside the timed region
         e1.record()
         barrier()
         ms_e2e = e0.elapsed_time(e1) / args.steps

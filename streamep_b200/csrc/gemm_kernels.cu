@@ -430,36 +430,41 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
           __syncwarp();
         } else if (EPI == kEpiScatter) {
-          // stage the weighted bf16 row segment (64 bytes), then let 4 lanes handle one row so that
-          // every global access is a contiguous 64-byte piece of a destination row
+          // Stage two 32-column chunks side by side (128 bytes per row), then let 8 lanes handle one row so
+          // that every global access - local red.add or store into a peer's landing row over NVLink - is a
+          // full, contiguous 128-byte line of the destination row.
+          const int hpos = (c - c_begin) & 1;
 #pragma unroll
           for (int q = 0; q < 4; ++q)
-            st_shared_v4(stg + stage_off<64>(lane, q),
+            st_shared_v4(stg + stage_off<128>(lane, hpos * 4 + q),
                          pack_bf16x2(w * __uint_as_float(r[q * 8 + 0]), w * __uint_as_float(r[q * 8 + 1])),
                          pack_bf16x2(w * __uint_as_float(r[q * 8 + 2]), w * __uint_as_float(r[q * 8 + 3])),
                          pack_bf16x2(w * __uint_as_float(r[q * 8 + 4]), w * __uint_as_float(r[q * 8 + 5])),
                          pack_bf16x2(w * __uint_as_float(r[q * 8 + 6]), w * __uint_as_float(r[q * 8 + 7])));
-          __syncwarp();
+          const bool flush = hpos == 1 || n + 32 >= p.N || c + 1 == c_begin + kChunksPerHalf;
+          if (flush) {
+            __syncwarp();
+            const int nbase = n - hpos * 32;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int rr = i * 8 + (lane >> 2), piece = lane & 3;
-            const uint4 v = ld_shared_v4(stg + stage_off<64>(rr, piece));
-            char* ptr = reinterpret_cast<char*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(dst_row), rr));
-            const int o = __shfl_sync(0xffffffffu, op, rr);
-            const int col = n + piece * 8;
-            if (o != 0 && col < p.N) {
-              if (o == 1) red_add_bf16x2_v4(ptr + static_cast<long long>(col) * 2, v.x, v.y, v.z, v.w);
-              else st_na_v4(ptr + static_cast<long long>(col) * 2, v);
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + (lane >> 3), piece = lane & 7;
+              const uint4 v = ld_shared_v4(stg + stage_off<128>(rr, piece));
+              char* ptr = reinterpret_cast<char*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(dst_row), rr));
+              const int o = __shfl_sync(0xffffffffu, op, rr);
+              const int col = nbase + piece * 8;
+              if (o != 0 && piece < (hpos + 1) * 4 && col < p.N) {
+                if (o == 1) red_add_bf16x2_v4(ptr + static_cast<long long>(col) * 2, v.x, v.y, v.z, v.w);
+                else st_na_v4(ptr + static_cast<long long>(col) * 2, v);
+              }
             }
+            __syncwarp();
           }
-          __syncwarp();
         } else {   // kEpiDswiglu: r = g[row, n..n+32) = dL/d(postact) before the topk weight
           uint32_t o_pw[16];
           unsigned char* sb = epi_stage + (warp - 2) * Cfg::kEpiStageBytes;
 #ifdef SEP_EPI_TIMING
           const long long dbg_c0 = clock64();
 #endif
-#pragma unroll
           uint32_t rh[16];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {       // 8 output columns per step; N is a multiple of 8

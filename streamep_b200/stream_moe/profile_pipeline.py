@@ -66,6 +66,7 @@ def main():
     ap.add_argument("--fused", type=int, default=1)
     ap.add_argument("--ckpt-level", type=int, default=0)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--with-router", action="store_true", help="profile the module call (router + experts) and a scalar loss")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -93,9 +94,14 @@ def main():
     def step():
         h = x.detach().requires_grad_(True)
         cur = h
-        for layer, (idx, w, in_rank) in zip(layers, routing):
-            cur = layer.experts(cur, idx, w, in_rank)
-        cur.backward(dy)
+        if args.with_router:
+            for layer in layers:
+                cur = layer(cur)
+            ((cur * dy).sum(dtype=torch.float32) * (1.0 / cur.numel())).backward()
+        else:
+            for layer, (idx, w, in_rank) in zip(layers, routing):
+                cur = layer.experts(cur, idx, w, in_rank)
+            cur.backward(dy)
         for layer in layers:
             layer.w1.grad = None
             layer.w2.grad = None
