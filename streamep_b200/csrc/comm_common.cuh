@@ -129,6 +129,13 @@ __device__ __forceinline__ void push_chunk(const PushParams& p, const PushTarget
     const char* src_row = static_cast<const char*>(p.x) + static_cast<size_t>(tj) * row_bytes;
     char* dst_row = tg.pool[dj] + static_cast<size_t>(sj) * row_bytes;
     int v = lane;
+    for (; v + 224 < vec_per_row; v += 256) {      // 8 x 16 bytes in flight per lane: one 4 KB row per pass
+      uint4 a[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) a[u] = ld_nc_v4(src_row + static_cast<size_t>(v + 32 * u) * 16);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) st_na_v4(dst_row + static_cast<size_t>(v + 32 * u) * 16, a[u]);
+    }
     for (; v + 96 < vec_per_row; v += 128) {
       uint4 a0 = ld_nc_v4(src_row + static_cast<size_t>(v) * 16);
       uint4 a1 = ld_nc_v4(src_row + static_cast<size_t>(v + 32) * 16);

@@ -29,7 +29,7 @@ constexpr int BK = 64;           // bf16 elements per k-block: one 128-byte swiz
 constexpr int UMMA_K = 16;
 constexpr int kGemmWarps = 10;   // 0: TMA producer, 1: MMA issuer + TMEM owner, 2..9: epilogue
 // extra warps of the fused variants; the dSwiGLU epilogue keeps two preact segments in registers, so it gets fewer
-constexpr int push_warps(int epi) { return epi == kEpiDswiglu ? 4 : 6; }
+constexpr int push_warps(int epi) { return epi == kEpiDswiglu ? 6 : 10; }
 constexpr int kEpiThreads = 256; // two threads per accumulator row: each takes half of the tile's columns
 
 template <int BN> struct GemmCfg {

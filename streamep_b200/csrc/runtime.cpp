@@ -829,6 +829,78 @@ class Runtime {
     return {out, postact, preact};
   }
 
+  // Whole fused backward in one native call (same reason as fused_forward: every host microsecond between
+  // two launches is a microsecond in which a slow host holds back all ranks at the next collective).
+  // `rows_saved` is the pool (checkpoint levels 0/1) or the compact per-recv-token rows (level 2).
+  // Returns {dL_dx, dL_dtopk_weights, dW1, dW2}.
+  std::vector<at::Tensor> fused_backward(const std::shared_ptr<DispatchState>& st, const at::Tensor& dl_dy, const at::Tensor& w1,
+                                         const at::Tensor& w2, const at::Tensor& rows_saved, const std::optional<at::Tensor>& preact_saved,
+                                         int level, int tile_n_a, int tile_n_y_bwd, int tile_n_a_bwd, int tile_n_dw1, int tile_n_dw2,
+                                         int num_sms_y_bwd, int num_sms_a_bwd) {
+    const int64_t tiles = st->total_tiles, TKp = tiles * st->tile_m, T = st->num_tokens, K = st->num_topk;
+    const int64_t H = w2.size(1), I = w2.size(2);
+    auto opts = st->x.options();
+    at::Tensor dswiglu_in = at::empty({TKp, 2 * I}, opts), postact_dw2 = at::empty({TKp, I}, opts);
+    at::Tensor dW1 = at::empty_like(w1), dW2 = at::empty_like(w2);
+    const int64_t nt = std::max<int64_t>(tiles, 1);
+    at::Tensor zeros = at::zeros({nt + TKp}, opts.dtype(at::kInt));
+    at::Tensor stripes = zeros.narrow(0, 0, nt), dl_dweight = zeros.narrow(0, nt, TKp).view(at::kFloat);
+    at::Tensor dx = at::zeros({T, H}, opts);
+    at::Tensor landing = alloc_symmetric({num_ranks_ > 1 ? T * K : 0, H}, at::kBFloat16, false);
+    at::Tensor dwt = alloc_symmetric({T, K}, at::kFloat, true);
+    auto g = grads_begin(st);
+    grads_set_aux(g, 0, landing);
+    grads_set_aux(g, 1, dwt);
+    at::Tensor pool = rows_saved;
+    if (level == 2) pool = TKp > 0 ? pool_expand(rows_saved, st->pool_recv_token, TKp) : at::empty({0, H}, opts);
+    at::Tensor preact;
+    if (preact_saved.has_value() && preact_saved->defined()) {
+      preact = *preact_saved;
+    } else {
+      preact = at::empty({TKp, 2 * I}, opts);
+      if (tiles > 0) {
+        GemmArgs r;
+        r.mode = kVarlenM; r.epilogue = kEpiStore; r.block_n = tile_n_a;
+        r.a = pool; r.b = w1; r.tile_id_to_expert = st->tile_id_to_expert; r.out0 = preact;
+        grouped_gemm(r);
+      }
+    }
+    GemmArgs y;
+    y.mode = kVarlenM; y.epilogue = kEpiDswiglu; y.block_n = tile_n_y_bwd; y.b_mn_major = true; y.num_ctas = num_sms_y_bwd;
+    y.a = g->dl_do_pool; y.b = w2; y.tile_id_to_expert = st->tile_id_to_expert;
+    y.preact = preact; y.out0 = dswiglu_in; y.out1 = postact_dw2;
+    y.row_weight = st->pool_topk_weight; y.row_token = st->pool_recv_token; y.dl_dweight = dl_dweight;
+    y.arrival_count = g->bwd_dispatch_arrival_count; y.arrival_target = st->pool_arrival_target;
+    y.remote_dw = {kKindDispatchGrads, g->epoch, 11};
+    y.row_src = st->pool_src; y.row_k_slot = st->pool_k_slot; y.num_topk = static_cast<int>(K); y.tile_stripes_done = stripes;
+    y.fused_push_grads = g; y.fused_push_routing = st; y.fused_push_rows = dl_dy; y.push_flags = 3;
+    grouped_gemm(y);
+    GemmArgs a;
+    a.mode = kVarlenM; a.epilogue = kEpiScatter; a.block_n = tile_n_a_bwd; a.b_mn_major = true; a.num_ctas = num_sms_a_bwd;
+    a.a = dswiglu_in; a.b = w1; a.tile_id_to_expert = st->tile_id_to_expert;
+    a.row_token = st->pool_recv_token; a.scatter_local = dx;
+    a.remote_out = {kKindDispatchGrads, g->epoch, 10};
+    a.row_src = st->pool_src; a.row_k_slot = st->pool_k_slot; a.num_topk = static_cast<int>(K);
+    a.tail = true; a.tail_kind = kKindGemmABwdTail; a.tail_wait = true;
+    grouped_gemm(a);
+    combine_reduce(dx, landing, st->topk_idx, st->num_experts);
+    if (tiles > 0) {
+      GemmArgs d2;
+      d2.mode = kVarlenK; d2.epilogue = kEpiStore; d2.block_n = tile_n_dw2; d2.a_mn_major = d2.b_mn_major = true;
+      d2.a = g->dl_do_pool; d2.b = postact_dw2; d2.out0 = dW2;
+      d2.expert_pool_block_offset = st->expert_pool_block_offset; d2.expert_frequency = st->expert_frequency;
+      grouped_gemm(d2);
+      GemmArgs d1;
+      d1.mode = kVarlenK; d1.epilogue = kEpiStore; d1.block_n = tile_n_dw1; d1.a_mn_major = d1.b_mn_major = true;
+      d1.a = dswiglu_in; d1.b = pool; d1.out0 = dW1;
+      d1.expert_pool_block_offset = st->expert_pool_block_offset; d1.expert_frequency = st->expert_frequency;
+      grouped_gemm(d1);
+    } else {
+      dW1.zero_(); dW2.zero_();
+    }
+    return {dx, dwt, dW1, dW2};
+  }
+
   // ---- small ops ---------------------------------------------------------------------------------------
   void tile_producer(const at::Tensor& count, const at::Tensor& target, double delay_us) {
     ++launches_; launch_tile_producer(count.data_ptr<int>(), target.data_ptr<int>(), count.numel(), static_cast<long long>(delay_us * 1000.0),
@@ -1047,6 +1119,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_epochs", &Runtime::set_epochs)
       .def("grouped_gemm", &Runtime::grouped_gemm)
       .def("fused_forward", &Runtime::fused_forward)
+      .def("fused_backward", &Runtime::fused_backward)
       .def("tile_producer", &Runtime::tile_producer)
       .def("combine_reduce", &Runtime::combine_reduce)
       .def("pool_compress", &Runtime::pool_compress)

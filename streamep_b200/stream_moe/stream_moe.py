@@ -256,6 +256,16 @@ def moe_backward(ctx, dL_dy):
     comm, comp = streams.communicate, streams.compute
     dL_dy = dL_dy.contiguous().to(torch.bfloat16)
     TKp, tiles = handle.TK_padded, handle.total_tiles
+    if fused and not buffer._emulated:
+        # Production path: one native call (Runtime::fused_backward) issues the whole backward.
+        comp.wait_stream(caller)
+        with torch.cuda.stream(comp):
+            dL_dx, dL_dw, dW1, dW2 = rt.fused_backward(
+                st, dL_dy, sv.w1, sv.w2, sv.pool, sv.preact, level, cfg.tile_n_a, cfg.tile_n_y_bwd, cfg.tile_n_a_bwd,
+                cfg.tile_n_dW1, cfg.tile_n_dW2, cfg.num_sms_y_bwd or 0, cfg.num_sms_a_bwd or 0)
+        caller.wait_stream(comp)
+        _nvtx_pop()
+        return dL_dx, dL_dw, dW1, dW2
 
     dswiglu_in = torch.empty(TKp, 2 * I, dtype=torch.bfloat16, device=dev)
     postact_dw2 = torch.empty(TKp, I, dtype=torch.bfloat16, device=dev)

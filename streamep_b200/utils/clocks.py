@@ -17,7 +17,7 @@ _REASONS = {  # NVML clocks-event-reason bits
 
 
 class ClockSampler:
-    def __init__(self, gpu_index: int, period_s: float = 0.002):
+    def __init__(self, gpu_index: int, period_s: float = 0.01):
         self.gpu_index, self.period_s = gpu_index, period_s
         self.sm: List[float] = []
         self.power: List[float] = []
