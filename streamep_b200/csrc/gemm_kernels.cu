@@ -168,6 +168,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       for (int lin = blockIdx.x; lin < total_tiles && ok; lin += gridDim.x) {
         const TileCoord t = decode_tile(p, lin);
         if (p.mode == kVarlenM && p.arrival_count != nullptr) {
+#ifdef SEP_EPI_TIMING
+          const unsigned long long dbg_g0 = globaltimer_ns();
+#endif
           const int target = p.arrival_target[t.m_tile];
           const int* cnt = p.arrival_count + t.m_tile;
           if (!spin_until([&] { return ld_acquire_sys(cnt) == target; }, budget, p.status)) {
@@ -175,6 +178,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             ok = false; break;
           }
           fence_proxy_async();   // rows were written through the generic proxy (possibly by a peer GPU)
+#ifdef SEP_EPI_TIMING
+          if (PUSH && p.dbg_cycles != nullptr) {
+            const unsigned long long now = globaltimer_ns();
+            p.dbg_cycles[blockIdx.x * 16 + 8] += static_cast<long long>(now - dbg_g0);        // ns spent waiting on tile gates
+            if (lin == static_cast<int>(blockIdx.x)) p.dbg_cycles[blockIdx.x * 16 + 9] = static_cast<long long>(now);   // first tile ready
+            p.dbg_cycles[blockIdx.x * 16 + 10] = static_cast<long long>(now);                 // last tile ready
+          }
+#endif
         }
         for (int kb = 0; kb < t.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, budget, p.status)) {
@@ -594,12 +605,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #ifdef SEP_EPI_TIMING
     if (p.dbg_cycles != nullptr && warp == 2 && lane == 0) {
       dbg_t[7] = clock64() - dbg_start;
-      for (int i = 0; i < 8; ++i) p.dbg_cycles[blockIdx.x * 8 + i] = dbg_t[i];
+      for (int i = 0; i < 8; ++i) p.dbg_cycles[blockIdx.x * 16 + i] = dbg_t[i];
     }
 #endif
     if (p.tail.enabled) __threadfence_system();
   } else if (PUSH) {
     // ------------------------------------------------------------------ dispatch push warps
+#ifdef SEP_EPI_TIMING
+    if (p.dbg_cycles != nullptr && warp == kGemmWarps && lane == 0) p.dbg_cycles[blockIdx.x * 16 + 11] = static_cast<long long>(globaltimer_ns());
+#endif
     if (pp.flags & 2) {
       const int pw = warp - kGemmWarps;
       if (pw == 0 && lane < pp.num_ranks) {
@@ -622,8 +636,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           push_chunk(pp, s_tg, p0, min(p0 + ppc, num_send), lane);
         }
       }
+#ifdef SEP_EPI_TIMING
+      if (p.dbg_cycles != nullptr && lane == 0)
+        atomicMax(reinterpret_cast<unsigned long long*>(p.dbg_cycles + blockIdx.x * 16 + 12), globaltimer_ns());   // this CTA's push end
+      if (p.dbg_cycles != nullptr && pw == 0 && lane == 0) p.dbg_cycles[blockIdx.x * 16 + 13] = static_cast<long long>(globaltimer_ns());  // after record fetch .. first warp done
+#endif
     }
   }
+#ifdef SEP_EPI_TIMING
+  if (PUSH && p.dbg_cycles != nullptr && threadIdx.x == 0) p.dbg_cycles[blockIdx.x * 16 + 14] = static_cast<long long>(globaltimer_ns());
+#endif
 
   // ---------------------------------------------------------------------- teardown
   tc_fence_before_sync();

@@ -290,6 +290,9 @@ class Runtime {
   int num_ranks() const { return num_ranks_; }
   int num_channels() const { return num_channels_; }
   int64_t launch_count() const { return launches_; }
+  // Debug builds (-DSEP_EPI_TIMING): int64 [num_sms, 16] that the next fused dispatch+GEMM-A launches fill with timestamps.
+  void set_debug_tensor(const at::Tensor& t) { dbg_fused_a_ = t; }
+  void set_pairs_per_chunk(int n) { SEP_ASSERT(n >= 1 && n <= 32, "pairs per chunk must be 1..32"); pairs_per_chunk_ = n; }
   int64_t arena_bytes_in_use() const { return static_cast<int64_t>(arena_->bytes_in_use()); }
   int64_t arena_high_water() const { return static_cast<int64_t>(arena_->high_water()); }
   int64_t arena_capacity() const { return static_cast<int64_t>(arena_->capacity()); }
@@ -529,7 +532,7 @@ class Runtime {
     p.num_tokens = st.num_tokens; p.hidden = st.hidden; p.num_topk = st.num_topk; p.num_experts = st.num_experts;
     p.num_ranks = num_ranks_; p.rank = rank_; p.tile_m = st.tile_m;
     p.is_grads = is_grads ? 1 : 0; p.kind = kind; p.epoch = epoch; p.flags = flags;
-    p.pairs_per_chunk = 16;
+    p.pairs_per_chunk = pairs_per_chunk_;
     fill_peers(p.peer_base); p.ctl = ctl_; p.own = rec;
     p.own_arrival_count = own_count; p.own_arrival_target = st.pool_arrival_target.data_ptr<int>();
     p.own_total_tiles = st.total_tiles;
@@ -703,6 +706,7 @@ class Runtime {
     p.seq = a.seq; p.num_topk = a.num_topk;
     p.dbg_flags = a.dbg_flags;
     if (a.dbg_cycles.has_value()) p.dbg_cycles = reinterpret_cast<long long*>(a.dbg_cycles->data_ptr<int64_t>());
+    else if (dbg_fused_a_.defined() && a.fused_push && a.epilogue == kEpiSwiglu) p.dbg_cycles = reinterpret_cast<long long*>(dbg_fused_a_.data_ptr<int64_t>());
     p.num_ranks = num_ranks_; fill_peers(p.peer_base); p.ctl = ctl_;
     auto set_ref = [](RemoteRef& r, const std::vector<int>& v) {
       if (v.empty()) return;
@@ -987,6 +991,8 @@ class Runtime {
   int64_t timeout_ms_ = 0;
   int epochs_[kNumKinds];
   int64_t launches_ = 0;
+  int pairs_per_chunk_ = 4;   // small chunks keep the push progressive: tiles complete in push order, not all at the end
+  at::Tensor dbg_fused_a_;
   int gate_issued_[8];
   bool available_ = false, destroyed_ = false;
 };
@@ -1091,6 +1097,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_property_readonly("num_ranks", &Runtime::num_ranks)
       .def_property_readonly("num_channels", &Runtime::num_channels)
       .def("launch_count", &Runtime::launch_count)
+      .def("set_debug_tensor", &Runtime::set_debug_tensor)
+      .def("set_pairs_per_chunk", &Runtime::set_pairs_per_chunk)
       .def("arena_bytes_in_use", &Runtime::arena_bytes_in_use)
       .def("arena_high_water", &Runtime::arena_high_water)
       .def("arena_capacity", &Runtime::arena_capacity)
