@@ -991,7 +991,7 @@ class Runtime {
   int64_t timeout_ms_ = 0;
   int epochs_[kNumKinds];
   int64_t launches_ = 0;
-  int pairs_per_chunk_ = 4;   // small chunks keep the push progressive: tiles complete in push order, not all at the end
+  int pairs_per_chunk_ = 8;   // small chunks keep the push progressive: tiles complete in push order, not all at the end
   at::Tensor dbg_fused_a_;
   int gate_issued_[8];
   bool available_ = false, destroyed_ = false;
