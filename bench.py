@@ -10,7 +10,10 @@ router on x ~ N(0,1), SwiGLU ffn 1408, w1 [8, 2816, 2048], w2 [8, 2048, 1408] ~ 
 synthetic data, random-init weights.  Weak scaling: per-rank tokens and experts stay fixed as the
 number of GPUs grows.  ``--config scaling`` runs the Mixtral-style sweep shape (16384 tokens/rank,
 hidden 4096, 8 experts in total, top-2, ffn 14336, 3 layers back to back); ``--config wide`` the
-dispatch-heavy shape (4096 tokens/rank, hidden 7168, 32 experts/rank, top-8, ffn 2048).
+dispatch-heavy shape (4096 tokens/rank, hidden 7168, 32 experts/rank, top-8, ffn 2048);
+``--config skewed`` the stress shape (tokens per rank drawn from [2048, 6144], hidden 7168, 32
+experts/rank, top-8 distinct experts sampled Zipf(1.2) over expert ids, ffn 2048, forward GEMM
+recomputed in backward).  ``--impl nccl_baseline`` times the library all-to-all + cuBLAS layer.
 
 Timing: W (>= 3) untimed warm-up steps, then exactly K steps, the whole region bracketed by a
 barrier and a device synchronize on both sides.  Each step sits between its own pair of CUDA events
@@ -36,6 +39,10 @@ CONFIGS = {
     "scaling": dict(tokens=16384, hidden=4096, experts_per_rank=None, experts_total=8, topk=2, ffn=14336, layers=3),
     "wide":    dict(tokens=4096, hidden=7168, experts_per_rank=32, experts_total=None, topk=8, ffn=2048, layers=1),
     "tiny":    dict(tokens=512, hidden=256, experts_per_rank=4, experts_total=None, topk=2, ffn=128, layers=1),
+    # skewed / uneven stress: tokens per rank drawn once from [2048, 6144], top-8 distinct experts sampled
+    # Zipf(1.2) over the expert ids (rank 0 owns the hot experts), recompute of the forward GEMM in backward
+    "skewed":  dict(tokens=(2048, 6144), hidden=7168, experts_per_rank=32, experts_total=None, topk=8, ffn=2048,
+                    layers=1, routing="zipf", ckpt_level=1),
 }
 
 
@@ -64,7 +71,7 @@ def main():
     ap.add_argument("--config", default="full", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="streamep_b200", choices=["streamep_b200", "reference", "nccl_baseline"])
     ap.add_argument("--fused", type=int, default=1)
-    ap.add_argument("--ckpt-level", type=int, default=0)
+    ap.add_argument("--ckpt-level", type=int, default=None, help="0/1/2; default: the config's (0 unless it names one)")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -93,14 +100,25 @@ def main():
     from streamep_b200.parallel.nccl_baseline import NcclBaselineMoE
 
     c = CONFIGS[args.config]
-    T, H, K, I, L = c["tokens"], c["hidden"], c["topk"], c["ffn"], c["layers"]
+    H, K, I, L = c["hidden"], c["topk"], c["ffn"], c["layers"]
     E = c["experts_total"] if c["experts_total"] is not None else c["experts_per_rank"] * world
     assert E % world == 0
+    if args.ckpt_level is None:
+        args.ckpt_level = c.get("ckpt_level", 0)
+    if isinstance(c["tokens"], tuple):      # uneven: every rank draws the same list, then takes its entry
+        lo, hi = c["tokens"]
+        tokens_all = torch.randint(lo, hi + 1, (world,), generator=torch.Generator().manual_seed(4242)).tolist()
+    else:
+        tokens_all = [c["tokens"]] * world
+    T, T_max = tokens_all[rank], max(tokens_all)
+    zipf = c.get("routing") == "zipf"
     torch.manual_seed(1234 + rank)
 
     buffer = None
     if args.impl == "streamep_b200":
-        buffer = make_buffer(group, T, H, K, E, layers_in_flight=L, world_size=world)
+        # Zipf routing can send nearly every pair to one rank: size the arena for that
+        buffer = make_buffer(group, T_max, H, K, E, layers_in_flight=L, world_size=world,
+                             imbalance=1.6 * world if zipf else 1.5)
         layers = [StreamMoE(H, I, E, K, buffer, fused=bool(args.fused), activation_checkpoint_level=args.ckpt_level,
                             device=dev, seed=100 + i) for i in range(L)]
     else:
@@ -111,7 +129,15 @@ def main():
     dy_dev = (torch.randn(T, H, device=dev) * 0.1).to(torch.bfloat16)
     # routing comes from each layer's linear router on x (computed once: the timed value is the
     # layer's forward+backward with routing as an input, like the reference's harness)
-    routing = [layer.route(x_dev) for layer in layers]
+    if zipf:
+        g = torch.Generator().manual_seed(777 + rank)
+        prob = torch.arange(1, E + 1, dtype=torch.float64).pow(-1.2)
+        idx = torch.multinomial((prob / prob.sum()).expand(T, E), K, replacement=False, generator=g).to(dev)
+        wts = torch.softmax(torch.randn(T, K, generator=g), dim=-1).to(dev)
+        in_rank = torch.zeros(T, world, dtype=torch.bool, device=dev).scatter_(1, idx // (E // world), True)
+        routing = [(idx, wts, in_rank) for _ in layers]
+    else:
+        routing = [layer.route(x_dev) for layer in layers]
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB L2
 
     def barrier():
@@ -185,8 +211,9 @@ def main():
             torch.cuda.current_stream().wait_event(copied[i % 2])
             h = x_in[i % 2].detach().requires_grad_(True)
             cur = h
-            for layer in layers:
-                cur = layer(cur)            # router + experts: the call a user makes
+            for layer, r in zip(layers, routing):
+                # router + experts: the call a user makes (the Zipf config supplies its own routing)
+                cur = layer.experts(cur, *r) if zipf else layer(cur)
             loss = (cur * dy_dev).sum(dtype=torch.float32) * (1.0 / cur.numel())
             loss.backward()
             consumed[i % 2].record()
@@ -225,9 +252,9 @@ def main():
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
     ms_max, ms_e2e_max = float(vals[0]), float(vals[1])
     if rank == 0:
-        tokens_per_step = T * world
+        tokens_per_step = sum(tokens_all)
         value = tokens_per_step / (ms_max * 1e-3)
-        pairs = T * K
+        pairs = tokens_per_step * K / world       # average per rank; Zipf routing loads the ranks unevenly
         flops = 18.0 * pairs * H * I * L          # forward 6 + backward 12 per (token, expert) pair
         peaks = {}
         try:
@@ -243,7 +270,9 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (x ~ N(0,1), random-init weights ~ N(0,0.02))",
             "impl": args.impl,
             "config": {"model": f"moe_layer[{args.config}] H={H} ffn={I} E={E} ({E // world}/rank) top{K} layers={L}",
-                       "global_batch": tokens_per_step, "seq_len": T, "parallelism": f"ep{world}",
+                       "global_batch": tokens_per_step, "seq_len": T if len(set(tokens_all)) == 1 else tokens_all,
+                       "routing": "zipf(1.2) over expert ids, top-k distinct" if zipf else "linear router on x, softmax top-k renormalised",
+                       "parallelism": f"ep{world}",
                        "fused": bool(args.fused), "activation_checkpoint_level": args.ckpt_level,
                        "l2_flush": "256 MiB buffer rewritten between timed iterations"},
             "clocks": clocks,

@@ -161,6 +161,11 @@ class Buffer:
             assert self.runtime.is_available()
         self._next_seq = 0
         self._push_blocks = 0  # 0 = auto
+        self._compute_stream_handle = None
+        self._default_stream_handle = None
+        chunk = os.environ.get("STREAM_EP_PUSH_CHUNK_PAIRS")
+        if chunk:
+            self.runtime.set_pairs_per_chunk(int(chunk))
 
     # ------------------------------------------------------------------ lifecycle
     def destroy(self):
@@ -235,8 +240,19 @@ class Buffer:
         return int(per_layer * (layers_in_flight + 1.5))
 
     # ------------------------------------------------------------------ launch gates
+    def set_compute_stream_handle(self, stream) -> None:
+        """Remember the caller's compute stream (reference: csrc/stream_ep.cpp:387-456, called from
+        stream_ep/stream_moe/stream_moe.py:1239).  The gate helpers wait on it when no stream is given."""
+        self._compute_stream_handle = stream
+
+    def set_default_stream_handle(self, stream) -> None:
+        """Remember the stream the layer was called on (stream_ep/stream_moe/stream_moe.py:1247)."""
+        self._default_stream_handle = stream
+
     def _raw(self, stream):
-        return (stream if stream is not None else torch.cuda.current_stream()).cuda_stream
+        if stream is None:
+            stream = self._compute_stream_handle if self._compute_stream_handle is not None else torch.cuda.current_stream()
+        return stream.cuda_stream
 
     def wait_dispatch_main_started(self, stream=None) -> None:
         """Hold ``stream`` at the GPU front-end until the last dispatch kernel is resident

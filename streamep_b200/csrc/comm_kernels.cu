@@ -446,6 +446,7 @@ void launch_dispatch_push(const PushParams& p, int num_blocks, cudaStream_t stre
 // Pull combine
 // =============================================================================================
 constexpr int kCombineThreads = 512;
+constexpr int kPullUnroll = 2;          // 16-byte loads in flight per lane and contributing rank
 
 __global__ void __launch_bounds__(kCombineThreads, 1) combine_pull_kernel(const CombineParams p) {
   __shared__ const char* s_x[kMaxRanks];
@@ -493,20 +494,43 @@ __global__ void __launch_bounds__(kCombineThreads, 1) combine_pull_kernel(const 
                                   static_cast<int>(p.seq), static_cast<int>(ld_acquire_sys(g)));
         }
         if (!__all_sync(0xffffffffu, ok)) break;
-        for (int v = lane; v < vec_per_row; v += 32) {
-          float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-          for (int d = 0; d < R; ++d) {
-            const int r = __shfl_sync(0xffffffffu, my_r, d);
-            if (r < 0) continue;
-            const uint4 q = ld_relaxed_sys_v4(s_x[d] + static_cast<size_t>(r) * row_bytes + static_cast<size_t>(v) * 16);
-            const float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), c = unpack_bf16x2(q.z), e = unpack_bf16x2(q.w);
-            acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
-            acc[4] += c.x; acc[5] += c.y; acc[6] += e.x; acc[7] += e.y;
+        // Every contributing rank's row address, warp-uniform; a lane then keeps kPullUnroll x R
+        // predicated 16-byte loads in flight so that the NVLink round trip is paid once per batch,
+        // not once per load.
+        const char* src[kMaxRanks];
+#pragma unroll
+        for (int d = 0; d < kMaxRanks; ++d) {
+          const int r = __shfl_sync(0xffffffffu, my_r, d);
+          src[d] = (d < R && r >= 0) ? s_x[d] + static_cast<size_t>(r) * row_bytes : nullptr;
+        }
+        char* out_row = static_cast<char*>(p.out) + static_cast<size_t>(t) * row_bytes;
+        for (int v0 = lane; v0 < vec_per_row; v0 += 32 * kPullUnroll) {
+          uint4 q[kPullUnroll][kMaxRanks];
+#pragma unroll
+          for (int j = 0; j < kPullUnroll; ++j) {
+            const int v = v0 + 32 * j;
+#pragma unroll
+            for (int d = 0; d < kMaxRanks; ++d)
+              q[j][d] = (src[d] != nullptr && v < vec_per_row) ? ld_relaxed_sys_v4(src[d] + static_cast<size_t>(v) * 16)
+                                                              : make_uint4(0, 0, 0, 0);
           }
-          uint4 o;
-          o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-          o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
-          st_na_v4(static_cast<char*>(p.out) + static_cast<size_t>(t) * row_bytes + static_cast<size_t>(v) * 16, o);
+#pragma unroll
+          for (int j = 0; j < kPullUnroll; ++j) {
+            const int v = v0 + 32 * j;
+            if (v >= vec_per_row) break;
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+            for (int d = 0; d < kMaxRanks; ++d) {
+              const float2 a = unpack_bf16x2(q[j][d].x), b = unpack_bf16x2(q[j][d].y), c = unpack_bf16x2(q[j][d].z),
+                           e = unpack_bf16x2(q[j][d].w);
+              acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+              acc[4] += c.x; acc[5] += c.y; acc[6] += e.x; acc[7] += e.y;
+            }
+            uint4 o;
+            o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+            o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+            st_na_v4(out_row + static_cast<size_t>(v) * 16, o);
+          }
         }
         if (!p.is_fwd && lane < K) {
           const long long e = p.topk_idx[static_cast<size_t>(t) * K + lane];

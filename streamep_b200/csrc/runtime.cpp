@@ -100,6 +100,12 @@ struct Config {
     SEP_ASSERT(nvl_send > 0 && nvl_recv > 0 && nvl_send < nvl_recv, "NVL chunk sizes must satisfy 0 < send < recv");
     SEP_ASSERT(rdma_send > 0 && rdma_recv > 0, "RDMA chunk sizes must be positive");
   }
+  // Same call shape as the reference's ring-size hints (csrc/config.hpp:52-87).  There are no rings
+  // here: the arena holds the pools themselves, whose size depends on the token count, so the hint
+  // covers a stated workload (8192 tokens per rank, top-8, 1.5x imbalance, two layers in flight).
+  // Callers that know their shapes use Buffer.get_arena_size_hint instead.
+  size_t get_nvl_buffer_size_hint(size_t hidden_bytes, int num_ranks) const;
+  size_t get_rdma_buffer_size_hint(int64_t, int) const { return 0; }   // no RDMA tier on one NVSwitch domain
 };
 
 struct ArenaSizeHint {
@@ -115,6 +121,12 @@ struct ArenaSizeHint {
     return static_cast<size_t>(b * 1.05) + (8u << 20);
   }
 };
+
+size_t Config::get_nvl_buffer_size_hint(size_t hidden_bytes, int num_ranks) const {
+  SEP_ASSERT(num_ranks >= 1 && num_ranks <= kMaxRanks && hidden_bytes % 2 == 0, "bad hint arguments");
+  const size_t per_layer = ArenaSizeHint::layer_bytes(8192, static_cast<int64_t>(hidden_bytes / 2), 8, num_ranks, 32, 1.5);
+  return per_layer * 7 / 2;
+}
 
 // ---------------------------------------------------------------------------------------------
 // Event handle (reference: csrc/event.hpp:9-35)
@@ -1033,6 +1045,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def(py::init<int, int, int, int, int>(), py::arg("num_sms") = 20, py::arg("num_max_nvl_chunked_send_tokens") = 6,
            py::arg("num_max_nvl_chunked_recv_tokens") = 256, py::arg("num_max_rdma_chunked_send_tokens") = 6,
            py::arg("num_max_rdma_chunked_recv_tokens") = 256)
+      .def("get_nvl_buffer_size_hint", &Config::get_nvl_buffer_size_hint)
+      .def("get_rdma_buffer_size_hint", &Config::get_rdma_buffer_size_hint)
       .def_readonly("num_sms", &Config::num_sms)
       .def_readonly("num_max_nvl_chunked_send_tokens", &Config::num_max_nvl_chunked_send_tokens)
       .def_readonly("num_max_nvl_chunked_recv_tokens", &Config::num_max_nvl_chunked_recv_tokens)
@@ -1042,7 +1056,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   py::class_<EventHandle>(m, "EventHandle")
       .def(py::init<>())
       .def("current_stream_wait", &EventHandle::current_stream_wait)
-      .def("wait_on", &EventHandle::wait_on);
+      .def("wait_on", &EventHandle::wait_on)
+      // same duck type as torch.cuda.Event: ``stream.wait_event(handle)`` calls ``handle.wait(stream)``
+      .def("wait", [](const EventHandle& e, const py::object& stream) {
+        e.wait_on(stream.attr("cuda_stream").cast<int64_t>(), stream.attr("device_index").cast<int>());
+      });
 
   py::class_<DispatchState, std::shared_ptr<DispatchState>>(m, "DispatchState")
 #define RO(name) .def_readonly(#name, &DispatchState::name)

@@ -210,3 +210,25 @@ def test_combine_gate_timeout_is_reported(native):
     world.combine([h.o for h in handles], handles)
     torch.cuda.synchronize()
     world.check_status()
+
+
+def test_event_handle_and_stream_handles(native):
+    """``EventHandle`` behaves like a ``torch.cuda.Event`` for ``Stream.wait_event`` and the buffer
+    keeps the stream handles that the layer registers (csrc/event.hpp:9-35, csrc/stream_ep.cpp:387-456)."""
+    from streamep_b200 import EventHandle
+    world = _world(1)
+    buf = world.buffers[0]
+    side = torch.cuda.Stream()
+    a = torch.zeros(1 << 20, device=DEV)
+    a.add_(1.0)
+    ev = EventHandle()                       # recorded on the current stream, after the add
+    side.wait_event(ev)                      # duck-typed: calls ev.wait(side)
+    with torch.cuda.stream(side):
+        b = a * 2
+    side.synchronize()
+    assert float(b.sum()) == 2.0 * (1 << 20)
+    buf.set_compute_stream_handle(side)
+    buf.set_default_stream_handle(torch.cuda.current_stream())
+    assert buf._raw(None) == side.cuda_stream
+    buf.set_compute_stream_handle(None)
+    assert buf._raw(None) == torch.cuda.current_stream().cuda_stream

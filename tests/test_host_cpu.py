@@ -132,6 +132,12 @@ def test_config_validation_and_fields():
     assert (cfg.num_sms, cfg.num_max_nvl_chunked_send_tokens, cfg.num_max_nvl_chunked_recv_tokens) == (80, 6, 256)
     with pytest.raises(ValueError):
         streamep_b200.Config(80, 256, 6, 6, 128)        # send must be smaller than recv
+    # the ring-size hints of the reference keep their call shape; the value covers a stated workload
+    small, large = cfg.get_nvl_buffer_size_hint(2048 * 2, 8), cfg.get_nvl_buffer_size_hint(7168 * 2, 8)
+    assert 0 < small < large and large >= streamep_b200.Buffer.get_arena_size_hint(8192, 7168, 8, 8, 32)
+    assert cfg.get_rdma_buffer_size_hint(7168 * 2, 8) == 0
+    with pytest.raises(ValueError):
+        cfg.get_nvl_buffer_size_hint(14336, 9)
 
 
 def test_buffer_policy_tables_without_gpu():
