@@ -93,6 +93,28 @@ class StreamingHandle:
     def num_recv_tokens(self) -> int:
         return self._dispatch_out.num_recv_tokens
 
+    def stats(self, rank: Optional[int] = None) -> dict:
+        """Per-dispatch counters for logging (synchronises: it reads device tensors).
+
+        ``pairs_received`` / ``recv_tokens`` / ``total_tiles`` / ``padding_ratio`` describe this
+        rank's pool; ``pairs_sent_remote`` and the byte counts describe what this rank's push
+        (dispatch: one row per pair) and the matching combine traffic (one row per pair back to
+        the source) move over NVLink.  ``rank`` (this rank's index) is needed for the remote counts."""
+        hidden = int(self.pool.shape[1]) if self.pool.dim() == 2 else 0
+        freq = self.expert_frequency.cpu()
+        pairs = int(freq.sum())
+        out = {"pairs_received": pairs, "recv_tokens": self.num_recv_tokens, "total_tiles": int(self.total_tiles),
+               "rows_padded": int(self.TK_padded),
+               "padding_ratio": (self.TK_padded - pairs) / self.TK_padded if self.TK_padded else 0.0,
+               "max_expert_rows": int(freq.max()) if freq.numel() else 0, "dispatch_seq": int(self.dispatch_seq)}
+        if rank is not None and self._dispatch_out is not None:
+            idx = self._dispatch_out.topk_idx
+            el = max(self._dispatch_out.num_experts // max(int(self.is_token_in_rank.shape[1]), 1), 1)
+            remote = int(((idx >= 0) & (idx // el != rank)).sum())
+            out.update(pairs_sent_remote=remote, dispatch_bytes_out=remote * hidden * 2,
+                       combine_bytes_in=remote * hidden * 2)
+        return out
+
 
 class Buffer:
     """Symmetric-memory communication buffer for one expert-parallel group.

@@ -680,73 +680,103 @@ void launch_combine_reduce(void* out, const void* rows, const long long* topk_id
 // =============================================================================================
 constexpr int kRouterMaxExpertsPerLane = 16;   // up to 512 experts
 constexpr int kRouterTokens = 64;              // tokens per CTA
-constexpr int kRouterKChunk = 32;              // hidden elements per shared-memory step
+constexpr int kRouterKChunk = 64;              // hidden elements per shared-memory step (128 bytes of a row)
+constexpr int kRouterLd = kRouterKChunk + 4;   // padded row: float4 reads of 8 consecutive rows hit 32 different banks
 
-// One CTA routes 64 tokens: a register-tiled fp32 GEMM (4 tokens x 4 experts per thread, operands staged
-// k-major in shared memory) produces the logits of 64 experts at a time into shared memory; then each
-// warp finishes 8 tokens: softmax over all experts, top-k by repeated arg-max, renormalise, rank bitmap.
+// One CTA routes 64 tokens.  Logits: a register-tiled fp32 GEMM, 16 x 16 threads with 4 tokens x JE experts
+// each, so one pass covers 16 * JE experts (16 / 32 / 64; wider expert counts loop).  Operands are fetched
+// 128 contiguous bytes per row (8 lanes per row), converted to fp32 and kept row-major in shared memory; the
+// next chunk's global loads are in flight while the current chunk is multiplied.  Then each warp finishes 8
+// tokens: softmax over all experts, top-k by repeated arg-max, renormalise, rank bitmap.
+template <int JE>
 __global__ void __launch_bounds__(256) router_kernel(const RouterParams p) {
+  constexpr int NE = 16 * JE;                                      // experts per pass
+  constexpr int EPL = JE == 4 ? kRouterMaxExpertsPerLane : 1;      // experts per lane in the softmax / top-k part
+  constexpr int XV = kRouterTokens * 8 / 256;                      // 16-byte loads of x per thread and chunk (2)
+  constexpr int WV = (NE * 8 + 255) / 256;                         // ... of the gate weights (1 or 2)
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  float* xs = reinterpret_cast<float*>(smem_raw);                 // [kRouterKChunk][64 tokens]
-  float* ws = xs + kRouterKChunk * kRouterTokens;                 // [kRouterKChunk][64 experts]
-  float* logits = ws + kRouterKChunk * 64;                        // [64 tokens][E_pad]
+  float* xs = reinterpret_cast<float*>(smem_raw);                 // [64 tokens][kRouterLd]
+  float* ws = xs + kRouterTokens * kRouterLd;                     // [NE experts][kRouterLd]
+  float* logits = ws + NE * kRouterLd;                            // [64 tokens][e_pad]
   const int E = p.num_experts, H = p.hidden, K = p.num_topk;
-  const int e_pad = (E + 63) / 64 * 64 + 1;                       // +1: rows start in different banks
+  const int e_pad = (E + NE - 1) / NE * NE + 1;                   // +1: rows start in different banks
   const int e_local = E / p.num_ranks;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int ty = tid >> 4, tx = tid & 15;                          // 16 x 16 threads, 4 x 4 outputs each
+  const int ty = tid >> 4, tx = tid & 15;
   const __nv_bfloat16* xg = static_cast<const __nv_bfloat16*>(p.x);
   const __nv_bfloat16* wg = static_cast<const __nv_bfloat16*>(p.w_gate);
   const int t0 = blockIdx.x * kRouterTokens;
-  const int ld_row = tid & 63, ld_kc = (tid >> 6) * 8;             // loader: row 0..63, 8 consecutive k
 
-  for (int e0 = 0; e0 < E; e0 += 64) {
-    float acc[4][4];
+  for (int e0 = 0; e0 < E; e0 += NE) {
+    float acc[4][JE];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-    for (int k0 = 0; k0 < H; k0 += kRouterKChunk) {
-      uint4 xv = make_uint4(0, 0, 0, 0), wv = make_uint4(0, 0, 0, 0);
-      const int kk = k0 + ld_kc;
-      if (t0 + ld_row < p.num_tokens && kk < H) xv = ld_nc_v4(xg + static_cast<size_t>(t0 + ld_row) * H + kk);
-      if (e0 + ld_row < E && kk < H) wv = __ldg(reinterpret_cast<const uint4*>(wg + static_cast<size_t>(e0 + ld_row) * H + kk));
-      __syncthreads();   // previous step's tiles are no longer read
-      const uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w}, wu[4] = {wv.x, wv.y, wv.z, wv.w};
+      for (int j = 0; j < JE; ++j) acc[i][j] = 0.f;
+    uint4 xv[XV], wv[WV];
+    auto fetch = [&](int k0) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 a = unpack_bf16x2(xu[j]), b = unpack_bf16x2(wu[j]);
-        xs[(ld_kc + 2 * j) * kRouterTokens + ld_row] = a.x;
-        xs[(ld_kc + 2 * j + 1) * kRouterTokens + ld_row] = a.y;
-        ws[(ld_kc + 2 * j) * 64 + ld_row] = b.x;
-        ws[(ld_kc + 2 * j + 1) * 64 + ld_row] = b.y;
+      for (int i = 0; i < XV; ++i) {
+        const int idx = tid + 256 * i, row = idx >> 3, kk = k0 + (idx & 7) * 8;
+        xv[i] = (t0 + row < p.num_tokens && kk < H) ? ld_nc_v4(xg + static_cast<size_t>(t0 + row) * H + kk)
+                                                    : make_uint4(0, 0, 0, 0);
       }
-      __syncthreads();
 #pragma unroll
-      for (int k = 0; k < kRouterKChunk; ++k) {
-        const float4 a = *reinterpret_cast<const float4*>(xs + k * kRouterTokens + ty * 4);
-        const float4 b = *reinterpret_cast<const float4*>(ws + k * 64 + tx * 4);
-        const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+      for (int i = 0; i < WV; ++i) {
+        const int idx = tid + 256 * i, row = idx >> 3, kk = k0 + (idx & 7) * 8;
+        wv[i] = (row < NE && e0 + row < E && kk < H)
+                    ? __ldg(reinterpret_cast<const uint4*>(wg + static_cast<size_t>(e0 + row) * H + kk))
+                    : make_uint4(0, 0, 0, 0);
+      }
+    };
+    auto stash = [&](float* dst, const uint4& v, int idx) {
+      const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+      float4* o = reinterpret_cast<float4*>(dst + (idx >> 3) * kRouterLd + (idx & 7) * 8);
+      o[0] = make_float4(a.x, a.y, b.x, b.y);
+      o[1] = make_float4(c.x, c.y, d.x, d.y);
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < H; k0 += kRouterKChunk) {
+      __syncthreads();   // the previous chunk's tiles are no longer read
+#pragma unroll
+      for (int i = 0; i < XV; ++i) stash(xs, xv[i], tid + 256 * i);
+#pragma unroll
+      for (int i = 0; i < WV; ++i)
+        if (tid + 256 * i < NE * 8) stash(ws, wv[i], tid + 256 * i);
+      __syncthreads();
+      if (k0 + kRouterKChunk < H) fetch(k0 + kRouterKChunk);      // in flight during the multiply below
+#pragma unroll 4
+      for (int k = 0; k < kRouterKChunk; k += 4) {
+        float4 a[4], b[JE];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(xs + (ty * 4 + i) * kRouterLd + k);
+#pragma unroll
+        for (int j = 0; j < JE; ++j) b[j] = *reinterpret_cast<const float4*>(ws + (j * 16 + tx) * kRouterLd + k);   // lanes on consecutive rows: no bank conflict
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
-          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+          for (int j = 0; j < JE; ++j) {
+            acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
+            acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
+            acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
+            acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
+          }
       }
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) logits[(ty * 4 + i) * e_pad + e0 + tx * 4 + j] = acc[i][j];
+      for (int j = 0; j < JE; ++j) logits[(ty * 4 + i) * e_pad + e0 + j * 16 + tx] = acc[i][j];
   }
   __syncthreads();
 
   for (int tt = warp; tt < kRouterTokens; tt += 8) {
     const int t = t0 + tt;
     if (t >= p.num_tokens) break;
-    float logit[kRouterMaxExpertsPerLane];
+    float logit[EPL];
     float mx = -INFINITY;
 #pragma unroll
-    for (int j = 0; j < kRouterMaxExpertsPerLane; ++j) {
+    for (int j = 0; j < EPL; ++j) {
       const int e = j * 32 + lane;
       logit[j] = (e < E) ? logits[tt * e_pad + e] : -INFINITY;
       mx = fmaxf(mx, logit[j]);
@@ -755,7 +785,7 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterParams p) {
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     float sum = 0.f;
 #pragma unroll
-    for (int j = 0; j < kRouterMaxExpertsPerLane; ++j) {
+    for (int j = 0; j < EPL; ++j) {
       const int e = j * 32 + lane;
       logit[j] = (e < E) ? __expf(logit[j] - mx) : 0.f;
       sum += logit[j];
@@ -764,7 +794,7 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterParams p) {
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     const float inv = 1.f / sum;
 #pragma unroll
-    for (int j = 0; j < kRouterMaxExpertsPerLane; ++j) {
+    for (int j = 0; j < EPL; ++j) {
       logit[j] *= inv;
       const int e = j * 32 + lane;
       if (p.probs != nullptr && e < E) p.probs[static_cast<size_t>(t) * E + e] = logit[j];
@@ -776,7 +806,7 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterParams p) {
     for (int k = 0; k < K; ++k) {
       float best = -1.f; int best_e = 0x7fffffff;
 #pragma unroll
-      for (int j = 0; j < kRouterMaxExpertsPerLane; ++j) {
+      for (int j = 0; j < EPL; ++j) {
         const int e = j * 32 + lane;
         if (e < E && logit[j] > best) { best = logit[j]; best_e = e; }
       }
@@ -787,7 +817,7 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterParams p) {
         if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
       }
 #pragma unroll
-      for (int j = 0; j < kRouterMaxExpertsPerLane; ++j)
+      for (int j = 0; j < EPL; ++j)
         if (j * 32 + lane == best_e) logit[j] = -2.f;
       if (lane == k) { my_w = best; my_e = best_e; }
       wsum += best;
@@ -802,13 +832,21 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterParams p) {
   }
 }
 
-void launch_router(const RouterParams& p, cudaStream_t stream) {
-  const int e_pad = (p.num_experts + 63) / 64 * 64 + 1;
-  const size_t smem = sizeof(float) * (kRouterKChunk * kRouterTokens + kRouterKChunk * 64 + static_cast<size_t>(kRouterTokens) * e_pad);
+template <int JE>
+static void launch_router_je(const RouterParams& p, cudaStream_t stream) {
+  constexpr int NE = 16 * JE;
+  const int e_pad = (p.num_experts + NE - 1) / NE * NE + 1;
+  const size_t smem = sizeof(float) * (static_cast<size_t>(kRouterTokens + NE) * kRouterLd + static_cast<size_t>(kRouterTokens) * e_pad);
   const int grid = (p.num_tokens + kRouterTokens - 1) / kRouterTokens;
   if (smem > 48 * 1024)
-    cudaFuncSetAttribute(router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  router_kernel<<<grid, 256, smem, stream>>>(p);
+    cudaFuncSetAttribute(router_kernel<JE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  router_kernel<JE><<<grid, 256, smem, stream>>>(p);
+}
+
+void launch_router(const RouterParams& p, cudaStream_t stream) {
+  if (p.num_experts <= 16) launch_router_je<1>(p, stream);
+  else if (p.num_experts <= 32) launch_router_je<2>(p, stream);
+  else launch_router_je<4>(p, stream);
 }
 
 }  // namespace sep

@@ -221,6 +221,10 @@ class Runtime {
     SEP_ASSERT(num_channels >= 1 && num_channels <= kMaxChannels, "num_channels out of range");
     SEP_ASSERT(num_experts_cap >= 1 && num_experts_cap <= kMaxExperts, "num_experts_cap out of range");
     SEP_CUDA_CHECK(cudaGetDevice(&device_));
+    // Rows are pushed in chunks of this many (token, expert) pairs, each followed by the arrival signals of
+    // the tiles it touched.  Small chunks let remote tiles complete progressively; with one rank only the
+    // signalling overhead matters and larger chunks measured faster.
+    pairs_per_chunk_ = num_ranks == 1 ? 16 : 8;
     ctl_ = make_control_layout(num_ranks, num_channels, num_experts_cap);
     arena_bytes_ = static_cast<size_t>(arena_bytes) + ctl_.total_bytes;
     arena_bytes_ = (arena_bytes_ + (2u << 20) - 1) / (2u << 20) * (2u << 20);
@@ -1003,7 +1007,7 @@ class Runtime {
   int64_t timeout_ms_ = 0;
   int epochs_[kNumKinds];
   int64_t launches_ = 0;
-  int pairs_per_chunk_ = 8;   // small chunks keep the push progressive: tiles complete in push order, not all at the end
+  int pairs_per_chunk_ = 8;
   at::Tensor dbg_fused_a_;
   int gate_issued_[8];
   bool available_ = false, destroyed_ = false;

@@ -232,3 +232,18 @@ def test_event_handle_and_stream_handles(native):
     assert buf._raw(None) == side.cuda_stream
     buf.set_compute_stream_handle(None)
     assert buf._raw(None) == torch.cuda.current_stream().cuda_stream
+
+
+def test_handle_stats(native):
+    R, T, H, K, E = 2, 200, 256, 4, 8
+    world = _world(R)
+    xs, idxs, ws = _inputs(R, T, H, K, E, seed=21, sentinel_p=0.05)
+    handles = world.dispatch(xs, idxs, ws, E)
+    torch.cuda.synchronize()
+    total_pairs = sum(int((i >= 0).sum()) for i in idxs)
+    got = [h.stats(rank=r) for r, h in enumerate(handles)]
+    assert sum(g["pairs_received"] for g in got) == total_pairs
+    for r, g in enumerate(got):
+        assert g["rows_padded"] == handles[r].TK_padded and 0.0 <= g["padding_ratio"] < 1.0
+        want_remote = int(((idxs[r] >= 0) & (idxs[r] // (E // R) != r)).sum())
+        assert g["pairs_sent_remote"] == want_remote and g["dispatch_bytes_out"] == want_remote * H * 2

@@ -252,20 +252,24 @@ def test_pool_compress_roundtrip(native):
     assert torch.equal(x_recv[case["recv_token"][valid].long()], case["pool"][valid])
 
 
-def test_router(native):
+@pytest.mark.parametrize("T,H,E,K,R", [(300, 256, 64, 6, 8), (515, 2048, 8, 6, 1), (130, 200, 24, 4, 2),
+                                       (257, 1032, 256, 8, 8), (64, 512, 136, 3, 1)])
+def test_router(native, T, H, E, K, R):
+    """Every expert-width instance of the kernel (16 / 32 / 64 experts per pass, several passes, widths that
+    are not a multiple of the chunk) against softmax -> top-k -> renormalise in fp32."""
     from streamep_b200.models.reference import router_reference
     gg = _ops()
     g = torch.Generator(device="cpu").manual_seed(20)
-    x = torch.randn(300, 256, generator=g).to(torch.bfloat16).to(DEV)
-    wg = (torch.randn(64, 256, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
-    idx, w, in_rank, probs = gg.router_topk(x, wg, 6, num_ranks=8, return_probs=True)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(DEV)
+    wg = (torch.randn(E, H, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    idx, w, in_rank, probs = gg.router_topk(x, wg, K, num_ranks=R, return_probs=True)
     torch.cuda.synchronize()
-    ridx, rw = router_reference(x, wg, 6)
+    ridx, rw = router_reference(x, wg, K)
     check_close("probs", probs, torch.softmax(x.float() @ wg.float().t(), -1), atol=1e-5, rtol=1e-3)
     # compare as sets per token (near-ties may order differently) through the weights gathered by expert id
-    dense = torch.zeros(300, 64, device=DEV).scatter_(1, idx, w)
-    rdense = torch.zeros(300, 64, device=DEV).scatter_(1, ridx, rw)
+    dense = torch.zeros(T, E, device=DEV).scatter_(1, idx, w)
+    rdense = torch.zeros(T, E, device=DEV).scatter_(1, ridx, rw)
     check_close("topk weights", dense, rdense, atol=1e-4, rtol=1e-3)
-    want_rank = torch.zeros(300, 8, dtype=torch.bool, device=DEV)
-    want_rank.scatter_(1, idx // 8, True)
+    want_rank = torch.zeros(T, R, dtype=torch.bool, device=DEV)
+    want_rank.scatter_(1, idx // (E // R), True)
     assert torch.equal(in_rank, want_rank)

@@ -5,6 +5,7 @@ same kernels with the ranks emulated in threads.  Mirrors the reference's end-to
 (stream_ep/stream_moe/validate_multi_iter.py) and tests/test_activation_checkpoint.py,
 tests/test_skewed_experts.py, tests/test_uneven_tokens_per_rank.py.
 """
+import gc
 from types import SimpleNamespace
 
 import pytest
@@ -31,6 +32,15 @@ def _make(R, tokens, H, I, E, K, seed, sentinel_p=0.0, routing="uniform"):
         elif routing == "half_empty":
             idx = torch.where(idx >= 0, idx % (E // 2), idx)
             idx = torch.where(idx >= 0, idx * 2, idx)      # only even experts; duplicates within a token allowed
+        elif routing == "uniform_rotating":
+            idx = ((torch.arange(T, device=DEV)[:, None] * K + torch.arange(K, device=DEV)[None, :] + r) % E).contiguous()
+        elif routing == "per_rank_imbalance":              # 90 % of the tokens send every pair to rank 0's experts
+            hot = torch.rand(T, generator=g) < 0.9
+            hot_idx = torch.stack([torch.randperm(E // R, generator=g)[:K] for _ in range(T)]) if T else idx.cpu()
+            idx = torch.where(hot[:, None].to(DEV), hot_idx.to(DEV), idx)
+        elif routing == "power_law":                       # Zipf(1.2) over expert ids, distinct per token
+            prob = torch.arange(1, E + 1, dtype=torch.float64).pow(-1.2)
+            idx = torch.multinomial((prob / prob.sum()).expand(max(T, 1), E), K, replacement=False, generator=g)[:T].to(DEV)
         w = w / w.sum(-1, keepdim=True)
         idxs.append(idx); ws.append(w)
         dys.append(torch.randn(T, H, generator=g).to(torch.bfloat16).to(DEV))
@@ -83,6 +93,10 @@ def test_layer_ep1_autograd(native, fused, level):
     (4, True, 2, "first_k", 200),                    # all pairs to rank 0: three ranks compute nothing
     (4, True, 0, "half_empty", 300),
     (8, True, 0, "uniform", 130),
+    (4, True, 0, "uniform_rotating", 256),
+    (4, True, 1, "per_rank_imbalance", 300),
+    (4, False, 0, "per_rank_imbalance", 300),
+    (4, True, 0, "power_law", [300, 40, 512, 129]),
 ])
 def test_layer_emulated_ranks(native, R, fused, level, routing, tokens):
     from streamep_b200 import LocalWorld
@@ -115,3 +129,43 @@ def test_layer_emulated_ranks(native, R, fused, level, routing, tokens):
         got_dw2 = torch.cat([res[r][1][3] for r in range(R)])
         check_close("dW1", got_dw1, acc[0], atol=3e-2 * float(acc[0].abs().max()), rtol=3e-2)
         check_close("dW2", got_dw2, acc[1], atol=3e-2 * float(acc[1].abs().max()), rtol=3e-2)
+
+
+def test_layer_stack_depth_and_arena_reuse(native):
+    """Several layers back to back for several steps on one buffer (the reference's
+    tests/test_pipeline_depth_stress.py without the fault injection): every layer's forward state
+    stays alive until its backward, results repeat from step to step, and the symmetric arena is
+    back to its starting level after each step."""
+    from streamep_b200 import LocalWorld
+    from streamep_b200.stream_moe import make_streams, stream_moe_func
+    T, H, I, E, K, L = 400, 256, 128, 8, 2, 6
+    w1, w2, xs, idxs, ws, dys = _make(1, T, H, I, E, K, seed=5, sentinel_p=0.02)
+    g = torch.Generator(device="cpu").manual_seed(6)
+    w1s = [(torch.randn(E, 2 * I, H, generator=g) * 0.08).to(torch.bfloat16).to(DEV).requires_grad_(True) for _ in range(L)]
+    w2s = [(torch.randn(E, H, I, generator=g) * 0.08).to(torch.bfloat16).to(DEV).requires_grad_(True) for _ in range(L)]
+    world = LocalWorld(1, arena_bytes=256 << 20)
+    buf = world.buffers[0]
+    streams = make_streams()
+    base = buf.runtime.arena_bytes_in_use()
+    outs, dxs = [], []
+    for step in range(3):
+        x = xs[0].clone().requires_grad_(True)
+        cur = x
+        for l in range(L):
+            cur = stream_moe_func(buf, cur, idxs[0], ws[0], None, w1s[l], w2s[l], streams=streams, num_experts=E,
+                                  activation_checkpoint_level=l % 3)
+        cur.backward(dys[0])
+        torch.cuda.synchronize()
+        buf.check_status()
+        assert torch.isfinite(cur.float()).all() and torch.isfinite(x.grad.float()).all()
+        for w in w1s + w2s:
+            assert w.grad is not None and torch.isfinite(w.grad.float()).all()
+            w.grad = None
+        outs.append(cur.detach().float()); dxs.append(x.grad.float())
+        del cur, x
+        gc.collect()
+        assert buf.runtime.arena_bytes_in_use() == base, "a layer leaked symmetric memory"
+    s = float(outs[0].abs().max())
+    for o, d in zip(outs[1:], dxs[1:]):
+        check_close("out repeats", o, outs[0], atol=2e-2 * s, rtol=2e-2)
+        check_close("dx repeats", d, dxs[0], atol=2e-2 * float(dxs[0].abs().max()), rtol=2e-2)
