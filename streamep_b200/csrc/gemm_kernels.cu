@@ -397,6 +397,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             for (int i = 0; i < (EPI == kEpiDswiglu ? 1 : 32); ++i) r[i] = 0;
           }
         }
+        if (EPI == kEpiStore || EPI == kEpiSwiglu) {
+          // The staging tile is reused by every chunk: the previous chunk's bulk store must have read it.
+          // Waiting here, after the accumulator fetch, instead of right after the store was issued lets the
+          // read overlap the TMEM load.
+          if (lane == 0) bulk_wait_read();
+          __syncwarp();
+        }
         if (EPI == kEpiStore) {
 #pragma unroll
           for (int q = 0; q < 4; ++q)
@@ -407,8 +414,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                          pack_bf16x2(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7])));
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) { tma_store_3d(&tmap_o0, epi_stage + (warp - 2) * Cfg::kEpiStageBytes, n, warp_row0, zc); bulk_commit(); bulk_wait_read(); }
-          __syncwarp();
+          if (lane == 0) { tma_store_3d(&tmap_o0, epi_stage + (warp - 2) * Cfg::kEpiStageBytes, n, warp_row0, zc); bulk_commit(); }
         } else if (EPI == kEpiSwiglu) {
           // columns (2i, 2i+1) = (gate_i, up_i); preact tile at +0 (64-byte rows), postact tile at +2048 (32-byte rows)
           if (p.out1 != nullptr) {
@@ -437,9 +443,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             unsigned char* sb = epi_stage + (warp - 2) * Cfg::kEpiStageBytes;
             if (p.out1 != nullptr) tma_store_3d(&tmap_o1, sb, n, warp_row0, 0);
             tma_store_3d(&tmap_o0, sb + 2048, n / 2, warp_row0, 0);
-            bulk_commit(); bulk_wait_read();
+            bulk_commit();
           }
-          __syncwarp();
         } else if (EPI == kEpiScatter) {
           // Stage two 32-column chunks side by side (128 bytes per row), then let 8 lanes handle one row so
           // that every global access - local red.add or store into a peer's landing row over NVLink - is a
@@ -456,10 +461,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (flush) {
             __syncwarp();
             const int nbase = n - hpos * 32;
+            uint4 vs[8];      // shared-memory reads first: volatile asm keeps program order, see the dSwiGLU branch
+#pragma unroll
+            for (int i = 0; i < 8; ++i) vs[i] = ld_shared_v4(stg + stage_off<128>(i * 4 + (lane >> 3), lane & 7));
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int rr = i * 4 + (lane >> 3), piece = lane & 7;
-              const uint4 v = ld_shared_v4(stg + stage_off<128>(rr, piece));
+              const uint4 v = vs[i];
               char* ptr = reinterpret_cast<char*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(dst_row), rr));
               const int o = __shfl_sync(0xffffffffu, op, rr);
               const int col = nbase + piece * 8;
@@ -480,6 +488,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
           for (int q = 0; q < 4; ++q) {       // 8 output columns per step; N is a multiple of 8
             if ((q & 1) == 0) {
+              // One 16-column half at a time, fetched where it is used: fetching both halves up front, or the
+              // first half before the preact hand-over, costs registers (spills at the 168-register cap of a
+              // 10-warp CTA) and measured 7-12 % slower.
               if (!empty) { tmem_ld_32x16(taddr + c * 32 + q * 8, rh); tmem_ld_wait(); }
               else {
 #pragma unroll
@@ -543,12 +554,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           __syncwarp();
           {
             char* din_base = reinterpret_cast<char*>(static_cast<__nv_bfloat16*>(p.out0) + static_cast<long long>(warp_row0) * p.ld0 + 2 * n);
+            // all shared-memory reads first, then all global stores: the helpers are volatile asm, which the
+            // compiler keeps in program order, so an interleaved loop would wait for every read in turn
+            uint4 v[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int rr = i * 4 + (lane >> 3), piece = lane & 7;
-              const uint4 v = ld_shared_v4(stg + stage_off<128>(rr, piece));
-              if (2 * n + piece * 8 < 2 * p.N)
-                st_global_v4(din_base + static_cast<long long>(rr) * p.ld0 * 2 + piece * 16, v.x, v.y, v.z, v.w);
+            for (int i = 0; i < 8; ++i) v[i] = ld_shared_v4(stg + stage_off<128>(i * 4 + (lane >> 3), lane & 7));
+            if (2 * n + (lane & 7) * 8 < 2 * p.N) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                st_global_v4(din_base + static_cast<long long>(i * 4 + (lane >> 3)) * p.ld0 * 2 + (lane & 7) * 16,
+                             v[i].x, v[i].y, v[i].z, v[i].w);
             }
           }
           __syncwarp();
@@ -558,12 +573,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           __syncwarp();
           {
             char* pw_base = reinterpret_cast<char*>(static_cast<__nv_bfloat16*>(p.out1) + static_cast<long long>(warp_row0) * p.ld1 + n);
+            uint4 v[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int rr = i * 8 + (lane >> 2), piece = lane & 3;
-              const uint4 v = ld_shared_v4(stg + stage_off<64>(rr, piece));
-              if (n + piece * 8 < p.N)
-                st_global_v4(pw_base + static_cast<long long>(rr) * p.ld1 * 2 + piece * 16, v.x, v.y, v.z, v.w);
+            for (int i = 0; i < 4; ++i) v[i] = ld_shared_v4(stg + stage_off<64>(i * 8 + (lane >> 2), lane & 3));
+            if (n + (lane & 3) * 8 < p.N) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                st_global_v4(pw_base + static_cast<long long>(i * 8 + (lane >> 2)) * p.ld1 * 2 + (lane & 3) * 16,
+                             v[i].x, v[i].y, v[i].z, v[i].w);
             }
           }
           __syncwarp();
