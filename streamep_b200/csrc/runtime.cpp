@@ -150,6 +150,7 @@ struct DispatchState {
   int num_tokens = 0, hidden = 0, num_topk = 0, num_experts = 0, tile_m = kTileM;
   int64_t seq = 0;
   int meta_epoch = 0, push_epoch = 0;
+  int64_t slab_off[11] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};   // byte offsets of the arrays inside meta_slab
   // sender side (regular device memory)
   at::Tensor sender_slab;
   at::Tensor pair_rank, pair_slot, token_rank_in_channel, send_recv_token, send_head, is_token_in_rank,
@@ -440,7 +441,10 @@ class Runtime {
   }
 
   // ---- dispatch: phase 2, host poll + receiver allocation + defaults --------------------------
-  void dispatch_allocate(const std::shared_ptr<DispatchState>& st) {
+  // `need_o`: allocate and zero the per-recv-token accumulator `o` (the fused layer combines in the GEMM epilogue
+  // and does not use it).  `defer_views`: create only the tensors the first GEMM launch needs; the caller
+  // creates the rest with dispatch_finish_views() once that launch is queued, off the GPU's critical path.
+  void dispatch_allocate(const std::shared_ptr<DispatchState>& st, bool need_o = true, bool defer_views = false) {
     // The metadata kernel writes the sizes to mapped pinned memory; the epoch word goes last.
     const auto t0 = std::chrono::steady_clock::now();
     bool timed_out = false;
@@ -476,43 +480,35 @@ class Runtime {
     st->tile_id_to_expert = st->tile_id_to_expert.narrow(0, 0, tiles);
     size_t off_pool = 0, off_slab = 0;   // empty tensors report a null data pointer, so offsets are tracked here
     st->pool = alloc_symmetric({TKp, H}, at::kBFloat16, false, &off_pool);
-    st->o = alloc_symmetric({Tr, H}, at::kBFloat16, true);
+    st->o = need_o ? alloc_symmetric({Tr, H}, at::kBFloat16, true) : at::empty({0, H}, opts);
     // one arena block for everything small that peers write
     auto al = [](int64_t b) { return (b + 255) / 256 * 256; };
     const int64_t b_w = al(TKp * 4), b_rt = al(TKp * 4), b_ks = al(TKp * 4), b_src = al(TKp * 8), b_r2s = al(Tr * K * 4),
                   b_klt = al(Tr * 4), b_klr = al(Tr * 4), b_cnt = al(tiles * 4), b_rsrc = al(Tr * 8), b_done = al(Tr * 8);
     st->meta_slab = alloc_symmetric({b_w + b_rt + b_ks + b_src + b_r2s + b_klt + b_klr + b_cnt + b_rsrc + b_done}, at::kByte, false, &off_slab);
-    int64_t off = 0;
-    std::vector<unsigned long long> sub_off;
-    auto sub = [&](int64_t bytes, int64_t used, at::ScalarType dt, std::vector<int64_t> shape) {
-      auto t = st->meta_slab.narrow(0, off, used).view(dt).view(shape);
-      sub_off.push_back(off_slab + off);
-      off += bytes;
-      return t;
-    };
-    st->pool_topk_weight = sub(b_w, TKp * 4, at::kFloat, {TKp});
-    st->pool_recv_token = sub(b_rt, TKp * 4, at::kInt, {TKp});
-    st->pool_k_slot = sub(b_ks, TKp * 4, at::kInt, {TKp});
-    st->pool_src = sub(b_src, TKp * 8, at::kInt, {TKp, 2});
-    st->recv_token_to_slots = sub(b_r2s, Tr * K * 4, at::kInt, {Tr, K});
-    st->k_local_total = sub(b_klt, Tr * 4, at::kInt, {Tr});
-    st->k_local_remaining = sub(b_klr, Tr * 4, at::kInt, {Tr});
-    st->pool_arrival_count = sub(b_cnt, tiles * 4, at::kInt, {tiles});
-    st->recv_src = sub(b_rsrc, Tr * 8, at::kInt, {Tr, 2});
-    st->y_done_per_token = sub(b_done, Tr * 8, at::kLong, {Tr});
+    const int64_t sizes[10] = {b_w, b_rt, b_ks, b_src, b_r2s, b_klt, b_klr, b_cnt, b_rsrc, b_done};
+    st->slab_off[0] = 0;
+    for (int i = 0; i < 10; ++i) st->slab_off[i + 1] = st->slab_off[i] + sizes[i];
+    unsigned long long sub_off[10];
+    for (int i = 0; i < 10; ++i) sub_off[i] = off_slab + st->slab_off[i];
+    st->pool_arrival_count = slab_view(*st, 7);
+    if (!defer_views) dispatch_finish_views(st);
 
+    char* sb = st->meta_slab.numel() ? static_cast<char*>(st->meta_slab.data_ptr()) : nullptr;
+    auto at_off = [&](int i) { return sb ? sb + st->slab_off[i] : nullptr; };
     FillParams f{};
     f.total_tiles = tiles; f.tile_m = st->tile_m; f.num_local_experts = EL; f.tk_padded = TKp; f.num_recv_tokens = Tr; f.num_topk = K;
     f.expert_frequency = st->expert_frequency.data_ptr<int>();
     f.expert_pool_block_offset = st->expert_pool_block_offset.data_ptr<int>();
     f.tile_id_to_expert = st->tile_id_to_expert.data_ptr<int>(); f.pool_arrival_target = st->pool_arrival_target.data_ptr<int>();
-    f.pool_arrival_count = st->pool_arrival_count.data_ptr<int>();
-    f.pool_recv_token = st->pool_recv_token.data_ptr<int>(); f.pool_k_slot = st->pool_k_slot.data_ptr<int>();
-    f.pool_src = reinterpret_cast<int2*>(st->pool_src.data_ptr<int>()); f.pool_topk_weight = st->pool_topk_weight.data_ptr<float>();
-    f.recv_token_to_slots = st->recv_token_to_slots.data_ptr<int>(); f.k_local_total = st->k_local_total.data_ptr<int>();
-    f.k_local_remaining = st->k_local_remaining.data_ptr<int>();
-    f.y_done_per_token = reinterpret_cast<long long*>(st->y_done_per_token.data_ptr<int64_t>());
-    f.recv_src = reinterpret_cast<int2*>(st->recv_src.data_ptr<int>());
+    f.pool_topk_weight = reinterpret_cast<float*>(at_off(0));
+    f.pool_recv_token = reinterpret_cast<int*>(at_off(1)); f.pool_k_slot = reinterpret_cast<int*>(at_off(2));
+    f.pool_src = reinterpret_cast<int2*>(at_off(3));
+    f.recv_token_to_slots = reinterpret_cast<int*>(at_off(4)); f.k_local_total = reinterpret_cast<int*>(at_off(5));
+    f.k_local_remaining = reinterpret_cast<int*>(at_off(6));
+    f.pool_arrival_count = reinterpret_cast<int*>(at_off(7));
+    f.recv_src = reinterpret_cast<int2*>(at_off(8));
+    f.y_done_per_token = reinterpret_cast<long long*>(at_off(9));
     ++launches_; launch_fill_tile_metadata(f, at::cuda::getCurrentCUDAStream());
     SEP_CUDA_CHECK(cudaGetLastError());
 
@@ -522,6 +518,24 @@ class Runtime {
     r.k_local_remaining = sub_off[6]; r.arrival_count = sub_off[7]; r.recv_src = sub_off[8];
     st->push_epoch = ++epochs_[kKindDispatch];
     st->metadata_done_event = EventHandle(at::cuda::getCurrentCUDAStream());
+  }
+
+  // The i-th array of the per-dispatch slab (order: pool_topk_weight, pool_recv_token, pool_k_slot, pool_src,
+  // recv_token_to_slots, k_local_total, k_local_remaining, pool_arrival_count, recv_src, y_done_per_token).
+  at::Tensor slab_view(const DispatchState& st, int i) const {
+    const int64_t tiles = st.total_tiles, TKp = tiles * st.tile_m, Tr = st.num_recv_tokens, K = st.num_topk;
+    const int64_t used[10] = {TKp * 4, TKp * 4, TKp * 4, TKp * 8, Tr * K * 4, Tr * 4, Tr * 4, tiles * 4, Tr * 8, Tr * 8};
+    const at::ScalarType dt[10] = {at::kFloat, at::kInt, at::kInt, at::kInt, at::kInt, at::kInt, at::kInt, at::kInt, at::kInt, at::kLong};
+    auto t = st.meta_slab.narrow(0, st.slab_off[i], used[i]).view(dt[i]);
+    if (i == 3) return t.view({TKp, 2});
+    if (i == 4) return t.view({Tr, K});
+    if (i == 8) return t.view({Tr, 2});
+    return t;
+  }
+  void dispatch_finish_views(const std::shared_ptr<DispatchState>& st) {
+    st->pool_topk_weight = slab_view(*st, 0); st->pool_recv_token = slab_view(*st, 1); st->pool_k_slot = slab_view(*st, 2);
+    st->pool_src = slab_view(*st, 3); st->recv_token_to_slots = slab_view(*st, 4); st->k_local_total = slab_view(*st, 5);
+    st->k_local_remaining = slab_view(*st, 6); st->recv_src = slab_view(*st, 8); st->y_done_per_token = slab_view(*st, 9);
   }
 
   // Extra words of the dispatch record: arena tensors of this rank that peers address by (rank, row),
@@ -823,13 +837,14 @@ class Runtime {
   std::vector<at::Tensor> fused_forward(const std::shared_ptr<DispatchState>& st, const at::Tensor& w1, const at::Tensor& w2,
                                         const at::Tensor& landing, bool store_preact, int tile_n_a, int tile_n_y,
                                         int num_sms_a, int num_sms_y) {
-    dispatch_allocate(st);
-    dispatch_set_aux(st, 0, landing);
-    const int64_t TKp = static_cast<int64_t>(st->total_tiles) * st->tile_m, I = w2.size(2), H = w2.size(1);
+    // Queued behind the metadata kernel, so the output is zeroed while the host waits for the sizes.
     auto opts = st->x.options();
+    at::Tensor out = at::zeros({static_cast<int64_t>(st->num_tokens), w2.size(1)}, opts);
+    dispatch_allocate(st, /*need_o=*/false, /*defer_views=*/true);
+    dispatch_set_aux(st, 0, landing);
+    const int64_t TKp = static_cast<int64_t>(st->total_tiles) * st->tile_m, I = w2.size(2);
     at::Tensor postact = at::empty({TKp, I}, opts);
     at::Tensor preact = store_preact ? at::empty({TKp, 2 * I}, opts) : at::Tensor();
-    at::Tensor out = at::zeros({static_cast<int64_t>(st->num_tokens), H}, opts);
     GemmArgs a;
     a.mode = kVarlenM; a.epilogue = kEpiSwiglu; a.block_n = tile_n_a; a.num_ctas = num_sms_a;
     a.a = st->pool; a.b = w1; a.tile_id_to_expert = st->tile_id_to_expert;
@@ -837,6 +852,7 @@ class Runtime {
     a.arrival_count = st->pool_arrival_count; a.arrival_target = st->pool_arrival_target;
     a.fused_push = st; a.push_flags = 3;
     grouped_gemm(a);
+    dispatch_finish_views(st);          // host work in the shadow of kernel A
     GemmArgs y;
     y.mode = kVarlenM; y.epilogue = kEpiScatter; y.block_n = tile_n_y; y.num_ctas = num_sms_y;
     y.a = postact; y.b = w2; y.tile_id_to_expert = st->tile_id_to_expert;
@@ -1135,7 +1151,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("gate_flag_tensor", &Runtime::gate_flag_tensor)
       .def("dispatch_begin", &Runtime::dispatch_begin)
       .def("dispatch_metadata", &Runtime::dispatch_metadata)
-      .def("dispatch_allocate", &Runtime::dispatch_allocate)
+      .def("dispatch_allocate", &Runtime::dispatch_allocate, py::arg("state"), py::arg("need_o") = true, py::arg("defer_views") = false)
+      .def("dispatch_finish_views", &Runtime::dispatch_finish_views)
       .def("dispatch_push", &Runtime::dispatch_push)
       .def("grads_begin", &Runtime::grads_begin)
       .def("dispatch_set_aux", &Runtime::dispatch_set_aux)
