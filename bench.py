@@ -21,7 +21,8 @@ on the launching stream and a 256 MiB buffer (larger than the 126 MB L2) is rewr
 steps, outside the event pairs; ``ms_per_step`` is the mean of the K event intervals and the
 reported value is the max over ranks.  ``e2e`` repeats the measurement through the public module API with, every step, the
 host-to-device copy of that step's inputs from pinned memory (prefetched on a copy stream, two buffers)
-and a device-to-host read of that step's loss (read on the host one step behind the launches).
+and a device-to-host read of that step's loss (read on the host one step behind the launches).  The copy of
+step i+1's input is released by the event the library records where step i's backward enters its local dW GEMMs.
 """
 from __future__ import annotations
 
@@ -193,12 +194,13 @@ def main():
         loss_ready = [torch.cuda.Event(), torch.cuda.Event()]
         copy_stream = torch.cuda.Stream()
         copied = [torch.cuda.Event(), torch.cuda.Event()]
-        consumed = [torch.cuda.Event(), torch.cuda.Event()]
         losses = []
 
-        def prefetch(i):
+        def prefetch(i, after):
+            """Copy step i's input on the copy stream once `after` has happened on the compute stream."""
             with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(consumed[i % 2])
+                if after is not None:
+                    copy_stream.wait_event(after)
                 x_in[i % 2].copy_(x_host[i % 2], non_blocking=True)
                 copied[i % 2].record(copy_stream)
 
@@ -216,18 +218,23 @@ def main():
                 cur = layer.experts(cur, *r) if zipf else layer(cur)
             loss = (cur * dy_dev).sum(dtype=torch.float32) * (1.0 / cur.numel())
             loss.backward()
-            consumed[i % 2].record()
+            # The next step's input (other buffer, last read one step ago) is copied while this step's
+            # backward runs its local dW GEMMs: the library marks that point.  Kernels that synchronise
+            # with peers at system scope run slower while a PCIe copy is in flight, so the copy is kept
+            # away from them; without the mark (baseline arm) the copy waits for the end of the step.
+            mark = buffer.local_phase_event() if buffer is not None else None
+            if mark is None:
+                mark = torch.cuda.Event()
+                mark.record()
+            prefetch(i + 1, mark)
             if not first:
                 read_loss(i - 1)            # every step's loss is read on the host, one step behind the launches
             loss_host[i % 2].copy_(loss.detach().reshape(1), non_blocking=True)
             loss_ready[i % 2].record()
-            prefetch(i + 2)
             for p in params:
                 p.grad = None
 
-        for j in range(2):
-            consumed[j].record()
-        prefetch(0); prefetch(1)
+        prefetch(0, None)
         for i in range(max(args.warmup, 3)):
             step_e2e(i, first=(i == 0))
         base = max(args.warmup, 3)

@@ -262,6 +262,14 @@ class Buffer:
         return int(per_layer * (layers_in_flight + 1.5))
 
     # ------------------------------------------------------------------ launch gates
+    def local_phase_event(self):
+        """``EventHandle`` recorded where the most recent backward finished its last kernel that talks to
+        peers (what follows are the local dW GEMMs), or ``None`` before the first backward.  A loader that
+        makes its host-to-device copy of the next batch wait on it (``copy_stream.wait_event(ev)``) overlaps
+        the copy with local compute only: kernels that synchronise with peers at system scope measured up to
+        4x slower while a PCIe copy was in flight."""
+        return self.runtime.local_phase_event()
+
     def set_compute_stream_handle(self, stream) -> None:
         """Remember the caller's compute stream (reference: csrc/stream_ep.cpp:387-456, called from
         stream_ep/stream_moe/stream_moe.py:1239).  The gate helpers wait on it when no stream is given."""

@@ -679,25 +679,27 @@ void launch_combine_reduce(void* out, const void* rows, const long long* topk_id
 // (stream_ep/stream_moe/profile_pipeline.py:102-139).
 // =============================================================================================
 constexpr int kRouterMaxExpertsPerLane = 16;   // up to 512 experts
-constexpr int kRouterTokens = 64;              // tokens per CTA
 constexpr int kRouterKChunk = 64;              // hidden elements per shared-memory step (128 bytes of a row)
 constexpr int kRouterLd = kRouterKChunk + 4;   // padded row: float4 reads of 8 consecutive rows hit 32 different banks
 
-// One CTA routes 64 tokens.  Logits: a register-tiled fp32 GEMM, 16 x 16 threads with 4 tokens x JE experts
-// each, so one pass covers 16 * JE experts (16 / 32 / 64; wider expert counts loop).  Operands are fetched
-// 128 contiguous bytes per row (8 lanes per row), converted to fp32 and kept row-major in shared memory; the
-// next chunk's global loads are in flight while the current chunk is multiplied.  Then each warp finishes 8
-// tokens: softmax over all experts, top-k by repeated arg-max, renormalise, rank bitmap.
-template <int JE>
-__global__ void __launch_bounds__(256) router_kernel(const RouterParams p) {
+// One CTA routes TOK tokens with TOK * 4 threads.  Logits: a register-tiled fp32 GEMM, (TOK / 4) x 16 threads
+// with 4 tokens x JE experts each, so one pass covers 16 * JE experts (16 / 32 / 64; wider expert counts loop).
+// Operands are fetched 128 contiguous bytes per row (8 lanes per row), converted to fp32 and kept row-major in
+// shared memory; the global loads of the next two chunks are in flight while the current one is multiplied.
+// Few experts make the kernel latency-bound, so those instances use 32 tokens per CTA (twice the CTAs); 64
+// experts per pass are FMA-bound and use 64 tokens for operand reuse.  Then each warp finishes 8 tokens:
+// softmax over all experts, top-k by repeated arg-max, renormalise, rank bitmap.
+template <int JE, int TOK>
+__global__ void __launch_bounds__(TOK * 4) router_kernel(const RouterParams p) {
+  constexpr int THREADS = TOK * 4;
   constexpr int NE = 16 * JE;                                      // experts per pass
   constexpr int EPL = JE == 4 ? kRouterMaxExpertsPerLane : 1;      // experts per lane in the softmax / top-k part
-  constexpr int XV = kRouterTokens * 8 / 256;                      // 16-byte loads of x per thread and chunk (2)
-  constexpr int WV = (NE * 8 + 255) / 256;                         // ... of the gate weights (1 or 2)
+  constexpr int XV = TOK * 8 / THREADS;                            // 16-byte loads of x per thread and chunk (2)
+  constexpr int WV = (NE * 8 + THREADS - 1) / THREADS;             // ... of the gate weights (1 or 2)
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  float* xs = reinterpret_cast<float*>(smem_raw);                 // [64 tokens][kRouterLd]
-  float* ws = xs + kRouterTokens * kRouterLd;                     // [NE experts][kRouterLd]
-  float* logits = ws + NE * kRouterLd;                            // [64 tokens][e_pad]
+  float* xs = reinterpret_cast<float*>(smem_raw);                 // [TOK tokens][kRouterLd]
+  float* ws = xs + TOK * kRouterLd;                               // [NE experts][kRouterLd]
+  float* logits = ws + NE * kRouterLd;                            // [TOK tokens][e_pad]
   const int E = p.num_experts, H = p.hidden, K = p.num_topk;
   const int e_pad = (E + NE - 1) / NE * NE + 1;                   // +1: rows start in different banks
   const int e_local = E / p.num_ranks;
@@ -705,7 +707,7 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterParams p) {
   const int ty = tid >> 4, tx = tid & 15;
   const __nv_bfloat16* xg = static_cast<const __nv_bfloat16*>(p.x);
   const __nv_bfloat16* wg = static_cast<const __nv_bfloat16*>(p.w_gate);
-  const int t0 = blockIdx.x * kRouterTokens;
+  const int t0 = blockIdx.x * TOK;
 
   for (int e0 = 0; e0 < E; e0 += NE) {
     float acc[4][JE];
@@ -713,38 +715,38 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterParams p) {
     for (int i = 0; i < 4; ++i)
 #pragma unroll
       for (int j = 0; j < JE; ++j) acc[i][j] = 0.f;
-    uint4 xv[XV], wv[WV];
-    auto fetch = [&](int k0) {
+    uint4 xv0[XV], wv0[WV], xv1[XV], wv1[WV];
+    auto fetch = [&](int k0, uint4 (&xv)[XV], uint4 (&wv)[WV]) {
 #pragma unroll
       for (int i = 0; i < XV; ++i) {
-        const int idx = tid + 256 * i, row = idx >> 3, kk = k0 + (idx & 7) * 8;
+        const int idx = tid + THREADS * i, row = idx >> 3, kk = k0 + (idx & 7) * 8;
         xv[i] = (t0 + row < p.num_tokens && kk < H) ? ld_nc_v4(xg + static_cast<size_t>(t0 + row) * H + kk)
                                                     : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
       for (int i = 0; i < WV; ++i) {
-        const int idx = tid + 256 * i, row = idx >> 3, kk = k0 + (idx & 7) * 8;
+        const int idx = tid + THREADS * i, row = idx >> 3, kk = k0 + (idx & 7) * 8;
         wv[i] = (row < NE && e0 + row < E && kk < H)
                     ? __ldg(reinterpret_cast<const uint4*>(wg + static_cast<size_t>(e0 + row) * H + kk))
                     : make_uint4(0, 0, 0, 0);
       }
     };
-    auto stash = [&](float* dst, const uint4& v, int idx) {
+    auto stash1 = [&](float* dst, const uint4& v, int idx) {
       const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
       float4* o = reinterpret_cast<float4*>(dst + (idx >> 3) * kRouterLd + (idx & 7) * 8);
       o[0] = make_float4(a.x, a.y, b.x, b.y);
       o[1] = make_float4(c.x, c.y, d.x, d.y);
     };
-    fetch(0);
-    for (int k0 = 0; k0 < H; k0 += kRouterKChunk) {
+    // one chunk: registers -> shared memory, refill the registers two chunks ahead, multiply
+    auto chunk = [&](int k_next, uint4 (&xv)[XV], uint4 (&wv)[WV]) {
       __syncthreads();   // the previous chunk's tiles are no longer read
 #pragma unroll
-      for (int i = 0; i < XV; ++i) stash(xs, xv[i], tid + 256 * i);
+      for (int i = 0; i < XV; ++i) stash1(xs, xv[i], tid + THREADS * i);
 #pragma unroll
       for (int i = 0; i < WV; ++i)
-        if (tid + 256 * i < NE * 8) stash(ws, wv[i], tid + 256 * i);
+        if (tid + THREADS * i < NE * 8) stash1(ws, wv[i], tid + THREADS * i);
       __syncthreads();
-      if (k0 + kRouterKChunk < H) fetch(k0 + kRouterKChunk);      // in flight during the multiply below
+      if (k_next < H) fetch(k_next, xv, wv);                       // in flight during this and the next multiply
 #pragma unroll 4
       for (int k = 0; k < kRouterKChunk; k += 4) {
         float4 a[4], b[JE];
@@ -762,6 +764,13 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterParams p) {
             acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
           }
       }
+    };
+    fetch(0, xv0, wv0);
+    if (kRouterKChunk < H) fetch(kRouterKChunk, xv1, wv1);
+    for (int k0 = 0; k0 < H; k0 += 2 * kRouterKChunk) {
+      chunk(k0 + 2 * kRouterKChunk, xv0, wv0);
+      if (k0 + kRouterKChunk >= H) break;
+      chunk(k0 + 3 * kRouterKChunk, xv1, wv1);
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -770,7 +779,7 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterParams p) {
   }
   __syncthreads();
 
-  for (int tt = warp; tt < kRouterTokens; tt += 8) {
+  for (int tt = warp; tt < TOK; tt += THREADS / 32) {
     const int t = t0 + tt;
     if (t >= p.num_tokens) break;
     float logit[EPL];
@@ -832,21 +841,21 @@ __global__ void __launch_bounds__(256) router_kernel(const RouterParams p) {
   }
 }
 
-template <int JE>
+template <int JE, int TOK>
 static void launch_router_je(const RouterParams& p, cudaStream_t stream) {
   constexpr int NE = 16 * JE;
   const int e_pad = (p.num_experts + NE - 1) / NE * NE + 1;
-  const size_t smem = sizeof(float) * (static_cast<size_t>(kRouterTokens + NE) * kRouterLd + static_cast<size_t>(kRouterTokens) * e_pad);
-  const int grid = (p.num_tokens + kRouterTokens - 1) / kRouterTokens;
+  const size_t smem = sizeof(float) * (static_cast<size_t>(TOK + NE) * kRouterLd + static_cast<size_t>(TOK) * e_pad);
+  const int grid = (p.num_tokens + TOK - 1) / TOK;
   if (smem > 48 * 1024)
-    cudaFuncSetAttribute(router_kernel<JE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  router_kernel<JE><<<grid, 256, smem, stream>>>(p);
+    cudaFuncSetAttribute(router_kernel<JE, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  router_kernel<JE, TOK><<<grid, TOK * 4, smem, stream>>>(p);
 }
 
 void launch_router(const RouterParams& p, cudaStream_t stream) {
-  if (p.num_experts <= 16) launch_router_je<1>(p, stream);
-  else if (p.num_experts <= 32) launch_router_je<2>(p, stream);
-  else launch_router_je<4>(p, stream);
+  if (p.num_experts <= 16) launch_router_je<1, 32>(p, stream);
+  else if (p.num_experts <= 32) launch_router_je<2, 32>(p, stream);
+  else launch_router_je<4, 64>(p, stream);
 }
 
 }  // namespace sep

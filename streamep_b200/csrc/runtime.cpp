@@ -307,6 +307,11 @@ class Runtime {
   int num_ranks() const { return num_ranks_; }
   int num_channels() const { return num_channels_; }
   int64_t launch_count() const { return launches_; }
+  // Event at the point of the current stream where the most recent backward left its last kernel that talks to
+  // peers: what follows (the dW GEMMs) is local.  A host-to-device prefetch that waits on it stays clear of the
+  // kernels that synchronise at system scope, which measured markedly slower while a PCIe copy was in flight.
+  void mark_local_phase() { local_phase_ = std::make_shared<EventHandle>(at::cuda::getCurrentCUDAStream()); }
+  std::optional<EventHandle> local_phase_event() const { return local_phase_ ? std::optional<EventHandle>(*local_phase_) : std::nullopt; }
   // Debug builds (-DSEP_EPI_TIMING): int64 [num_sms, 16] that the next fused dispatch+GEMM-A launches fill with timestamps.
   void set_debug_tensor(const at::Tensor& t) { dbg_fused_a_ = t; }
   void set_pairs_per_chunk(int n) { SEP_ASSERT(n >= 1 && n <= 32, "pairs per chunk must be 1..32"); pairs_per_chunk_ = n; }
@@ -920,6 +925,7 @@ class Runtime {
     a.tail = true; a.tail_kind = kKindGemmABwdTail; a.tail_wait = true;
     grouped_gemm(a);
     combine_reduce(dx, landing, st->topk_idx, st->num_experts);
+    mark_local_phase();
     if (tiles > 0) {
       GemmArgs d2;
       d2.mode = kVarlenK; d2.epilogue = kEpiStore; d2.block_n = tile_n_dw2; d2.a_mn_major = d2.b_mn_major = true;
@@ -1024,6 +1030,7 @@ class Runtime {
   int epochs_[kNumKinds];
   int64_t launches_ = 0;
   int pairs_per_chunk_ = 8;
+  std::shared_ptr<EventHandle> local_phase_;
   at::Tensor dbg_fused_a_;
   int gate_issued_[8];
   bool available_ = false, destroyed_ = false;
@@ -1165,6 +1172,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("get_epochs", &Runtime::get_epochs)
       .def("set_epochs", &Runtime::set_epochs)
       .def("grouped_gemm", &Runtime::grouped_gemm)
+      .def("mark_local_phase", &Runtime::mark_local_phase)
+      .def("local_phase_event", &Runtime::local_phase_event)
       .def("fused_forward", &Runtime::fused_forward)
       .def("fused_backward", &Runtime::fused_backward)
       .def("tile_producer", &Runtime::tile_producer)

@@ -365,6 +365,7 @@ def moe_backward(ctx, dL_dy):
 def _launch_dw(buffer, handle, cfg, dl_do_pool, postact_dw2, dswiglu_in, pool, dW1, dW2):
     """dW2[e] = dL_do_pool[rows_e]^T @ (w * postact)[rows_e];  dW1[e] = dL_dswiglu_in[rows_e]^T @ pool[rows_e]
     (stream_ep/stream_moe/stream_moe.py:1107-1146, including the empty-rank guard)."""
+    buffer.runtime.mark_local_phase()
     if handle.total_tiles > 0:
         gg.grouped_gemm_dw(dl_do_pool, postact_dw2, handle.expert_pool_block_offset, handle.expert_frequency,
                            out=dW2, tile_n=cfg.tile_n_dW2, buffer=buffer)
