@@ -188,6 +188,12 @@ class Buffer:
         chunk = os.environ.get("STREAM_EP_PUSH_CHUNK_PAIRS")
         if chunk:
             self.runtime.set_pairs_per_chunk(int(chunk))
+        order = os.environ.get("STREAM_EP_PUSH_ORDER")
+        if order:
+            self.runtime.set_push_order(int(order))
+        warps = os.environ.get("STREAM_EP_PUSH_WARPS")
+        if warps:
+            self.runtime.set_active_push_warps(int(warps))
 
     # ------------------------------------------------------------------ lifecycle
     def destroy(self):

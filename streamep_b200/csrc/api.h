@@ -67,6 +67,7 @@ struct MetadataParams {
   int num_tokens, num_topk, num_experts, num_ranks, rank, num_channels, tile_m;
   int epoch;                     // monotonic per-buffer collective counter
   int phase_mask;                // bit0: count + exchange + signal; bit1: wait + synthesize; bit2: materialise (own launch)
+  int push_order;                // order of send_list: 0 = (local expert, rotated dst, channel), 1 = (local expert, channel, rotated dst)
   // symmetric memory
   void* peer_base[kMaxRanks];    // arena bases (own entry included)
   ControlLayout ctl;
@@ -81,7 +82,7 @@ struct MetadataParams {
   int* send_base;                // [C, E] scratch: base slot at the owner for (channel, expert), src = this rank
   int* send_token_base;          // [C, R] scratch: first recv-token id at dst for (channel, dst)
   int* send_order_base;          // [C, E] scratch: first position in `send_list` of this rank's (channel, expert) pairs
-  int* send_list;                // [T * K] pair ids (t * K + k) in push order: (local expert, rotated dst rank, channel, t, k)
+  int* send_list;                // [T * K] pair ids (t * K + k) in push order (see push_order), then (t, k)
   int* num_send;                 // [1] number of valid pairs == used length of send_list
   int* peer_total_tiles;         // [R]
   int* peer_num_recv;            // [R]
@@ -135,6 +136,7 @@ struct PushParams {
   int epoch;
   int flags;                     // bit0 publish own record, bit1 push, bit2 tail wait for own tiles
   int pairs_per_chunk;           // pairs one warp ships between two counter releases (<= 32)
+  int active_push_warps;         // push warps per CTA of the fused kernels that take chunks (0 = all)
   void* peer_base[kMaxRanks];
   ControlLayout ctl;
   BufferRecord own;              // offsets of this rank's freshly allocated buffers (grads: only `pool`

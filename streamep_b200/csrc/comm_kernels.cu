@@ -285,35 +285,84 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
       p.recv_channel_prefix_matrix[s * C + c] = rc;
     }
   }
-  // 6. push order of this rank's pairs: experts sorted by (local index, destination rank rotated by
-  //    this rank), channels in order inside an expert.  s_off is reused as the per-expert base.
+  // 6. push order of this rank's pairs (p.push_order).
+  //    0: experts sorted by (local index, destination rank rotated by this rank), channels in order inside an
+  //       expert: long runs per destination.  s_off is reused as the per-expert base.
+  //    1: local expert index, then channel, then rotated destination, see below.
+  if (p.push_order == 0) {
+    __syncthreads();
+    for (int e = tid; e < E; e += blockDim.x) {
+      int cnt = 0;
+      for (int c = 0; c < C; ++c) cnt += ctl_inbox_counts(own, p.ctl, parity, p.rank, c)[e];
+      const int d = e / EL, el = e - d * EL;
+      s_hist[el * R + ((d - p.rank + R) % R)] = cnt;     // keyed by push order
+    }
+    __syncthreads();
+    if (warp == 0) {
+      int carry = 0;
+      for (int base = 0; base < E; base += 32) {
+        const int i = base + lane;
+        const int v = (i < E) ? s_hist[i] : 0;
+        int total;
+        const int excl = warp_excl_scan(v, lane, total);
+        if (i < E) s_off[i] = carry + excl;
+        carry += total;
+      }
+      if (lane == 0) *p.num_send = carry;
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += blockDim.x) {
+      const int d = e / EL, el = e - d * EL;
+      int run = s_off[el * R + ((d - p.rank + R) % R)];
+      for (int c = 0; c < C; ++c) {
+        p.send_order_base[static_cast<size_t>(c) * E + e] = run;
+        run += ctl_inbox_counts(own, p.ctl, parity, p.rank, c)[e];
+      }
+    }
+    return;
+  }
+  // 6. push order of this rank's pairs: local expert index first, then channel, then destination rank (rotated
+  //    by this rank so that the sources do not all write to the same peer at once).  Slots inside an expert
+  //    are laid out channel-major on every destination, so this order sends the rows of tile 0 of expert 0 of
+  //    every destination first, then tile 1, ...: all sources fill the same tiles at the same time and tiles
+  //    complete in the order the GEMM consumes them, from the first microseconds of the push.
+  //    s_hist[el] = pairs of local expert index el over all destinations; s_off[el] = its exclusive prefix.
   __syncthreads();
-  for (int e = tid; e < E; e += blockDim.x) {
-    int cnt = 0;
-    for (int c = 0; c < C; ++c) cnt += ctl_inbox_counts(own, p.ctl, parity, p.rank, c)[e];
-    const int d = e / EL, el = e - d * EL;
-    s_hist[el * R + ((d - p.rank + R) % R)] = cnt;     // keyed by push order
+  for (int el = warp; el < EL; el += num_warps) {
+    int acc = 0;
+    for (int i = lane; i < C * R; i += 32) {
+      const int c = i / R, d = i - c * R;
+      acc += ctl_inbox_counts(own, p.ctl, parity, p.rank, c)[d * EL + el];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) s_hist[el] = acc;
   }
   __syncthreads();
   if (warp == 0) {
     int carry = 0;
-    for (int base = 0; base < E; base += 32) {
+    for (int base = 0; base < EL; base += 32) {
       const int i = base + lane;
-      const int v = (i < E) ? s_hist[i] : 0;
+      const int v = (i < EL) ? s_hist[i] : 0;
       int total;
       const int excl = warp_excl_scan(v, lane, total);
-      if (i < E) s_off[i] = carry + excl;
+      if (i < EL) s_off[i] = carry + excl;
       carry += total;
     }
     if (lane == 0) *p.num_send = carry;
   }
   __syncthreads();
-  for (int e = tid; e < E; e += blockDim.x) {
-    const int d = e / EL, el = e - d * EL;
-    int run = s_off[el * R + ((d - p.rank + R) % R)];
-    for (int c = 0; c < C; ++c) {
-      p.send_order_base[static_cast<size_t>(c) * E + e] = run;
-      run += ctl_inbox_counts(own, p.ctl, parity, p.rank, c)[e];
+  for (int el = warp; el < EL; el += num_warps) {
+    int carry = s_off[el];
+    for (int base = 0; base < C * R; base += 32) {
+      const int i = base + lane;
+      const int c = i / R, drot = i - c * R;
+      const int d = (drot + p.rank) % R;
+      const int v = (i < C * R) ? ctl_inbox_counts(own, p.ctl, parity, p.rank, c)[d * EL + el] : 0;
+      int total;
+      const int excl = warp_excl_scan(v, lane, total);
+      if (i < C * R) p.send_order_base[static_cast<size_t>(c) * E + d * EL + el] = carry + excl;
+      carry += total;
     }
   }
 }

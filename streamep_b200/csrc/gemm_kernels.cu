@@ -640,7 +640,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         else resolve_push_targets(s_tg, lane, pp.peer_base[lane], rec);
       }
       asm volatile("bar.sync 2, %0;" :: "r"(push_warps(EPI) * 32) : "memory");
-      if (s_push_ok) {
+      if (s_push_ok && (pp.active_push_warps <= 0 || pw < pp.active_push_warps)) {
         const int ppc = pp.pairs_per_chunk;
         const int num_send = *pp.num_send;
         const int num_chunks = (num_send + ppc - 1) / ppc;

@@ -314,6 +314,8 @@ class Runtime {
   std::optional<EventHandle> local_phase_event() const { return local_phase_ ? std::optional<EventHandle>(*local_phase_) : std::nullopt; }
   // Debug builds (-DSEP_EPI_TIMING): int64 [num_sms, 16] that the next fused dispatch+GEMM-A launches fill with timestamps.
   void set_debug_tensor(const at::Tensor& t) { dbg_fused_a_ = t; }
+  void set_push_order(int n) { SEP_ASSERT(n == 0 || n == 1, "push order must be 0 or 1"); push_order_ = n; }
+  void set_active_push_warps(int n) { SEP_ASSERT(n >= 0 && n <= 16, "active push warps must be 0..16"); active_push_warps_ = n; }
   void set_pairs_per_chunk(int n) { SEP_ASSERT(n >= 1 && n <= 32, "pairs per chunk must be 1..32"); pairs_per_chunk_ = n; }
   int64_t arena_bytes_in_use() const { return static_cast<int64_t>(arena_->bytes_in_use()); }
   int64_t arena_high_water() const { return static_cast<int64_t>(arena_->high_water()); }
@@ -423,7 +425,7 @@ class Runtime {
     p.topk_idx = st->topk_idx.data_ptr<int64_t>() ? reinterpret_cast<const long long*>(st->topk_idx.data_ptr<int64_t>()) : nullptr;
     p.num_tokens = st->num_tokens; p.num_topk = st->num_topk; p.num_experts = st->num_experts;
     p.num_ranks = num_ranks_; p.rank = rank_; p.num_channels = num_channels_; p.tile_m = st->tile_m;
-    p.epoch = st->meta_epoch; p.phase_mask = phase_mask;
+    p.epoch = st->meta_epoch; p.phase_mask = phase_mask; p.push_order = push_order_;
     fill_peers(p.peer_base); p.ctl = ctl_;
     p.pair_rank = st->pair_rank.data_ptr<int>(); p.pair_slot = st->pair_slot.data_ptr<int>();
     p.token_rank_in_channel = st->token_rank_in_channel.data_ptr<int>();
@@ -567,7 +569,7 @@ class Runtime {
     p.num_tokens = st.num_tokens; p.hidden = st.hidden; p.num_topk = st.num_topk; p.num_experts = st.num_experts;
     p.num_ranks = num_ranks_; p.rank = rank_; p.tile_m = st.tile_m;
     p.is_grads = is_grads ? 1 : 0; p.kind = kind; p.epoch = epoch; p.flags = flags;
-    p.pairs_per_chunk = pairs_per_chunk_;
+    p.pairs_per_chunk = pairs_per_chunk_; p.active_push_warps = active_push_warps_;
     fill_peers(p.peer_base); p.ctl = ctl_; p.own = rec;
     p.own_arrival_count = own_count; p.own_arrival_target = st.pool_arrival_target.data_ptr<int>();
     p.own_total_tiles = st.total_tiles;
@@ -1030,6 +1032,8 @@ class Runtime {
   int epochs_[kNumKinds];
   int64_t launches_ = 0;
   int pairs_per_chunk_ = 8;
+  int active_push_warps_ = 0;
+  int push_order_ = 0;
   std::shared_ptr<EventHandle> local_phase_;
   at::Tensor dbg_fused_a_;
   int gate_issued_[8];
@@ -1144,6 +1148,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("launch_count", &Runtime::launch_count)
       .def("set_debug_tensor", &Runtime::set_debug_tensor)
       .def("set_pairs_per_chunk", &Runtime::set_pairs_per_chunk)
+      .def("set_active_push_warps", &Runtime::set_active_push_warps)
+      .def("set_push_order", &Runtime::set_push_order)
       .def("arena_bytes_in_use", &Runtime::arena_bytes_in_use)
       .def("arena_high_water", &Runtime::arena_high_water)
       .def("arena_capacity", &Runtime::arena_capacity)
