@@ -219,12 +219,15 @@ struct RouterParams {
   float* probs;         // optional [T, E] softmax output (for the backward), may be null
 };
 void launch_router(const RouterParams& p, cudaStream_t stream);
+// Second half of the tensor-core router: softmax / top-k / rank bitmap from fp32 logits [T, ld_logits] that the
+// grouped GEMM wrote with its fp32 store epilogue (p.x / p.w_gate are not read).
+void launch_router_finish(const RouterParams& p, const float* logits, int ld_logits, cudaStream_t stream);
 
 // ---------------------------------------------------------------------------------------------
 // Grouped GEMM on tcgen05 / TMEM
 // ---------------------------------------------------------------------------------------------
 enum GemmMode : int { kVarlenM = 0, kVarlenK = 1 };
-enum GemmEpilogue : int { kEpiStore = 0, kEpiSwiglu = 1, kEpiScatter = 2, kEpiDswiglu = 3 };
+enum GemmEpilogue : int { kEpiStore = 0, kEpiSwiglu = 1, kEpiScatter = 2, kEpiDswiglu = 3, kEpiStoreF32 = 4 };
 
 struct TailSignal {              // end-of-kernel "all my remote writes are done" handshake
   int enabled;

@@ -731,6 +731,70 @@ constexpr int kRouterMaxExpertsPerLane = 16;   // up to 512 experts
 constexpr int kRouterKChunk = 64;              // hidden elements per shared-memory step (128 bytes of a row)
 constexpr int kRouterLd = kRouterKChunk + 4;   // padded row: float4 reads of 8 consecutive rows hit 32 different banks
 
+// One warp finishes one token from its fp32 logits (shared or global memory): softmax over all experts, top-k by
+// repeated arg-max (ties -> lowest expert id), renormalise, rank bitmap.  EPL = experts per lane.
+template <int EPL>
+__device__ __forceinline__ void route_token(const RouterParams& p, const float* row, int t, int lane) {
+  const int E = p.num_experts, K = p.num_topk;
+  const int e_local = E / p.num_ranks;
+  float logit[EPL];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    const int e = j * 32 + lane;
+    logit[j] = (e < E) ? row[e] : -INFINITY;
+    mx = fmaxf(mx, logit[j]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    const int e = j * 32 + lane;
+    logit[j] = (e < E) ? __expf(logit[j] - mx) : 0.f;
+    sum += logit[j];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float inv = 1.f / sum;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    logit[j] *= inv;
+    const int e = j * 32 + lane;
+    if (p.probs != nullptr && e < E) p.probs[static_cast<size_t>(t) * E + e] = logit[j];
+  }
+  // top-k by repeated arg-max (ties -> lowest expert id)
+  float wsum = 0.f, my_w = 0.f;
+  int my_e = -1;
+  unsigned rank_mask = 0;
+  for (int k = 0; k < K; ++k) {
+    float best = -1.f; int best_e = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      const int e = j * 32 + lane;
+      if (e < E && logit[j] > best) { best = logit[j]; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+#pragma unroll
+    for (int j = 0; j < EPL; ++j)
+      if (j * 32 + lane == best_e) logit[j] = -2.f;
+    if (lane == k) { my_w = best; my_e = best_e; }
+    wsum += best;
+    rank_mask |= 1u << (best_e / e_local);
+  }
+  if (lane < K) {
+    p.topk_idx[static_cast<size_t>(t) * K + lane] = my_e;
+    p.topk_weights[static_cast<size_t>(t) * K + lane] = p.renormalize ? my_w / wsum : my_w;
+  }
+  if (lane < p.num_ranks && p.is_token_in_rank != nullptr)
+    p.is_token_in_rank[static_cast<size_t>(t) * p.num_ranks + lane] = (rank_mask >> lane) & 1u;
+}
+
 // One CTA routes TOK tokens with TOK * 4 threads.  Logits: a register-tiled fp32 GEMM, (TOK / 4) x 16 threads
 // with 4 tokens x JE experts each, so one pass covers 16 * JE experts (16 / 32 / 64; wider expert counts loop).
 // Operands are fetched 128 contiguous bytes per row (8 lanes per row), converted to fp32 and kept row-major in
@@ -749,9 +813,8 @@ __global__ void __launch_bounds__(TOK * 4) router_kernel(const RouterParams p) {
   float* xs = reinterpret_cast<float*>(smem_raw);                 // [TOK tokens][kRouterLd]
   float* ws = xs + TOK * kRouterLd;                               // [NE experts][kRouterLd]
   float* logits = ws + NE * kRouterLd;                            // [TOK tokens][e_pad]
-  const int E = p.num_experts, H = p.hidden, K = p.num_topk;
+  const int E = p.num_experts, H = p.hidden;
   const int e_pad = (E + NE - 1) / NE * NE + 1;                   // +1: rows start in different banks
-  const int e_local = E / p.num_ranks;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int ty = tid >> 4, tx = tid & 15;
   const __nv_bfloat16* xg = static_cast<const __nv_bfloat16*>(p.x);
@@ -831,63 +894,24 @@ __global__ void __launch_bounds__(TOK * 4) router_kernel(const RouterParams p) {
   for (int tt = warp; tt < TOK; tt += THREADS / 32) {
     const int t = t0 + tt;
     if (t >= p.num_tokens) break;
-    float logit[EPL];
-    float mx = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      const int e = j * 32 + lane;
-      logit[j] = (e < E) ? logits[tt * e_pad + e] : -INFINITY;
-      mx = fmaxf(mx, logit[j]);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    float sum = 0.f;
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      const int e = j * 32 + lane;
-      logit[j] = (e < E) ? __expf(logit[j] - mx) : 0.f;
-      sum += logit[j];
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    const float inv = 1.f / sum;
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      logit[j] *= inv;
-      const int e = j * 32 + lane;
-      if (p.probs != nullptr && e < E) p.probs[static_cast<size_t>(t) * E + e] = logit[j];
-    }
-    // top-k by repeated arg-max (ties -> lowest expert id)
-    float wsum = 0.f, my_w = 0.f;
-    int my_e = -1;
-    unsigned rank_mask = 0;
-    for (int k = 0; k < K; ++k) {
-      float best = -1.f; int best_e = 0x7fffffff;
-#pragma unroll
-      for (int j = 0; j < EPL; ++j) {
-        const int e = j * 32 + lane;
-        if (e < E && logit[j] > best) { best = logit[j]; best_e = e; }
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-        if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
-      }
-#pragma unroll
-      for (int j = 0; j < EPL; ++j)
-        if (j * 32 + lane == best_e) logit[j] = -2.f;
-      if (lane == k) { my_w = best; my_e = best_e; }
-      wsum += best;
-      rank_mask |= 1u << (best_e / e_local);
-    }
-    if (lane < K) {
-      p.topk_idx[static_cast<size_t>(t) * K + lane] = my_e;
-      p.topk_weights[static_cast<size_t>(t) * K + lane] = p.renormalize ? my_w / wsum : my_w;
-    }
-    if (lane < p.num_ranks && p.is_token_in_rank != nullptr)
-      p.is_token_in_rank[static_cast<size_t>(t) * p.num_ranks + lane] = (rank_mask >> lane) & 1u;
+    route_token<EPL>(p, logits + tt * e_pad, t, lane);
   }
+}
+
+// Second half of the tensor-core router: one warp per token reads the fp32 logits the grouped GEMM stored.
+template <int EPL>
+__global__ void __launch_bounds__(256) router_finish_kernel(const RouterParams p, const float* __restrict__ logits, int ld) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= p.num_tokens) return;
+  route_token<EPL>(p, logits + static_cast<size_t>(t) * ld, t, lane);
+}
+
+void launch_router_finish(const RouterParams& p, const float* logits, int ld_logits, cudaStream_t stream) {
+  const int grid = (p.num_tokens + 7) / 8;
+  if (p.num_experts <= 32) router_finish_kernel<1><<<grid, 256, 0, stream>>>(p, logits, ld_logits);
+  else if (p.num_experts <= 128) router_finish_kernel<4><<<grid, 256, 0, stream>>>(p, logits, ld_logits);
+  else router_finish_kernel<kRouterMaxExpertsPerLane><<<grid, 256, 0, stream>>>(p, logits, ld_logits);
 }
 
 template <int JE, int TOK>

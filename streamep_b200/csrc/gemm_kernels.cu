@@ -478,6 +478,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
             __syncwarp();
           }
+        } else if (EPI == kEpiStoreF32) {
+          // fp32 accumulator values as they are (router logits): a thread owns a row, so its 32 columns are
+          // one full 128-byte line of the output row.  Rows past the end of A are TMA zero fill: not stored.
+          if (grow < p.total_rows) {
+            float* dst = static_cast<float*>(p.out0) + grow * p.ld0 + n;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              if (n + q * 4 < p.N) st_global_v4(dst + q * 4, r[q * 4], r[q * 4 + 1], r[q * 4 + 2], r[q * 4 + 3]);
+          }
         } else {   // kEpiDswiglu: r = g[row, n..n+32) = dL/d(postact) before the topk weight
           uint32_t o_pw[16];
           unsigned char* sb = epi_stage + (warp - 2) * Cfg::kEpiStageBytes;
@@ -721,6 +730,7 @@ static bool dispatch_layout(const GemmParams& p, const CUtensorMap& ta, const CU
     if constexpr (!PUSH) {
       if (p.epilogue == kEpiStore) { launch_instance<BN, false, false, kEpiStore, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
       if (p.epilogue == kEpiScatter) { launch_instance<BN, false, false, kEpiScatter, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
+      if (p.epilogue == kEpiStoreF32) { launch_instance<BN, false, false, kEpiStoreF32, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
     }
   }
   if (p.mode == kVarlenM && !p.a_mn_major && p.b_mn_major) {

@@ -699,7 +699,8 @@ class Runtime {
       SEP_ASSERT(K % 8 == 0 && N % 8 == 0, "K and N must be multiples of 8");
       p.N = N; p.K = K; p.num_experts = E; p.total_rows = rows;
       p.num_m_tiles = a.num_m_tiles >= 0 ? a.num_m_tiles : a.tile_id_to_expert->numel();
-      SEP_ASSERT(static_cast<int64_t>(p.num_m_tiles) * BM_ <= rows, "tile list longer than A");
+      // (the fp32-store epilogue guards rows itself: its last tile may hang over the end of A, TMA zero-fills it)
+      SEP_ASSERT(static_cast<int64_t>(p.num_m_tiles) * BM_ <= rows || a.epilogue == kEpiStoreF32, "tile list longer than A");
       p.num_n_tiles = (N + BN - 1) / BN;
       p.tile_id_to_expert = a.tile_id_to_expert->data_ptr<int>();
       if (rows == 0) { launch_without_tiles(a); return; }
@@ -764,7 +765,8 @@ class Runtime {
         SEP_ASSERT(p.row_src != nullptr && p.row_k_slot != nullptr && p.tile_stripes_done != nullptr && p.dl_dweight != nullptr,
                    "dL/dweight return needs pool_src, pool_k_slot, stripe counters and dl_dweight");
     }
-    if (a.epilogue == kEpiSwiglu || a.epilogue == kEpiStore) SEP_ASSERT(p.out0 != nullptr, "this epilogue needs out0");
+    if (a.epilogue == kEpiSwiglu || a.epilogue == kEpiStore || a.epilogue == kEpiStoreF32) SEP_ASSERT(p.out0 != nullptr, "this epilogue needs out0");
+    if (a.epilogue == kEpiStoreF32) SEP_ASSERT(a.out0->scalar_type() == at::kFloat && p.ld0 % 4 == 0, "the fp32 store epilogue writes float rows of a multiple of 4 elements");
     if (a.tail) {
       p.tail.enabled = 1; p.tail.kind = a.tail_kind; p.tail.epoch = ++epochs_[a.tail_kind];
       p.tail.wait = a.tail_wait ? 1 : 0;
@@ -990,10 +992,30 @@ class Runtime {
     p.topk_idx = reinterpret_cast<long long*>(idx.data_ptr<int64_t>()); p.topk_weights = w.data_ptr<float>();
     p.is_token_in_rank = reinterpret_cast<unsigned char*>(in_rank.data_ptr<bool>());
     p.probs = want_probs ? probs.data_ptr<float>() : nullptr;
-    if (p.num_tokens > 0) ++launches_, launch_router(p, at::cuda::getCurrentCUDAStream());
+    if (p.num_tokens > 0) {
+      const int64_t T = x.size(0), E = w_gate.size(0);
+      if (router_on_tensor_cores_ && E % 8 == 0 && E <= 256 && x.size(1) % 64 == 0) {
+        // Logits on the tensor cores: the grouped GEMM with x as the only "expert group" and W_gate as its weight,
+        // fp32 accumulators stored as they are (bf16 x bf16 products are exact in fp32, so this matches an fp32
+        // GEMM up to summation order); then one warp per token for softmax / top-k.
+        const int64_t tiles = (T + BM_ - 1) / BM_;
+        if (!router_tiles_.defined() || router_tiles_.numel() < tiles)
+          router_tiles_ = at::zeros({std::max<int64_t>(tiles, 64)}, x.options().dtype(at::kInt));
+        at::Tensor logits = at::empty({T, E}, x.options().dtype(at::kFloat));
+        GemmArgs g;
+        g.mode = kVarlenM; g.epilogue = kEpiStoreF32; g.block_n = E > 128 ? 256 : 128;
+        g.a = x; g.b = w_gate.unsqueeze(0); g.tile_id_to_expert = router_tiles_.narrow(0, 0, tiles); g.out0 = logits;
+        grouped_gemm(g);
+        ++launches_; launch_router_finish(p, logits.data_ptr<float>(), static_cast<int>(E), at::cuda::getCurrentCUDAStream());
+      } else {
+        ++launches_; launch_router(p, at::cuda::getCurrentCUDAStream());
+      }
+    }
     SEP_CUDA_CHECK(cudaGetLastError());
     return {idx, w, in_rank, probs};
   }
+  // false: always the SIMT router kernel (also used for expert counts the GEMM path does not take)
+  void set_router_on_tensor_cores(bool on) { router_on_tensor_cores_ = on; }
 
  private:
   static constexpr int BM_ = kTileM;
@@ -1033,6 +1055,8 @@ class Runtime {
   int64_t launches_ = 0;
   int pairs_per_chunk_ = 8;
   int active_push_warps_ = 0;
+  bool router_on_tensor_cores_ = true;
+  at::Tensor router_tiles_;            // zeros: every M tile of the router GEMM belongs to "expert" 0
   int push_order_ = 0;
   std::shared_ptr<EventHandle> local_phase_;
   at::Tensor dbg_fused_a_;
@@ -1150,6 +1174,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_pairs_per_chunk", &Runtime::set_pairs_per_chunk)
       .def("set_active_push_warps", &Runtime::set_active_push_warps)
       .def("set_push_order", &Runtime::set_push_order)
+      .def("set_router_on_tensor_cores", &Runtime::set_router_on_tensor_cores)
       .def("arena_bytes_in_use", &Runtime::arena_bytes_in_use)
       .def("arena_high_water", &Runtime::arena_high_water)
       .def("arena_capacity", &Runtime::arena_capacity)

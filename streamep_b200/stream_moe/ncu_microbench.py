@@ -95,6 +95,11 @@ def make_launcher(kernel, c, tile_n=None):
     if kernel == "dw2":
         return (lambda: gg.grouped_gemm_dw(c["pool"], c["postact"], c["offsets"], c["freqs"], out=c["dw2"], tile_n=tile_n)), \
             2.0 * pairs * H * I, pairs * (I + H) * 2 + c["w2"].numel() * 2
+    if kernel == "router":   # tokens = rows, experts = --router-experts, top-6
+        E = c["router_experts"]
+        g = torch.Generator(device="cpu").manual_seed(3)
+        wg = (torch.randn(E, H, generator=g) * 0.02).to(torch.bfloat16).to(c["pool"].device)
+        return (lambda: gg.router_topk(c["pool"], wg, min(6, E), num_ranks=1)), 2.0 * rows * H * E, rows * H * 2 + E * H * 2
     if kernel == "cublas":   # yardstick: the library GEMM of kernel A's FLOPs (one expert's weights)
         w = c["w1"][0]
         return (lambda: torch.matmul(c["pool"], w.t())), 2.0 * pairs * H * 2 * I, pairs * (H + 2 * I) * 2 + w.numel() * 2
@@ -125,11 +130,13 @@ def main():
     ap.add_argument("--experts", type=int, default=8)
     ap.add_argument("--rows-per-expert", type=int, default=6144)
     ap.add_argument("--tile-n", type=int, default=None)
+    ap.add_argument("--router-experts", type=int, default=64, help="expert count of --kernel router (not part of 'all')")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
     peak_tf, peak_bw, label = _peaks()
     c = build_case(args.hidden, args.ffn, args.experts, args.rows_per_expert)
+    c["router_experts"] = args.router_experts
     names = KERNELS if args.kernel == "all" else (args.kernel,)
     for name in names:
         fn, flops, nbytes = make_launcher(name, c, args.tile_n)

@@ -254,16 +254,23 @@ def test_pool_compress_roundtrip(native):
 
 @pytest.mark.parametrize("T,H,E,K,R", [(300, 256, 64, 6, 8), (515, 2048, 8, 6, 1), (130, 200, 24, 4, 2),
                                        (257, 1032, 256, 8, 8), (64, 512, 136, 3, 1)])
-def test_router(native, T, H, E, K, R):
-    """Every expert-width instance of the kernel (16 / 32 / 64 experts per pass, several passes, widths that
-    are not a multiple of the chunk) against softmax -> top-k -> renormalise in fp32."""
+@pytest.mark.parametrize("tensor_cores", [True, False])
+def test_router(native, T, H, E, K, R, tensor_cores):
+    """Both router paths - logits from the tcgen05 grouped GEMM with the fp32 store epilogue plus the finishing
+    kernel, and the SIMT kernel in every expert-width instance (16 / 32 / 64 experts per pass, several passes,
+    widths that are not a multiple of the chunk) - against softmax -> top-k -> renormalise in fp32."""
     from streamep_b200.models.reference import router_reference
     gg = _ops()
     g = torch.Generator(device="cpu").manual_seed(20)
     x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(DEV)
     wg = (torch.randn(E, H, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
-    idx, w, in_rank, probs = gg.router_topk(x, wg, K, num_ranks=R, return_probs=True)
-    torch.cuda.synchronize()
+    gg.default_runtime().set_router_on_tensor_cores(tensor_cores)
+    try:
+        idx, w, in_rank, probs = gg.router_topk(x, wg, K, num_ranks=R, return_probs=True)
+        torch.cuda.synchronize()
+    finally:
+        gg.default_runtime().set_router_on_tensor_cores(True)
+    _check_status()
     ridx, rw = router_reference(x, wg, K)
     check_close("probs", probs, torch.softmax(x.float() @ wg.float().t(), -1), atol=1e-5, rtol=1e-3)
     # compare as sets per token (near-ties may order differently) through the weights gathered by expert id
