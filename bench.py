@@ -22,7 +22,8 @@ steps, outside the event pairs; ``ms_per_step`` is the mean of the K event inter
 reported value is the max over ranks.  ``e2e`` repeats the measurement through the public module API with, every step, the
 host-to-device copy of that step's inputs from pinned memory (prefetched on a copy stream, two buffers)
 and a device-to-host read of that step's loss (read on the host one step behind the launches).  The copy of
-step i+1's input is released by the event the library records where step i's backward enters its local dW GEMMs.
+step i+2's input (three buffers) is released by the event the library records where step i's backward enters its
+local dW GEMMs.
 """
 from __future__ import annotations
 
@@ -188,12 +189,13 @@ def main():
     # ---------------------------------------------------------------- end-to-end through the public API
     e2e = None
     if not args.no_e2e:
-        x_host = [torch.randn(T, H).to(torch.bfloat16).pin_memory() for _ in range(2)]
-        x_in = [torch.empty(T, H, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        NB = 3      # input buffers: step i computes on i % 3 while the copy of step i + 2 lands in (i + 2) % 3
+        x_host = [torch.randn(T, H).to(torch.bfloat16).pin_memory() for _ in range(NB)]
+        x_in = [torch.empty(T, H, dtype=torch.bfloat16, device=dev) for _ in range(NB)]
         loss_host = [torch.empty(1, dtype=torch.float32).pin_memory() for _ in range(2)]
         loss_ready = [torch.cuda.Event(), torch.cuda.Event()]
         copy_stream = torch.cuda.Stream()
-        copied = [torch.cuda.Event(), torch.cuda.Event()]
+        copied = [torch.cuda.Event() for _ in range(NB)]
         losses = []
 
         def prefetch(i, after):
@@ -201,8 +203,8 @@ def main():
             with torch.cuda.stream(copy_stream):
                 if after is not None:
                     copy_stream.wait_event(after)
-                x_in[i % 2].copy_(x_host[i % 2], non_blocking=True)
-                copied[i % 2].record(copy_stream)
+                x_in[i % NB].copy_(x_host[i % NB], non_blocking=True)
+                copied[i % NB].record(copy_stream)
 
         def read_loss(i):
             """Host read of step i's loss (blocks until its device-to-host copy has landed)."""
@@ -210,23 +212,24 @@ def main():
             losses.append(float(loss_host[i % 2][0]))
 
         def step_e2e(i, first):
-            torch.cuda.current_stream().wait_event(copied[i % 2])
-            h = x_in[i % 2].detach().requires_grad_(True)
+            torch.cuda.current_stream().wait_event(copied[i % NB])
+            h = x_in[i % NB].detach().requires_grad_(True)
             cur = h
             for layer, r in zip(layers, routing):
                 # router + experts: the call a user makes (the Zipf config supplies its own routing)
                 cur = layer.experts(cur, *r) if zipf else layer(cur)
             loss = (cur * dy_dev).sum(dtype=torch.float32) * (1.0 / cur.numel())
             loss.backward()
-            # The next step's input (other buffer, last read one step ago) is copied while this step's
-            # backward runs its local dW GEMMs: the library marks that point.  Kernels that synchronise
-            # with peers at system scope run slower while a PCIe copy is in flight, so the copy is kept
-            # away from them; without the mark (baseline arm) the copy waits for the end of the step.
+            # The input of step i + 2 (a buffer last read by step i - 1) is copied from where this step's
+            # backward enters its local dW GEMMs: the library marks that point.  Kernels that synchronise
+            # with peers at system scope run slower while a PCIe copy is in flight, so the copy starts under
+            # local compute, and it has a whole further step to finish, so a slow copy never stalls a step.
+            # Without the mark (baseline arm) the copy waits for the end of the step.
             mark = buffer.local_phase_event() if buffer is not None else None
             if mark is None:
                 mark = torch.cuda.Event()
                 mark.record()
-            prefetch(i + 1, mark)
+            prefetch(i + 2, mark)
             if not first:
                 read_loss(i - 1)            # every step's loss is read on the host, one step behind the launches
             loss_host[i % 2].copy_(loss.detach().reshape(1), non_blocking=True)
@@ -235,6 +238,7 @@ def main():
                 p.grad = None
 
         prefetch(0, None)
+        prefetch(1, None)
         for i in range(max(args.warmup, 3)):
             step_e2e(i, first=(i == 0))
         base = max(args.warmup, 3)
