@@ -1,7 +1,7 @@
 """Multi-process, one rank per GPU, checks of the real NVLink paths (launched by torchrun).
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        --master-port 29533 tests/multigpu/layer_check.py [--scenario all|layer|comm|missing_rank]
+        --master-port 29533 tests/multigpu/layer_check.py [--scenario all|layer|comm|lopsided|missing_rank]
 
 Covers what the reference's torchrun scripts cover (tests/test_dispatch.py, test_combine.py,
 test_dispatch_grads.py, test_combine_grads.py, stream_ep/stream_moe/validate_multi_iter.py) plus a
@@ -110,18 +110,25 @@ def comm_checks(buf, rank, R, dev):
         report(f"dispatch_grads + combine_grads (rep {rep})", grads, rank)
 
 
-def layer_checks(buf, rank, R, dev):
+def layer_checks(buf, rank, R, dev, lopsided=False):
+    """Layer forward + backward against the global fp32 oracle.  ``lopsided``: the last rank has no tokens
+    and every pair goes to rank 0's experts, so every other rank receives nothing (empty pools, no tiles)
+    but still takes part in every collective."""
     H, I, K = 512, 384, 4
     EL = 4
     E = EL * R
     T = 700 + 64 * rank
+    if lopsided:
+        T = 0 if rank == R - 1 else 300 + 32 * rank
     g = torch.Generator(device="cpu").manual_seed(7)
     w1_full = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.bfloat16)
     w2_full = (torch.randn(E, H, I, generator=g) * 0.05).to(torch.bfloat16)
     gr = torch.Generator(device="cpu").manual_seed(300 + rank)
     x0 = torch.randn(T, H, generator=gr).to(torch.bfloat16).to(dev)
     idx, w0 = make_routing(T, K, E, 400 + rank, dev, sentinel_p=0.03)
-    w0 = w0 / w0.sum(-1, keepdim=True)
+    if lopsided:
+        idx = torch.where(idx >= 0, idx % EL, idx)       # experts 0..EL-1 live on rank 0 (duplicates allowed)
+    w0 = w0 / w0.sum(-1, keepdim=True).clamp_min(1e-6)
     dy = torch.randn(T, H, generator=gr).to(torch.bfloat16).to(dev)
     xs, idxs, ws, dys = gather_list(x0), gather_list(idx), gather_list(w0), gather_list(dy)
     # global oracle on this rank's device: all tokens of all ranks
@@ -132,8 +139,9 @@ def layer_checks(buf, rank, R, dev):
     streams = make_streams()
     s = lambda t: max(float(t.abs().max()), 1e-6)   # noqa: E731
 
+    tag = "lopsided " if lopsided else ""
     for fused in (True, False):
-        for level in (0, 1, 2):
+        for level in ((0, 2) if lopsided else (0, 1, 2)):
             def run():
                 x = x0.clone().requires_grad_(True)
                 w = w0.clone().requires_grad_(True)
@@ -146,12 +154,13 @@ def layer_checks(buf, rank, R, dev):
                                           activation_checkpoint_level=level, fused=fused)
                     out.backward(dy)
                     torch.cuda.synchronize(); buf.check_status()
-                    check_close("out", out, want_out[sl], 2e-2 * s(want_out), 2e-2)
-                    check_close("dx", x.grad, want_dx[sl], 2e-2 * s(want_dx), 2e-2)
-                    check_close("dw_topk", w.grad, want_dw[sl], 2e-2 * s(want_dw), 2e-2)
+                    if T > 0:
+                        check_close("out", out, want_out[sl], 2e-2 * s(want_out), 2e-2)
+                        check_close("dx", x.grad, want_dx[sl], 2e-2 * s(want_dx), 2e-2)
+                        check_close("dw_topk", w.grad, want_dw[sl], 2e-2 * s(want_dw), 2e-2)
                     check_close("dW1", w1.grad, want_dw1[rank * EL:(rank + 1) * EL], 3e-2 * s(want_dw1), 3e-2)
                     check_close("dW2", w2.grad, want_dw2[rank * EL:(rank + 1) * EL], 3e-2 * s(want_dw2), 3e-2)
-            report(f"layer fwd+bwd vs fp32 oracle (fused={fused}, ckpt level {level})", run, rank)
+            report(f"{tag}layer fwd+bwd vs fp32 oracle (fused={fused}, ckpt level {level})", run, rank)
 
 
 def missing_rank_check(buf, rank, R, dev):
@@ -198,6 +207,8 @@ def main():
         comm_checks(buf, rank, world, dev)
     if args.scenario in ("all", "layer"):
         layer_checks(buf, rank, world, dev)
+    if args.scenario in ("all", "lopsided"):
+        layer_checks(buf, rank, world, dev, lopsided=True)
     if args.scenario in ("all", "missing_rank"):
         missing_rank_check(buf, rank, world, dev)
     dist.barrier(device_ids=[local])
