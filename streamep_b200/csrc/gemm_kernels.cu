@@ -748,7 +748,7 @@ static bool dispatch_layout(const GemmParams& p, const CUtensorMap& ta, const CU
   return false;
 }
 
-void launch_grouped_gemm(const GemmParams& p, const void* tmap_a, const void* tmap_b, const void* tmap_o0,
+bool launch_grouped_gemm(const GemmParams& p, const void* tmap_a, const void* tmap_b, const void* tmap_o0,
                          const void* tmap_o1, const PushParams* fused_push, int num_ctas, cudaStream_t stream) {
   const CUtensorMap& ta = *static_cast<const CUtensorMap*>(tmap_a);
   const CUtensorMap& tb = *static_cast<const CUtensorMap*>(tmap_b);
@@ -763,8 +763,7 @@ void launch_grouped_gemm(const GemmParams& p, const void* tmap_a, const void* tm
     ok = (p.block_n == 256) ? dispatch_layout<256, false>(p, ta, tb, to0, to1, none, num_ctas, stream)
                             : dispatch_layout<128, false>(p, ta, tb, to0, to1, none, num_ctas, stream);
   }
-  if (!ok) fprintf(stderr, "streamep_b200: unsupported grouped GEMM configuration (mode=%d epi=%d a_mn=%d b_mn=%d)\n",
-                   p.mode, p.epilogue, p.a_mn_major, p.b_mn_major);
+  return ok;
 }
 
 }  // namespace sep

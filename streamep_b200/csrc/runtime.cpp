@@ -198,7 +198,7 @@ struct GemmArgs {
   std::optional<at::Tensor> scatter_local, row_src, row_k_slot;
   std::optional<at::Tensor> tile_stripes_done, k_remaining, done_per_token;
   int dbg_flags = 0;
-  std::optional<at::Tensor> dbg_cycles;             // int64 [num_ctas, 8], only filled by -DSEP_EPI_TIMING builds
+  std::optional<at::Tensor> dbg_cycles;             // int64 [num_ctas, 16], only filled by -DSEP_EPI_TIMING builds
   // remote scatter / remote dL/dweight return: (record kind, epoch, word) naming the buffer on every rank
   std::vector<int> remote_out;
   std::vector<int> remote_dw;
@@ -809,8 +809,9 @@ class Runtime {
     }
     if (ppp == nullptr) n_ctas = static_cast<int>(std::min<int64_t>(n_ctas, std::max<int64_t>(total, 1)));
     ++launches_;
-    launch_grouped_gemm(p, &ta, &tb, have_o0 ? &to0 : nullptr, have_o1 ? &to1 : nullptr, ppp, n_ctas,
-                        at::cuda::getCurrentCUDAStream());
+    const bool launched = launch_grouped_gemm(p, &ta, &tb, have_o0 ? &to0 : nullptr, have_o1 ? &to1 : nullptr, ppp, n_ctas,
+                                              at::cuda::getCurrentCUDAStream());
+    SEP_ASSERT(launched, "no grouped GEMM kernel for this combination of mode, operand layouts, epilogue and fused push");
     SEP_CUDA_CHECK(cudaGetLastError());
   }
 
