@@ -34,8 +34,10 @@ LOGICAL = [  # substring of the kernel name -> logical name (template args: BN, 
     ("false, true, 2, false>", "GEMM-A_bwd (+ combine_grads when remote)"),
     ("true, true, 0, false>", "dW grouped GEMM"),
     ("false, false, 0, false>", "preact recompute GEMM"),
+    ("false, false, 4, false>", "router logits GEMM (fp32 store)"),
+    ("router_finish_kernel", "router softmax / top-k"),
     ("pool_rows_kernel", "pool compress / expand"),
-    ("router_kernel", "router"),
+    ("router_kernel", "router (SIMT path)"),
     ("device_barrier_kernel", "barrier / tail handshake"),
 ]
 
@@ -152,10 +154,21 @@ def main():
         total = 0.0
         lines.append(f"config: tokens/rank={T} hidden={H} ffn={I} experts={E} ({args.experts_per_rank}/rank) top{K} "
                      f"layers={args.layers} world={world} fused={args.fused} ckpt_level={args.ckpt_level}")
-        lines.append(f"{'kernel':58s} {'calls/step':>10s} {'us/step':>10s}")
+        from ..utils.roofline import layer_rooflines, load_peaks
+        peaks = load_peaks()
+        roof = layer_rooflines(T, H, I, K, world, peaks, experts_per_rank=args.experts_per_rank,
+                               store_preact=args.ckpt_level == 0)
+        lines.append(f"{'kernel':58s} {'calls/step':>10s} {'us/step':>10s} {'roofline us':>12s} {'fraction':>9s}  bound")
         for label, (n, us) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
-            lines.append(f"{label:58s} {n / args.steps:10.1f} {us / args.steps:10.1f}")
+            row = f"{label:58s} {n / args.steps:10.1f} {us / args.steps:10.1f}"
+            if label in roof and us > 0:
+                r = roof[label]
+                want = r.roofline_us * args.layers
+                row += f" {want:12.1f} {want / (us / args.steps):9.2f}  {r.bound}"
+            lines.append(row)
             total += us / args.steps
+        lines.append(f"(roofline per kernel = slowest of its GEMM at {peaks.tflops:.0f} TFLOP/s, its HBM bytes at "
+                     f"{peaks.hbm_gbs:.0f} GB/s and its NVLink bytes at {peaks.nvlink_gbs:.0f} GB/s, {peaks.label}; balanced routing assumed)")
         lines.append(f"{'serial sum of device kernels':58s} {'':10s} {total:10.1f}")
         lines.append(f"{'end-to-end step (median, max over ranks)':58s} {'':10s} {float(t[0]) * 1e3:10.1f}")
         lines.append(f"{'overlap saved (serial sum - e2e)':58s} {'':10s} {total - float(t[0]) * 1e3:10.1f}")

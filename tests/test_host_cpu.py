@@ -219,3 +219,21 @@ def test_rank_monitor_detects_a_rank_that_left(tmp_path):
 def test_errors_hierarchy():
     from streamep_b200 import StreamEPError, StreamEPTimeout
     assert issubclass(StreamEPTimeout, StreamEPError) and issubclass(StreamEPError, RuntimeError)
+
+
+# ------------------------------------------------------------------ roofline arithmetic
+def test_roofline_model_of_the_flagship_layer():
+    from streamep_b200.utils.roofline import Peaks, layer_rooflines, step_flops
+    pk = Peaks(tflops=1600.0, hbm_gbs=6400.0, nvlink_gbs=800.0, label="of test")
+    one = layer_rooflines(8192, 2048, 1408, 6, 1, pk)
+    eight = layer_rooflines(8192, 2048, 1408, 6, 8, pk)
+    a1, a8 = one["dispatch (+) GEMM-A SwiGLU (fused)"], eight["dispatch (+) GEMM-A SwiGLU (fused)"]
+    pairs = 8192 * 6
+    assert a1.flops == 2.0 * pairs * 2048 * 2 * 1408 and a1.nvlink_bytes == 0 and a1.bound == "tensor cores"
+    assert a8.nvlink_bytes == pairs * 7 / 8 * 2048 * 2                       # 7 of 8 rows leave the rank
+    assert abs(a8.nvlink_us - a8.nvlink_bytes / 800e3) < 1e-9 and a8.roofline_us == a8.gemm_us
+    y8 = eight["GEMM-Y (+ combine when remote)"]
+    assert y8.bound == "NVLink" and y8.roofline_us == y8.nvlink_us           # half the FLOPs, same bytes on the wire
+    total = sum(v.flops for v in one.values())
+    assert total == step_flops(8192, 2048, 1408, 6)                          # 18 FLOPs per (pair, hidden, ffn) element
+    assert step_flops(8192, 2048, 1408, 6, recompute=True) == total / 18 * 22
