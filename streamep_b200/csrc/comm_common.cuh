@@ -172,8 +172,11 @@ __device__ __forceinline__ void push_chunk(const PushParams& p, const PushTarget
   __syncwarp();
   const int key = (lane < n) ? ((dst << 24) | (slot / p.tile_m)) : (-1 - lane);
   const unsigned peers = __match_any_sync(0xffffffffu, key);
-  if (lane < n && (__ffs(peers) - 1) == lane)
-    red_release_sys_add(tg.arrival_count[dst] + slot / p.tile_m, __popc(peers));
+  if (lane < n && (__ffs(peers) - 1) == lane) {
+    // with one rank the consumer is on this GPU and acquires at device scope: release at device scope
+    if (R == 1) red_release_gpu_add(tg.arrival_count[dst] + slot / p.tile_m, __popc(peers));
+    else red_release_sys_add(tg.arrival_count[dst] + slot / p.tile_m, __popc(peers));
+  }
 }
 
 }  // namespace sep

@@ -173,7 +173,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #endif
           const int target = p.arrival_target[t.m_tile];
           const int* cnt = p.arrival_count + t.m_tile;
-          if (!spin_until([&] { return ld_acquire_sys(cnt) == target; }, budget, p.status)) {
+          // with one rank every writer of the counter is on this GPU: device scope is enough and cheaper
+          const bool local_only = p.num_ranks == 1;
+          if (!spin_until([&] { return (local_only ? ld_acquire_gpu(cnt) : ld_acquire_sys(cnt)) == target; }, budget, p.status)) {
             report_failure(p.status, kStatusTimeoutTileGate, kKernelGemm, 0, p.rank, t.m_tile, target, ld_acquire_sys(cnt));
             ok = false; break;
           }
