@@ -7,8 +7,6 @@ all-to-all plus library GEMMs is the baseline, not the product.
 """
 from __future__ import annotations
 
-from typing import Optional
-
 import torch
 import torch.distributed as dist
 from torch import nn
