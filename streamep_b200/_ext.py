@@ -26,7 +26,7 @@ _NAME = "_C"
 _lock = threading.Lock()
 _module = None
 
-SOURCES = ["runtime.cpp", "comm_kernels.cu", "gemm_kernels.cu", "no_alloc.cu"]
+SOURCES = ["runtime.cpp", "comm_kernels.cu", "gemm_kernels.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
@@ -41,7 +41,10 @@ def _so_path() -> Path:
 
 
 def _sources():
-    return [str(_CSRC / s) for s in SOURCES if (_CSRC / s).exists()]
+    missing = [s for s in SOURCES if not (_CSRC / s).exists()]
+    if missing:
+        raise FileNotFoundError(f"extension sources missing from {_CSRC}: {missing}")
+    return [str(_CSRC / s) for s in SOURCES]
 
 
 def _stale() -> bool:

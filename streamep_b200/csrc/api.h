@@ -291,16 +291,17 @@ struct GemmParams {
   int rank;
   StatusBlock* status;
   unsigned long long wait_budget_ns;
-  int dbg_flags;                 // experiment switches of -DSEP_EPI_TIMING builds
-  long long* dbg_cycles;         // optional [num_ctas, 16]: per-CTA cycle / time counters (builds with -DSEP_EPI_TIMING)
 };
 
 // tmap_a / tmap_b: 128-byte CUtensorMap blobs (3-D, bf16, 128-byte swizzle) built by the host.
 // tmap_o0 / tmap_o1: output maps for the TMA-store epilogues (store, swiglu, dswiglu); box 32 rows x one
 // staging row (32, 64 or 128 bytes) with the matching swizzle.  Null for the scatter epilogue.
 // Returns false, launching nothing, when no kernel instance exists for the mode / layout / epilogue combination.
+// `setup_error` (optional) receives the error of the per-device kernel set-up (shared-memory attribute); when it is
+// not cudaSuccess nothing was launched either.
 bool launch_grouped_gemm(const GemmParams& p, const void* tmap_a, const void* tmap_b, const void* tmap_o0,
-                         const void* tmap_o1, const PushParams* fused_push, int num_ctas, cudaStream_t stream);
+                         const void* tmap_o1, const PushParams* fused_push, int num_ctas, cudaStream_t stream,
+                         cudaError_t* setup_error = nullptr);
 size_t grouped_gemm_smem_bytes(int block_n);
 
 }  // namespace sep

@@ -15,6 +15,19 @@
 
 namespace sep {
 
+// SM count of the current device (cached per device): grids are sized from it, never from a constant.
+static int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 ControlLayout make_control_layout(int num_ranks, int num_channels, int num_experts_cap) {
   ControlLayout c{};
   c.num_ranks = num_ranks;
@@ -380,7 +393,7 @@ void launch_dispatch_metadata(const MetadataParams& p, cudaStream_t stream) {
     const long long work = static_cast<long long>(p.num_tokens) * max(p.num_topk, p.num_ranks);
     long long blocks = (work + 1023) / 1024;
     if (blocks < 1) blocks = 1;
-    if (blocks > 148) blocks = 148;
+    if (blocks > sm_count()) blocks = sm_count();
     const int grid = static_cast<int>(blocks);
     dispatch_metadata_kernel<<<grid, kMetaThreads, 0, stream>>>(q);
   }
@@ -418,7 +431,7 @@ __global__ void fill_tile_metadata_kernel(const FillParams p) {
 
 void launch_fill_tile_metadata(const FillParams& p, cudaStream_t stream) {
   const int work = max(max(p.tk_padded, p.num_recv_tokens * p.num_topk), 1);
-  const int grid = min((work + 255) / 256, 592);
+  const int grid = min((work + 255) / 256, 4 * sm_count());
   fill_tile_metadata_kernel<<<grid, 256, 0, stream>>>(p);
 }
 
@@ -667,14 +680,14 @@ __global__ void pool_rows_kernel(const char* src, char* dst, const int* pool_rec
 void launch_pool_compress(const void* pool, void* recv, const int* pool_recv_token, int tk_padded, int hidden,
                           cudaStream_t stream) {
   if (tk_padded == 0) return;
-  const int grid = min((tk_padded + 7) / 8, 148 * 8);
+  const int grid = min((tk_padded + 7) / 8, sm_count() * 8);
   pool_rows_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const char*>(pool), static_cast<char*>(recv),
                                                    pool_recv_token, tk_padded, hidden);
 }
 void launch_pool_expand(const void* recv, void* pool, const int* pool_recv_token, int tk_padded, int hidden,
                         cudaStream_t stream) {
   if (tk_padded == 0) return;
-  const int grid = min((tk_padded + 7) / 8, 148 * 8);
+  const int grid = min((tk_padded + 7) / 8, sm_count() * 8);
   pool_rows_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const char*>(recv), static_cast<char*>(pool),
                                                     pool_recv_token, tk_padded, hidden);
 }
@@ -717,7 +730,7 @@ __global__ void combine_reduce_kernel(char* out, const char* rows, const long lo
 void launch_combine_reduce(void* out, const void* rows, const long long* topk_idx, int num_tokens, int hidden,
                            int num_topk, int num_experts, int num_ranks, int rank, cudaStream_t stream) {
   if (num_tokens == 0 || num_ranks == 1) return;
-  const int grid = min((num_tokens + 7) / 8, 148 * 8);
+  const int grid = min((num_tokens + 7) / 8, sm_count() * 8);
   combine_reduce_kernel<<<grid, 256, 0, stream>>>(static_cast<char*>(out), static_cast<const char*>(rows), topk_idx,
                                                   num_tokens, hidden, num_topk, num_experts / num_ranks, rank);
 }

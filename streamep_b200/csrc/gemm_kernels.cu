@@ -16,7 +16,9 @@
 // Reference counterparts: stream_ep/stream_moe/kernel_a.py, kernel_y.py, kernel_y_bwd.py,
 // kernel_a_bwd.py, tile_scheduler.py, epi_ops.py and the quack.gemm calls at
 // stream_ep/stream_moe/stream_moe.py:993-1004,1111-1142 (all Hopper WGMMA through CuTeDSL there).
+#include <atomic>
 #include <cstdio>
+#include <mutex>
 #include <cuda.h>
 
 #include "comm_common.cuh"
@@ -30,6 +32,7 @@ constexpr int UMMA_K = 16;
 constexpr int kGemmWarps = 10;   // 0: TMA producer, 1: MMA issuer + TMEM owner, 2..9: epilogue
 // extra warps of the fused variants; the dSwiGLU epilogue keeps two preact segments in registers, so it gets fewer
 constexpr int push_warps(int epi) { return epi == kEpiDswiglu ? 6 : 10; }
+constexpr int kMaxDevices = 64;  // per-device host-side tables (kernel attributes, no-alloc scratch address)
 constexpr int kEpiThreads = 256; // two threads per accumulator row: each takes half of the tile's columns
 
 template <int BN> struct GemmCfg {
@@ -98,6 +101,17 @@ __device__ __forceinline__ int atom_add_acq_rel_gpu(int* p, int v) {
   return old;
 }
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// OR of `pred` over the 256 epilogue threads (named barrier 1, as epi_bar_sync): every thread gets the same answer.
+__device__ __forceinline__ bool epi_vote_any(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "barrier.cta.red.or.pred q, 1, 256, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r) : "r"(static_cast<uint32_t>(pred)) : "memory");
+  return r != 0;
+}
 
 template <int BN, bool A_MN, bool B_MN, int EPI, bool PUSH>
 __global__ void __launch_bounds__((kGemmWarps + (PUSH ? push_warps(EPI) : 0)) * 32, 1)
@@ -168,9 +182,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       for (int lin = blockIdx.x; lin < total_tiles && ok; lin += gridDim.x) {
         const TileCoord t = decode_tile(p, lin);
         if (p.mode == kVarlenM && p.arrival_count != nullptr) {
-#ifdef SEP_EPI_TIMING
-          const unsigned long long dbg_g0 = globaltimer_ns();
-#endif
           const int target = p.arrival_target[t.m_tile];
           const int* cnt = p.arrival_count + t.m_tile;
           // with one rank every writer of the counter is on this GPU: device scope is enough and cheaper
@@ -180,14 +191,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             ok = false; break;
           }
           fence_proxy_async();   // rows were written through the generic proxy (possibly by a peer GPU)
-#ifdef SEP_EPI_TIMING
-          if (PUSH && p.dbg_cycles != nullptr) {
-            const unsigned long long now = globaltimer_ns();
-            p.dbg_cycles[blockIdx.x * 16 + 8] += static_cast<long long>(now - dbg_g0);        // ns spent waiting on tile gates
-            if (lin == static_cast<int>(blockIdx.x)) p.dbg_cycles[blockIdx.x * 16 + 9] = static_cast<long long>(now);   // first tile ready
-            p.dbg_cycles[blockIdx.x * 16 + 10] = static_cast<long long>(now);                 // last tile ready
-          }
-#endif
         }
         for (int kb = 0; kb < t.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, budget, p.status)) {
@@ -236,11 +239,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     for (int lin = blockIdx.x; lin < total_tiles && ok; lin += gridDim.x) {
       const TileCoord t = decode_tile(p, lin);
       if (t.k_blocks == 0) continue;   // empty expert: the epilogue writes zeros on its own
-      if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, budget, p.status)) { ok = false; break; }
+      // all 32 lanes wait; the outcome is made warp-uniform so that no lane leaves ahead of elect_one / __syncwarp
+      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_empty[acc], acc_phase ^ 1, budget, p.status))) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t tmem_d = tmem_base + acc * BN;
       for (int kb = 0; kb < t.k_blocks; ++kb) {
-        if (!mbar_wait(&full_bar[stage], phase, budget, p.status)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase, budget, p.status))) { ok = false; break; }
         unsigned char* sa = stage_base + stage * Cfg::kStageBytes;
         unsigned char* sb = sa + Cfg::kABytes;
         if (p.mode == kVarlenK && t.k_tail != 0 && kb == t.k_blocks - 1) {
@@ -265,9 +269,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                      : umma_smem_desc(a_addr + j * (UMMA_K * 2), 16, 1024);
             const uint64_t db = B_MN ? umma_smem_desc(b_addr + j * (UMMA_K * 128), BK * 128, 1024)
                                      : umma_smem_desc(b_addr + j * (UMMA_K * 2), 16, 1024);
-#ifdef SEP_EPI_TIMING
-            if (!(p.dbg_flags & 16))
-#endif
             umma_bf16_ss(tmem_d, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);                       // frees the smem stage when the MMAs retire
@@ -290,20 +291,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int half = (warp - 2) >> 2;
     constexpr int kChunksPerHalf = BN / 64;
     const uint32_t stg = smem_u32(epi_stage + (warp - 2) * Cfg::kEpiStageBytes);
-    int acc = 0; uint32_t acc_phase = 0; bool ok = true;
-#ifdef SEP_EPI_TIMING
-    long long dbg_t[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#define SEP_T(i, expr) { const long long c0__ = clock64(); expr; dbg_t[i] += clock64() - c0__; }
-    const long long dbg_start = clock64();
-#else
-#define SEP_T(i, expr) { expr; }
-#endif
+    int acc = 0; uint32_t acc_phase = 0;
     for (int lin = blockIdx.x; lin < total_tiles; lin += gridDim.x) {
       const TileCoord t = decode_tile(p, lin);
       const bool empty = (t.k_blocks == 0);
-#ifdef SEP_EPI_TIMING
-      const long long dbg_tile0 = clock64();
-#endif
       // Everything that does not need the accumulator is fetched while the tensor cores still work on this tile.
       const int n0 = t.n_tile * BN;
       const int warp_row0 = (p.mode == kVarlenM ? t.row0 : t.m_tile * BM) + quarter * 32;   // TMA y coordinate
@@ -347,22 +338,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                          : make_uint4(0, 0, 0, 0);
         }
       }
-#ifdef SEP_EPI_TIMING
-      dbg_t[0] += clock64() - dbg_tile0;                 // pre-accumulator bookkeeping
-      const long long dbg_w0 = clock64();
-#endif
-      if (!empty && ok) {
-        if (!mbar_wait(&tmem_full[acc], acc_phase, budget, p.status)) {
-          report_failure(p.status, kStatusTimeoutPipeline, kKernelGemm, 2, p.rank, lin, acc, 0);
-          ok = false;
-        }
+      if (!empty) {
+        const bool got = mbar_wait(&tmem_full[acc], acc_phase, budget, p.status);
+        if (!got) report_failure(p.status, kStatusTimeoutPipeline, kKernelGemm, 2, p.rank, lin, acc, 0);
+        // The give-up decision is taken by all 256 epilogue threads together: a thread that saw the accumulator
+        // must not go on to the stripe barriers (or to a warp-wide tcgen05.ld) while another one leaves the loop.
+        if (epi_vote_any(!got)) break;
         tc_fence_after_sync();
       }
-      if (!ok) break;
-#ifdef SEP_EPI_TIMING
-      dbg_t[1] += clock64() - dbg_w0;                    // waiting for the accumulator
-      const long long dbg_e0 = clock64();
-#endif
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
       float dw_acc = 0.f;
 #pragma unroll 1
@@ -379,9 +362,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           for (int j = 0; j < 8; ++j) pq[j] = ld_shared_v4(stg + stage_off<128>(lane, j));
           __syncwarp();
           const int nn = n + 32;
-#ifdef SEP_EPI_TIMING
-          if (!(p.dbg_flags & 64))
-#endif
           if (c + 1 < c_begin + kChunksPerHalf && nn < p.N) {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
@@ -393,7 +373,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         uint32_t r[EPI == kEpiDswiglu ? 1 : 32];   // the dSwiGLU epilogue reads the accumulator 16 columns at a time
         if (EPI != kEpiDswiglu) {
           if (!empty) {
-            SEP_T(2, tmem_ld_32x32(taddr + c * 32, reinterpret_cast<uint32_t(&)[32]>(r)); tmem_ld_wait();)
+            tmem_ld_32x32(taddr + c * 32, reinterpret_cast<uint32_t(&)[32]>(r)); tmem_ld_wait();
           } else {
 #pragma unroll
             for (int i = 0; i < (EPI == kEpiDswiglu ? 1 : 32); ++i) r[i] = 0;
@@ -492,9 +472,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         } else {   // kEpiDswiglu: r = g[row, n..n+32) = dL/d(postact) before the topk weight
           uint32_t o_pw[16];
           unsigned char* sb = epi_stage + (warp - 2) * Cfg::kEpiStageBytes;
-#ifdef SEP_EPI_TIMING
-          const long long dbg_c0 = clock64();
-#endif
           uint32_t rh[16];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {       // 8 output columns per step; N is a multiple of 8
@@ -509,29 +486,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               }
             }
             uint32_t o_in[8];
-#ifdef SEP_EPI_TIMING
-            if ((p.dbg_flags & 32)) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) o_in[i] = 0;
-#pragma unroll
-              for (int i = 0; i < 4; ++i) o_pw[q * 4 + i] = 0;
-            } else
-#endif
             if (tok >= 0 && n + q * 8 < p.N) {
               const uint4 p0 = pq[q * 2], p1 = pq[q * 2 + 1];
               const uint32_t pv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
               float post[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
-#ifdef SEP_EPI_TIMING
-                const float2 gu = (p.dbg_flags & 4) ? make_float2(0.5f, 0.25f) : unpack_bf16x2(pv[i]);
-                const float g = (p.dbg_flags & 8) ? 1.5f : __uint_as_float(rh[(q & 1) * 8 + i]);
-                const float sig = (p.dbg_flags & 1) ? gu.x * 0.25f + 0.5f : fast_sigmoid(gu.x);
-#else
                 const float2 gu = unpack_bf16x2(pv[i]);          // (gate, up)
                 const float g = __uint_as_float(rh[(q & 1) * 8 + i]);
                 const float sig = fast_sigmoid(gu.x);
-#endif
                 const float silu = gu.x * sig;
                 post[i] = silu * gu.y;
                 dw_acc = fmaf(post[i], g, dw_acc);
@@ -547,18 +510,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
               for (int i = 0; i < 4; ++i) o_pw[q * 4 + i] = 0;
             }
-#ifdef SEP_EPI_TIMING
-            if (!(p.dbg_flags & 2) || o_in[0] == 0x12345u) {
-#endif
             st_shared_v4(stg + stage_off<128>(lane, 2 * q), o_in[0], o_in[1], o_in[2], o_in[3]);
             st_shared_v4(stg + stage_off<128>(lane, 2 * q + 1), o_in[4], o_in[5], o_in[6], o_in[7]);
-#ifdef SEP_EPI_TIMING
-            }
-#endif
           }
-#ifdef SEP_EPI_TIMING
-          dbg_t[0] += clock64() - dbg_c0;                 // (reused slot) compute + st.shared
-#endif
           // Both outputs leave through the staging tile with plain coalesced stores (8 resp. 4 lanes per
           // 128- resp. 64-byte row segment).  No proxy fence here on purpose: a fence would wait for the
           // preact loads of the next chunk that are still in flight.
@@ -597,9 +551,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           __syncwarp();
         }
       }
-#ifdef SEP_EPI_TIMING
-      dbg_t[3] += clock64() - dbg_e0;                    // whole column loop of this tile
-#endif
       if (!empty) {
         tc_fence_before_sync();
         mbar_arrive(&tmem_empty[acc]);
@@ -620,7 +571,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         epi_bar_sync();
         if (last && tok >= 0 && half == 0) {
           if (EPI == kEpiScatter) {
-            if (atom_add_acq_rel_gpu(p.k_remaining + tok, -1) == 1) st_release_gpu(p.done_per_token + tok, p.seq);
+            if (atom_add_acq_rel_gpu(p.k_remaining + tok, -1) == 1) {
+              // The stand-alone combine of another GPU acquires this stamp at system scope and then reads the
+              // row: the release must be at system scope too (device scope is enough with one rank).
+              if (p.num_ranks > 1) { fence_acq_rel_sys(); st_release_sys(p.done_per_token + tok, p.seq); }
+              else st_release_gpu(p.done_per_token + tok, p.seq);
+            }
           } else {
             const int2 src = p.row_src[grow];
             const float v = *reinterpret_cast<volatile float*>(p.dl_dweight + grow);
@@ -630,18 +586,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
     }
     if (lane == 0) bulk_wait_all();     // every bulk store this warp issued has been performed
-#ifdef SEP_EPI_TIMING
-    if (p.dbg_cycles != nullptr && warp == 2 && lane == 0) {
-      dbg_t[7] = clock64() - dbg_start;
-      for (int i = 0; i < 8; ++i) p.dbg_cycles[blockIdx.x * 16 + i] = dbg_t[i];
-    }
-#endif
     if (p.tail.enabled) __threadfence_system();
   } else if (PUSH) {
     // ------------------------------------------------------------------ dispatch push warps
-#ifdef SEP_EPI_TIMING
-    if (p.dbg_cycles != nullptr && warp == kGemmWarps && lane == 0) p.dbg_cycles[blockIdx.x * 16 + 11] = static_cast<long long>(globaltimer_ns());
-#endif
     if (pp.flags & 2) {
       const int pw = warp - kGemmWarps;
       if (pw == 0 && lane < pp.num_ranks) {
@@ -664,16 +611,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           push_chunk(pp, s_tg, p0, min(p0 + ppc, num_send), lane);
         }
       }
-#ifdef SEP_EPI_TIMING
-      if (p.dbg_cycles != nullptr && lane == 0)
-        atomicMax(reinterpret_cast<unsigned long long*>(p.dbg_cycles + blockIdx.x * 16 + 12), globaltimer_ns());   // this CTA's push end
-      if (p.dbg_cycles != nullptr && pw == 0 && lane == 0) p.dbg_cycles[blockIdx.x * 16 + 13] = static_cast<long long>(globaltimer_ns());  // after record fetch .. first warp done
-#endif
     }
   }
-#ifdef SEP_EPI_TIMING
-  if (PUSH && p.dbg_cycles != nullptr && threadIdx.x == 0) p.dbg_cycles[blockIdx.x * 16 + 14] = static_cast<long long>(globaltimer_ns());
-#endif
 
   // ---------------------------------------------------------------------- teardown
   tc_fence_before_sync();
@@ -710,61 +649,69 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 // Host dispatch over the template instances
 // ---------------------------------------------------------------------------------------------
 template <int BN, bool A_MN, bool B_MN, int EPI, bool PUSH>
-static void launch_instance(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to0,
+static cudaError_t launch_instance(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to0,
                             const CUtensorMap& to1, const PushParams& pp, int num_ctas, cudaStream_t stream) {
   auto kernel = grouped_gemm_kernel<BN, A_MN, B_MN, EPI, PUSH>;
-  static bool configured = false;
+  // The shared-memory limit is an attribute of the function ON A DEVICE: raise it once per device.
+  static std::atomic<bool> configured[kMaxDevices];
   const int smem = GemmCfg<BN>::kSmemBytes;
-  if (!configured) {
-    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    configured = true;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  if (!configured[dev].load(std::memory_order_acquire)) {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured[dev].store(true, std::memory_order_release);
   }
   const int threads = (kGemmWarps + (PUSH ? push_warps(EPI) : 0)) * 32;
   kernel<<<num_ctas, threads, smem, stream>>>(ta, tb, to0, to1, p, pp);
+  return cudaSuccess;
 }
 
 template <int BN, bool PUSH>
 static bool dispatch_layout(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to0,
-                            const CUtensorMap& to1, const PushParams& pp, int n, cudaStream_t s) {
+                            const CUtensorMap& to1, const PushParams& pp, int n, cudaStream_t s, cudaError_t& err) {
   if (p.mode == kVarlenM && !p.a_mn_major && !p.b_mn_major) {
-    if (p.epilogue == kEpiSwiglu) { launch_instance<BN, false, false, kEpiSwiglu, PUSH>(p, ta, tb, to0, to1, pp, n, s); return true; }
+    if (p.epilogue == kEpiSwiglu) { err = launch_instance<BN, false, false, kEpiSwiglu, PUSH>(p, ta, tb, to0, to1, pp, n, s); return true; }
     if (PUSH) return false;
     if constexpr (!PUSH) {
-      if (p.epilogue == kEpiStore) { launch_instance<BN, false, false, kEpiStore, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
-      if (p.epilogue == kEpiScatter) { launch_instance<BN, false, false, kEpiScatter, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
-      if (p.epilogue == kEpiStoreF32) { launch_instance<BN, false, false, kEpiStoreF32, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
+      if (p.epilogue == kEpiStore) { err = launch_instance<BN, false, false, kEpiStore, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
+      if (p.epilogue == kEpiScatter) { err = launch_instance<BN, false, false, kEpiScatter, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
+      if (p.epilogue == kEpiStoreF32) { err = launch_instance<BN, false, false, kEpiStoreF32, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
     }
   }
   if (p.mode == kVarlenM && !p.a_mn_major && p.b_mn_major) {
-    if (p.epilogue == kEpiDswiglu) { launch_instance<BN, false, true, kEpiDswiglu, PUSH>(p, ta, tb, to0, to1, pp, n, s); return true; }
+    if (p.epilogue == kEpiDswiglu) { err = launch_instance<BN, false, true, kEpiDswiglu, PUSH>(p, ta, tb, to0, to1, pp, n, s); return true; }
     if constexpr (!PUSH) {
-      if (p.epilogue == kEpiScatter) { launch_instance<BN, false, true, kEpiScatter, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
-      if (p.epilogue == kEpiStore) { launch_instance<BN, false, true, kEpiStore, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
+      if (p.epilogue == kEpiScatter) { err = launch_instance<BN, false, true, kEpiScatter, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
+      if (p.epilogue == kEpiStore) { err = launch_instance<BN, false, true, kEpiStore, false>(p, ta, tb, to0, to1, pp, n, s); return true; }
     }
   }
   if constexpr (!PUSH) {
     if (p.mode == kVarlenK && p.a_mn_major && p.b_mn_major && p.epilogue == kEpiStore) {
-      launch_instance<BN, true, true, kEpiStore, false>(p, ta, tb, to0, to1, pp, n, s); return true;
+      err = launch_instance<BN, true, true, kEpiStore, false>(p, ta, tb, to0, to1, pp, n, s); return true;
     }
   }
   return false;
 }
 
 bool launch_grouped_gemm(const GemmParams& p, const void* tmap_a, const void* tmap_b, const void* tmap_o0,
-                         const void* tmap_o1, const PushParams* fused_push, int num_ctas, cudaStream_t stream) {
+                         const void* tmap_o1, const PushParams* fused_push, int num_ctas, cudaStream_t stream,
+                         cudaError_t* setup_error) {
   const CUtensorMap& ta = *static_cast<const CUtensorMap*>(tmap_a);
   const CUtensorMap& tb = *static_cast<const CUtensorMap*>(tmap_b);
   const CUtensorMap& to0 = *static_cast<const CUtensorMap*>(tmap_o0 ? tmap_o0 : tmap_a);
   const CUtensorMap& to1 = *static_cast<const CUtensorMap*>(tmap_o1 ? tmap_o1 : tmap_a);
   bool ok;
+  cudaError_t err = cudaSuccess;
   if (fused_push != nullptr) {
-    ok = (p.block_n == 256) ? dispatch_layout<256, true>(p, ta, tb, to0, to1, *fused_push, num_ctas, stream)
-                            : dispatch_layout<128, true>(p, ta, tb, to0, to1, *fused_push, num_ctas, stream);
+    ok = (p.block_n == 256) ? dispatch_layout<256, true>(p, ta, tb, to0, to1, *fused_push, num_ctas, stream, err)
+                            : dispatch_layout<128, true>(p, ta, tb, to0, to1, *fused_push, num_ctas, stream, err);
   } else {
     PushParams none{};
-    ok = (p.block_n == 256) ? dispatch_layout<256, false>(p, ta, tb, to0, to1, none, num_ctas, stream)
-                            : dispatch_layout<128, false>(p, ta, tb, to0, to1, none, num_ctas, stream);
+    ok = (p.block_n == 256) ? dispatch_layout<256, false>(p, ta, tb, to0, to1, none, num_ctas, stream, err)
+                            : dispatch_layout<128, false>(p, ta, tb, to0, to1, none, num_ctas, stream, err);
   }
+  if (setup_error != nullptr) *setup_error = err;
   return ok;
 }
 
@@ -775,12 +722,15 @@ bool launch_grouped_gemm(const GemmParams& p, const void* tmap_a, const void* tm
 // =============================================================================================
 namespace {
 
-// Scratch of the no-alloc entry point: per-M-tile "N stripes finished" counters.  In host code this
-// name is only a handle for cudaGetSymbolAddress; the device address is resolved once per device.
-static __device__ __align__(256) int g_noalloc_stripes_done[kNoAllocMaxTiles];
+// Scratch of the no-alloc entry point: per-M-tile "N stripes finished" counters, followed by the status block the
+// kernel's bounded waits report into.  In host code this name is only a handle for cudaGetSymbolAddress; the
+// device address is resolved once per device.
+constexpr int kNoAllocStatusInts = 64;    // 256 bytes: keeps the status block on its own 256-byte line
+static __device__ __align__(256) int g_noalloc_scratch[kNoAllocMaxTiles + kNoAllocStatusInts];
+static_assert(sizeof(sep::StatusBlock) <= kNoAllocStatusInts * sizeof(int), "status block must fit its slot");
 
-constexpr int kNoAllocMaxDevices = 64;
-int* g_noalloc_scratch_ptr[kNoAllocMaxDevices] = {};
+int* g_noalloc_scratch_ptr[sep::kMaxDevices] = {};
+std::mutex g_noalloc_setup_mutex;
 thread_local char g_noalloc_error[256] = "";
 
 int noalloc_fail(int code, const char* what, cudaError_t e = cudaSuccess) {
@@ -794,7 +744,8 @@ using NoAllocEncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32
                                      CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 bool noalloc_tmap(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t b0, uint32_t b1) {
-  static NoAllocEncodeFn encode = nullptr;
+  static std::atomic<NoAllocEncodeFn> encode_fn{nullptr};
+  NoAllocEncodeFn encode = encode_fn.load(std::memory_order_acquire);
   if (encode == nullptr) {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult q;
@@ -802,6 +753,7 @@ bool noalloc_tmap(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, ui
         q != cudaDriverEntryPointSuccess || fn == nullptr)
       return false;
     encode = reinterpret_cast<NoAllocEncodeFn>(fn);
+    encode_fn.store(encode, std::memory_order_release);
   }
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
@@ -812,9 +764,37 @@ bool noalloc_tmap(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, ui
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Device address of the scratch array on the current device (resolved under a lock on first use).
+int* noalloc_scratch(int dev, cudaError_t* e) {
+  std::lock_guard<std::mutex> g(g_noalloc_setup_mutex);
+  if (g_noalloc_scratch_ptr[dev] == nullptr) {
+    int* ptr = nullptr;
+    *e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+    if (*e != cudaSuccess || ptr == nullptr) return nullptr;
+    g_noalloc_scratch_ptr[dev] = ptr;
+  }
+  return g_noalloc_scratch_ptr[dev];
+}
+
 }  // namespace
 
 extern "C" const char* streamep_noalloc_last_error(void) { return g_noalloc_error; }
+
+extern "C" int streamep_noalloc_device_status(int* code, int* where) {
+  using namespace sep;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return noalloc_fail(-3, "cudaGetDevice", e);
+  if (dev < 0 || dev >= kMaxDevices) return noalloc_fail(-2, "device ordinal out of range");
+  int* scratch = noalloc_scratch(dev, &e);
+  if (scratch == nullptr) return noalloc_fail(-3, "cudaGetSymbolAddress(scratch)", e);
+  StatusBlock h;
+  e = cudaMemcpy(&h, scratch + kNoAllocMaxTiles, sizeof(h), cudaMemcpyDeviceToHost);   // waits for earlier work
+  if (e != cudaSuccess) return noalloc_fail(-3, "cudaMemcpy(status)", e);
+  if (code != nullptr) *code = h.code;
+  if (where != nullptr) *where = h.where;
+  return 0;
+}
 
 extern "C" int streamep_gemm_y_scatter_noalloc(const void* postact, const void* w2, const int* tile_id_to_expert,
                                                const float* pool_topk_weight, const int* pool_recv_token, void* o,
@@ -822,7 +802,8 @@ extern "C" int streamep_gemm_y_scatter_noalloc(const void* postact, const void* 
                                                int hidden, int ffn, int num_local_experts, long long seq, void* stream_v) {
   using namespace sep;
   g_noalloc_error[0] = 0;
-  if (total_tiles < 0 || total_tiles > kNoAllocMaxTiles)
+  if (total_tiles < 0) return noalloc_fail(-2, "total_tiles must not be negative");
+  if (total_tiles > kNoAllocMaxTiles)
     return noalloc_fail(-1, "total_tiles exceeds kNoAllocMaxTiles (32768): split the call or use the regular entry point");
   if (total_tiles == 0) return 0;
   if (!postact || !w2 || !tile_id_to_expert || !pool_topk_weight || !pool_recv_token || !o || !k_local_remaining || !y_done_per_token)
@@ -835,24 +816,26 @@ extern "C" int streamep_gemm_y_scatter_noalloc(const void* postact, const void* 
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return noalloc_fail(-3, "cudaGetDevice", e);
-  if (dev < 0 || dev >= kNoAllocMaxDevices) return noalloc_fail(-2, "device ordinal out of range");
-  if (g_noalloc_scratch_ptr[dev] == nullptr) {
-    // One-time set-up for this device (with it current): the device address behind the symbol.
-    int* ptr = nullptr;
-    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_stripes_done);
-    if (e != cudaSuccess || ptr == nullptr) return noalloc_fail(-3, "cudaGetSymbolAddress(scratch)", e);
-    g_noalloc_scratch_ptr[dev] = ptr;
-  }
-  int* scratch = g_noalloc_scratch_ptr[dev];
-  // The array keeps the previous call's counts: clear the part this call uses.
-  e = cudaMemsetAsync(scratch, 0, sizeof(int) * static_cast<size_t>(total_tiles), stream);
-  if (e != cudaSuccess) return noalloc_fail(-3, "cudaMemsetAsync(scratch)", e);
+  if (dev < 0 || dev >= kMaxDevices) return noalloc_fail(-2, "device ordinal out of range");
+  // One-time set-up for this device (with it current): the device address behind the symbol.
+  int* scratch = noalloc_scratch(dev, &e);
+  if (scratch == nullptr) return noalloc_fail(-3, "cudaGetSymbolAddress(scratch)", e);
 
   const int block_n = (hidden % 256 == 0) ? 256 : ((hidden % 128 == 0) ? 128 : (hidden > 128 ? 256 : 128));
   const long long rows = static_cast<long long>(total_tiles) * BM;
   CUtensorMap ta, tb;
   if (!noalloc_tmap(&ta, postact, ffn, rows, 1, 64, BM) || !noalloc_tmap(&tb, w2, ffn, hidden, num_local_experts, 64, block_n))
     return noalloc_fail(-3, "cuTensorMapEncodeTiled failed");
+  int sms = 0;
+  e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return noalloc_fail(-3, "cudaDeviceGetAttribute", e);
+
+  // Nothing was enqueued so far.  The array keeps the previous call's counts and status: clear the part this call
+  // uses (stream-ordered, so it cannot overtake an earlier call on the same stream).
+  e = cudaMemsetAsync(scratch, 0, sizeof(int) * static_cast<size_t>(total_tiles), stream);
+  if (e != cudaSuccess) return noalloc_fail(-3, "cudaMemsetAsync(scratch)", e);
+  e = cudaMemsetAsync(scratch + kNoAllocMaxTiles, 0, sizeof(int) * kNoAllocStatusInts, stream);
+  if (e != cudaSuccess) return noalloc_fail(-3, "cudaMemsetAsync(status)", e);
 
   GemmParams p{};
   p.mode = kVarlenM; p.epilogue = kEpiScatter; p.block_n = block_n;
@@ -863,16 +846,14 @@ extern "C" int streamep_gemm_y_scatter_noalloc(const void* postact, const void* 
   p.scatter_local = o;
   p.tile_stripes_done = scratch; p.k_remaining = k_local_remaining; p.done_per_token = y_done_per_token; p.seq = seq;
   p.num_ranks = 1; p.rank = 0;
-  p.status = nullptr;                       // waits stay bounded by the budget below
+  p.status = reinterpret_cast<StatusBlock*>(scratch + kNoAllocMaxTiles);   // read back by streamep_noalloc_device_status
   p.wait_budget_ns = 2000000000ull;
-  int sms = 0;
-  e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (e != cudaSuccess) return noalloc_fail(-3, "cudaDeviceGetAttribute", e);
   const long long total = static_cast<long long>(p.num_m_tiles) * p.num_n_tiles;
   const int ctas = static_cast<int>(total < sms ? total : sms);
   PushParams none{};
-  if (block_n == 256) launch_instance<256, false, false, kEpiScatter, false>(p, ta, tb, ta, ta, none, ctas, stream);
-  else launch_instance<128, false, false, kEpiScatter, false>(p, ta, tb, ta, ta, none, ctas, stream);
+  e = (block_n == 256) ? launch_instance<256, false, false, kEpiScatter, false>(p, ta, tb, ta, ta, none, ctas, stream)
+                       : launch_instance<128, false, false, kEpiScatter, false>(p, ta, tb, ta, ta, none, ctas, stream);
+  if (e != cudaSuccess) return noalloc_fail(-3, "kernel set-up (shared-memory attribute)", e);
   e = cudaGetLastError();
   if (e != cudaSuccess) return noalloc_fail(-3, "kernel launch", e);
   return 0;

@@ -142,6 +142,78 @@ struct EventHandle {
 };
 
 // ---------------------------------------------------------------------------------------------
+// Stream-safe release of arena blocks.  When the last reference to an arena tensor dies, kernels that
+// use the block may still be queued on any stream the runtime launched on (the two-stream plan, or a
+// caller of Buffer.alloc_symmetric).  The deleter records one event on each of those streams and parks
+// the block behind them (Arena::release_deferred); allocate() only reuses it once they have completed.
+// ---------------------------------------------------------------------------------------------
+struct ReleaseCtx {
+  std::mutex mu;
+  std::vector<cudaStream_t> streams;     // every stream the runtime has launched or allocated on
+  std::vector<cudaEvent_t> event_pool;
+  std::shared_ptr<Arena> arena;
+  int device = 0;
+  bool dead = false;                     // runtime destroyed (device drained): release at once
+
+  void note_stream(cudaStream_t s) {
+    std::lock_guard<std::mutex> g(mu);
+    for (cudaStream_t t : streams) if (t == s) return;
+    streams.push_back(s);
+  }
+  ~ReleaseCtx() { for (cudaEvent_t e : event_pool) cudaEventDestroy(e); }
+};
+
+struct CudaFence : ArenaFence {
+  std::shared_ptr<ReleaseCtx> ctx;
+  std::vector<cudaEvent_t> events;
+  bool ready() override {
+    for (cudaEvent_t e : events) {
+      const cudaError_t r = cudaEventQuery(e);
+      if (r == cudaErrorNotReady) return false;
+      if (r != cudaSuccess) cudaGetLastError();   // context going away: nothing can still be running
+    }
+    return true;
+  }
+  void wait() override {
+    for (cudaEvent_t e : events) if (cudaEventSynchronize(e) != cudaSuccess) cudaGetLastError();
+  }
+  ~CudaFence() override {
+    std::lock_guard<std::mutex> g(ctx->mu);
+    for (cudaEvent_t e : events) ctx->event_pool.push_back(e);
+  }
+};
+
+// Deleter of arena tensors.
+static void release_block(const std::shared_ptr<ReleaseCtx>& ctx, size_t off) {
+  std::shared_ptr<CudaFence> fence;
+  {
+    std::unique_lock<std::mutex> g(ctx->mu);
+    if (ctx->dead || ctx->streams.empty()) { g.unlock(); ctx->arena->release(off); return; }
+    fence = std::make_shared<CudaFence>();
+    fence->ctx = ctx;
+    int prev = -1;
+    cudaGetDevice(&prev);
+    if (prev != ctx->device) cudaSetDevice(ctx->device);
+    for (size_t i = 0; i < ctx->streams.size();) {
+      cudaEvent_t e = nullptr;
+      if (!ctx->event_pool.empty()) { e = ctx->event_pool.back(); ctx->event_pool.pop_back(); }
+      else if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); e = nullptr; }
+      if (e != nullptr && cudaEventRecord(e, ctx->streams[i]) == cudaSuccess) {
+        fence->events.push_back(e);
+        ++i;
+      } else {
+        // a stream that was destroyed by its owner (or a context that is shutting down) has nothing queued
+        cudaGetLastError();
+        if (e != nullptr) ctx->event_pool.push_back(e);
+        ctx->streams.erase(ctx->streams.begin() + static_cast<long>(i));
+      }
+    }
+    if (prev >= 0 && prev != ctx->device) cudaSetDevice(prev);
+  }
+  ctx->arena->release_deferred(off, fence);   // (the fence's destructor takes ctx->mu: call it unlocked)
+}
+
+// ---------------------------------------------------------------------------------------------
 // Per-dispatch state shared between the phases of one dispatch (and kept by the handle)
 // ---------------------------------------------------------------------------------------------
 struct DispatchState {
@@ -197,8 +269,6 @@ struct GemmArgs {
   std::optional<at::Tensor> out0, out1, preact, row_weight, row_token, dl_dweight;
   std::optional<at::Tensor> scatter_local, row_src, row_k_slot;
   std::optional<at::Tensor> tile_stripes_done, k_remaining, done_per_token;
-  int dbg_flags = 0;
-  std::optional<at::Tensor> dbg_cycles;             // int64 [num_ctas, 16], only filled by -DSEP_EPI_TIMING builds
   // remote scatter / remote dL/dweight return: (record kind, epoch, word) naming the buffer on every rank
   std::vector<int> remote_out;
   std::vector<int> remote_dw;
@@ -232,6 +302,9 @@ class Runtime {
     SEP_CUDA_CHECK(cudaMalloc(&base_, arena_bytes_));
     SEP_CUDA_CHECK(cudaMemset(base_, 0, ctl_.total_bytes));
     arena_ = std::make_shared<Arena>(ctl_.total_bytes, arena_bytes_ - ctl_.total_bytes);
+    release_ctx_ = std::make_shared<ReleaseCtx>();
+    release_ctx_->arena = arena_;
+    release_ctx_->device = device_;
     for (int i = 0; i < kMaxRanks; ++i) peer_base_[i] = nullptr;
     peer_base_[rank] = base_;
     // device scratch: status block, launch-gate flags, launch-local counters
@@ -256,6 +329,10 @@ class Runtime {
     if (destroyed_) return;
     destroyed_ = true;
     cudaDeviceSynchronize();
+    if (release_ctx_) {
+      { std::lock_guard<std::mutex> g(release_ctx_->mu); release_ctx_->dead = true; }
+      arena_->sweep(true);
+    }
     for (int i = 0; i < num_ranks_; ++i)
       if (i != rank_ && peer_base_[i] != nullptr && opened_[i]) cudaIpcCloseMemHandle(peer_base_[i]);
     // Tensors over arena blocks may outlive the runtime object; the slab itself is only freed when
@@ -310,30 +387,34 @@ class Runtime {
   // Event at the point of the current stream where the most recent backward left its last kernel that talks to
   // peers: what follows (the dW GEMMs) is local.  A host-to-device prefetch that waits on it stays clear of the
   // kernels that synchronise at system scope, which measured markedly slower while a PCIe copy was in flight.
-  void mark_local_phase() { local_phase_ = std::make_shared<EventHandle>(at::cuda::getCurrentCUDAStream()); }
+  void mark_local_phase() { local_phase_ = std::make_shared<EventHandle>(stream()); }
   std::optional<EventHandle> local_phase_event() const { return local_phase_ ? std::optional<EventHandle>(*local_phase_) : std::nullopt; }
-  // Debug builds (-DSEP_EPI_TIMING): int64 [num_sms, 16] that the next fused dispatch+GEMM-A launches fill with timestamps.
-  void set_debug_tensor(const at::Tensor& t) { dbg_fused_a_ = t; }
   void set_push_order(int n) { SEP_ASSERT(n == 0 || n == 1, "push order must be 0 or 1"); push_order_ = n; }
   void set_active_push_warps(int n) { SEP_ASSERT(n >= 0 && n <= 16, "active push warps must be 0..16"); active_push_warps_ = n; }
   void set_pairs_per_chunk(int n) { SEP_ASSERT(n >= 1 && n <= 32, "pairs per chunk must be 1..32"); pairs_per_chunk_ = n; }
+  // Blocks whose tensors died count as free here even while the arena still holds them back for queued work.
   int64_t arena_bytes_in_use() const { return static_cast<int64_t>(arena_->bytes_in_use()); }
+  int64_t arena_blocks_parked() const { arena_->sweep(false); return static_cast<int64_t>(arena_->num_parked()); }
   int64_t arena_high_water() const { return static_cast<int64_t>(arena_->high_water()); }
   int64_t arena_capacity() const { return static_cast<int64_t>(arena_->capacity()); }
 
-  // A tensor over a fresh arena block; the block returns to the arena when the tensor dies.
+  // A tensor over a fresh arena block.  When the tensor dies the block is parked until everything queued so far on
+  // the streams this runtime has used (launches and allocations) has completed, then returns to the arena: a
+  // kernel that still reads or writes the block is never overtaken by the block's next owner.  Work on a stream
+  // the runtime has never seen is not covered: make that stream wait for the tensor's last use, or keep a reference.
   at::Tensor alloc_symmetric(const std::vector<int64_t>& sizes, at::ScalarType dtype, bool zero, size_t* offset_out = nullptr) {
     int64_t n = 1;
     for (auto s : sizes) n *= s;
     const size_t bytes = static_cast<size_t>(n) * c10::elementSize(dtype);
     const size_t off = arena_->allocate(bytes);
     if (offset_out != nullptr) *offset_out = off;
-    std::shared_ptr<Arena> arena = arena_;
+    std::shared_ptr<ReleaseCtx> ctx = release_ctx_;
     std::shared_ptr<void> guard = arena_guard_;
     void* ptr = static_cast<char*>(base_) + off;
-    auto t = at::from_blob(ptr, sizes, [arena, guard, off](void*) { arena->release(off); },
+    auto t = at::from_blob(ptr, sizes, [ctx, guard, off](void*) { release_block(ctx, off); },
                            at::TensorOptions().dtype(dtype).device(at::kCUDA, device_));
-    if (zero && bytes > 0) SEP_CUDA_CHECK(cudaMemsetAsync(ptr, 0, bytes, at::cuda::getCurrentCUDAStream()));
+    if (zero && bytes > 0) SEP_CUDA_CHECK(cudaMemsetAsync(ptr, 0, bytes, stream()));
+    else stream();
     return t;
   }
   bool is_symmetric(const at::Tensor& t) const {
@@ -443,7 +524,7 @@ class Runtime {
     p.recv_channel_prefix_matrix = st->recv_channel_prefix_matrix.data_ptr<int>();
     p.blocks_done = counters_ + 0;
     p.host = host_dev_; p.status = status_; p.wait_budget_ns = budget_ns_;
-    ++launches_; launch_dispatch_metadata(p, at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_dispatch_metadata(p, stream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
 
@@ -516,7 +597,7 @@ class Runtime {
     f.pool_arrival_count = reinterpret_cast<int*>(at_off(7));
     f.recv_src = reinterpret_cast<int2*>(at_off(8));
     f.y_done_per_token = reinterpret_cast<long long*>(at_off(9));
-    ++launches_; launch_fill_tile_metadata(f, at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_fill_tile_metadata(f, stream());
     SEP_CUDA_CHECK(cudaGetLastError());
 
     BufferRecord& r = st->record;
@@ -524,7 +605,7 @@ class Runtime {
     r.pool_src = sub_off[3]; r.recv_token_to_slots = sub_off[4]; r.k_local_total = sub_off[5];
     r.k_local_remaining = sub_off[6]; r.arrival_count = sub_off[7]; r.recv_src = sub_off[8];
     st->push_epoch = ++epochs_[kKindDispatch];
-    st->metadata_done_event = EventHandle(at::cuda::getCurrentCUDAStream());
+    st->metadata_done_event = EventHandle(stream());
   }
 
   // The i-th array of the per-dispatch slab (order: pool_topk_weight, pool_recv_token, pool_k_slot, pool_src,
@@ -584,7 +665,7 @@ class Runtime {
     PushParams p = make_push_params(*st, st->x, false, st->record, kKindDispatch, st->push_epoch, flags,
                                     st->pool_arrival_count.data_ptr<int>(), 2);
     if (flags & 2) ++gate_issued_[0];
-    ++launches_; launch_dispatch_push(p, num_blocks, at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_dispatch_push(p, num_blocks, stream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
 
@@ -599,7 +680,7 @@ class Runtime {
     g->record.pool = off_pool;
     g->record.arrival_count = off_cnt;
     g->epoch = ++epochs_[kKindDispatchGrads];
-    g->started_event = EventHandle(at::cuda::getCurrentCUDAStream());
+    g->started_event = EventHandle(stream());
     return g;
   }
   void grads_push(const std::shared_ptr<DispatchState>& st, const std::shared_ptr<GradsState>& g, const at::Tensor& dl_dy,
@@ -609,7 +690,7 @@ class Runtime {
     PushParams p = make_push_params(*st, dl_dy, true, g->record, kKindDispatchGrads, g->epoch, flags,
                                     g->bwd_dispatch_arrival_count.data_ptr<int>(), 4);
     if (flags & 2) ++gate_issued_[1];
-    ++launches_; launch_dispatch_push(p, num_blocks, at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_dispatch_push(p, num_blocks, stream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
 
@@ -620,7 +701,7 @@ class Runtime {
                x.size(0) == st->num_recv_tokens && x.size(1) == st->hidden, "combine input must be contiguous [T_recv, H] bf16");
     SEP_ASSERT(done.scalar_type() == at::kLong && done.numel() == st->num_recv_tokens, "gate must be int64 [T_recv]");
     auto c = std::make_shared<CombineState>();
-    auto stream = at::cuda::getCurrentCUDAStream();
+    auto stream = this->stream();
     // Peers read these through NVLink, so they must sit in the arena.  Tensors the caller already
     // keeps there (handle.o, handle.y_done_per_token, Buffer.alloc_symmetric results) are used in
     // place, which is what lets the gate be written while this kernel runs.
@@ -657,7 +738,7 @@ class Runtime {
     fill_peers(p.peer_base); p.ctl = ctl_; p.own = c->record;
     p.blocks_done = counters_ + (is_fwd ? 6 : 7);
     p.status = status_; p.wait_budget_ns = budget_ns_;
-    ++launches_; launch_combine_pull(p, num_blocks, at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_combine_pull(p, num_blocks, stream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
 
@@ -666,7 +747,7 @@ class Runtime {
     BarrierParams p{};
     p.num_ranks = num_ranks_; p.rank = rank_; p.epoch = ++epochs_[kKindBarrier]; p.kind = kKindBarrier; p.wait = 1;
     fill_peers(p.peer_base); p.ctl = ctl_; p.status = status_; p.wait_budget_ns = budget_ns_;
-    ++launches_; launch_device_barrier(p, at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_device_barrier(p, stream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
   // Emulated ranks run one after another on one device: a barrier there is "every rank bumped its
@@ -742,9 +823,6 @@ class Runtime {
     if (a.k_remaining.has_value()) p.k_remaining = a.k_remaining->data_ptr<int>();
     if (a.done_per_token.has_value()) p.done_per_token = reinterpret_cast<long long*>(a.done_per_token->data_ptr<int64_t>());
     p.seq = a.seq; p.num_topk = a.num_topk;
-    p.dbg_flags = a.dbg_flags;
-    if (a.dbg_cycles.has_value()) p.dbg_cycles = reinterpret_cast<long long*>(a.dbg_cycles->data_ptr<int64_t>());
-    else if (dbg_fused_a_.defined() && a.fused_push && a.epilogue == kEpiSwiglu) p.dbg_cycles = reinterpret_cast<long long*>(dbg_fused_a_.data_ptr<int64_t>());
     p.num_ranks = num_ranks_; fill_peers(p.peer_base); p.ctl = ctl_;
     auto set_ref = [](RemoteRef& r, const std::vector<int>& v) {
       if (v.empty()) return;
@@ -809,16 +887,18 @@ class Runtime {
     }
     if (ppp == nullptr) n_ctas = static_cast<int>(std::min<int64_t>(n_ctas, std::max<int64_t>(total, 1)));
     ++launches_;
+    cudaError_t setup_error = cudaSuccess;
     const bool launched = launch_grouped_gemm(p, &ta, &tb, have_o0 ? &to0 : nullptr, have_o1 ? &to1 : nullptr, ppp, n_ctas,
-                                              at::cuda::getCurrentCUDAStream());
+                                              stream(), &setup_error);
     SEP_ASSERT(launched, "no grouped GEMM kernel for this combination of mode, operand layouts, epilogue and fused push");
+    SEP_CUDA_CHECK(setup_error);
     SEP_CUDA_CHECK(cudaGetLastError());
   }
 
   // A rank that received no rows has nothing to multiply, but it still takes part in the collective
   // halves of the fused kernels: its own rows must be pushed and its completion flags raised.
   void launch_without_tiles(const GemmArgs& a) {
-    auto stream = at::cuda::getCurrentCUDAStream();
+    auto stream = this->stream();
     if (a.fused_push) {
       PushParams pp = make_push_params(*a.fused_push, a.fused_push->x, false, a.fused_push->record, kKindDispatch,
                                        a.fused_push->push_epoch, a.push_flags & 3, a.fused_push->pool_arrival_count.data_ptr<int>(), 2);
@@ -951,7 +1031,7 @@ class Runtime {
   // ---- small ops ---------------------------------------------------------------------------------------
   void tile_producer(const at::Tensor& count, const at::Tensor& target, double delay_us) {
     ++launches_; launch_tile_producer(count.data_ptr<int>(), target.data_ptr<int>(), count.numel(), static_cast<long long>(delay_us * 1000.0),
-                         at::cuda::getCurrentCUDAStream());
+                         stream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
   void combine_reduce(const at::Tensor& out, const at::Tensor& rows, const at::Tensor& topk_idx, int num_experts) {
@@ -960,20 +1040,20 @@ class Runtime {
     if (out.size(0) == 0 || num_ranks_ == 1) return;
     SEP_ASSERT(rows.numel() == out.size(0) * topk_idx.size(1) * out.size(1), "rows must be [T * K, H]");
     ++launches_; launch_combine_reduce(out.data_ptr(), rows.data_ptr(), reinterpret_cast<const long long*>(topk_idx.data_ptr<int64_t>()),
-                          out.size(0), out.size(1), topk_idx.size(1), num_experts, num_ranks_, rank_, at::cuda::getCurrentCUDAStream());
+                          out.size(0), out.size(1), topk_idx.size(1), num_experts, num_ranks_, rank_, stream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
   at::Tensor pool_compress(const at::Tensor& pool, const at::Tensor& pool_recv_token, int64_t num_recv) {
     SEP_ASSERT(pool.is_contiguous() && pool.scalar_type() == at::kBFloat16 && pool.size(1) % 8 == 0, "pool must be contiguous bf16 with hidden % 8 == 0");
     auto out = at::empty({num_recv, pool.size(1)}, pool.options());
-    ++launches_; launch_pool_compress(pool.data_ptr(), out.data_ptr(), pool_recv_token.data_ptr<int>(), pool.size(0), pool.size(1), at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_pool_compress(pool.data_ptr(), out.data_ptr(), pool_recv_token.data_ptr<int>(), pool.size(0), pool.size(1), stream());
     SEP_CUDA_CHECK(cudaGetLastError());
     return out;
   }
   at::Tensor pool_expand(const at::Tensor& recv, const at::Tensor& pool_recv_token, int64_t tk_padded) {
     SEP_ASSERT(recv.is_contiguous() && recv.scalar_type() == at::kBFloat16 && recv.size(1) % 8 == 0, "recv must be contiguous bf16 with hidden % 8 == 0");
     auto out = at::empty({tk_padded, recv.size(1)}, recv.options());
-    ++launches_; launch_pool_expand(recv.data_ptr(), out.data_ptr(), pool_recv_token.data_ptr<int>(), tk_padded, recv.size(1), at::cuda::getCurrentCUDAStream());
+    ++launches_; launch_pool_expand(recv.data_ptr(), out.data_ptr(), pool_recv_token.data_ptr<int>(), tk_padded, recv.size(1), stream());
     SEP_CUDA_CHECK(cudaGetLastError());
     return out;
   }
@@ -1007,9 +1087,9 @@ class Runtime {
         g.mode = kVarlenM; g.epilogue = kEpiStoreF32; g.block_n = E > 128 ? 256 : 128;
         g.a = x; g.b = w_gate.unsqueeze(0); g.tile_id_to_expert = router_tiles_.narrow(0, 0, tiles); g.out0 = logits;
         grouped_gemm(g);
-        ++launches_; launch_router_finish(p, logits.data_ptr<float>(), static_cast<int>(E), at::cuda::getCurrentCUDAStream());
+        ++launches_; launch_router_finish(p, logits.data_ptr<float>(), static_cast<int>(E), stream());
       } else {
-        ++launches_; launch_router(p, at::cuda::getCurrentCUDAStream());
+        ++launches_; launch_router(p, stream());
       }
     }
     SEP_CUDA_CHECK(cudaGetLastError());
@@ -1020,6 +1100,12 @@ class Runtime {
 
  private:
   static constexpr int BM_ = kTileM;
+  // The current torch stream; remembered so that released arena blocks wait for the work queued on it.
+  at::cuda::CUDAStream stream() {
+    auto s = at::cuda::getCurrentCUDAStream();
+    if (s.stream() != last_stream_) { release_ctx_->note_stream(s.stream()); last_stream_ = s.stream(); }
+    return s;
+  }
   void fill_peers(void** dst) const { for (int i = 0; i < kMaxRanks; ++i) dst[i] = peer_base_[i]; }
   void finish_sync() {
     // keeps the slab alive as long as any arena tensor or the runtime itself exists
@@ -1042,6 +1128,8 @@ class Runtime {
   size_t arena_bytes_ = 0;
   std::shared_ptr<Arena> arena_;
   std::shared_ptr<void> arena_guard_;
+  std::shared_ptr<ReleaseCtx> release_ctx_;
+  cudaStream_t last_stream_ = reinterpret_cast<cudaStream_t>(-1);
   void* peer_base_[kMaxRanks];
   bool opened_[kMaxRanks] = {false, false, false, false, false, false, false, false};
   void* scratch_ = nullptr;
@@ -1060,7 +1148,6 @@ class Runtime {
   at::Tensor router_tiles_;            // zeros: every M tile of the router GEMM belongs to "expert" 0
   int push_order_ = 0;
   std::shared_ptr<EventHandle> local_phase_;
-  at::Tensor dbg_fused_a_;
   int gate_issued_[8];
   bool available_ = false, destroyed_ = false;
 };
@@ -1071,10 +1158,25 @@ class Runtime {
 // Host-only arena exerciser (no CUDA calls) so the allocator logic is testable on a CPU-only box.
 // -------------------------------------------------------------------------------------------------
 struct ArenaProbe {
+  // A fence the test completes by hand: `open_fences()` makes every fence handed out so far ready.
+  struct ManualFence : sep::ArenaFence {
+    std::shared_ptr<std::atomic<int>> opened; int ticket;
+    bool ready() override { return opened->load() >= ticket; }
+    void wait() override { int t = opened->load(); while (t < ticket && !opened->compare_exchange_weak(t, ticket)) {} }
+  };
   sep::Arena arena;
+  std::shared_ptr<std::atomic<int>> opened = std::make_shared<std::atomic<int>>(0);
+  int tickets = 0;
   ArenaProbe(int64_t offset, int64_t size) : arena(offset, size) {}
   int64_t allocate(int64_t bytes) { return arena.allocate(bytes); }
   void release(int64_t off) { arena.release(off); }
+  void release_deferred(int64_t off) {
+    auto f = std::make_shared<ManualFence>();
+    f->opened = opened; f->ticket = ++tickets;
+    arena.release_deferred(off, f);
+  }
+  void open_fences() { opened->store(tickets); }
+  int64_t parked() { arena.sweep(false); return arena.num_parked(); }
   int64_t in_use() const { return arena.bytes_in_use(); }
   int64_t high_water() const { return arena.high_water(); }
   int64_t capacity() const { return arena.capacity(); }
@@ -1094,6 +1196,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   py::class_<ArenaProbe>(m, "ArenaProbe")
       .def(py::init<int64_t, int64_t>())
       .def("allocate", &ArenaProbe::allocate).def("release", &ArenaProbe::release)
+      .def("release_deferred", &ArenaProbe::release_deferred).def("open_fences", &ArenaProbe::open_fences)
+      .def("parked", &ArenaProbe::parked)
       .def("in_use", &ArenaProbe::in_use).def("high_water", &ArenaProbe::high_water)
       .def("capacity", &ArenaProbe::capacity).def("free_blocks", &ArenaProbe::free_blocks);
 
@@ -1149,7 +1253,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       RW(mode) RW(epilogue) RW(block_n) RW(num_ctas) RW(a_mn_major) RW(b_mn_major) RW(a) RW(b)
       RW(tile_id_to_expert) RW(expert_pool_block_offset) RW(expert_frequency) RW(arrival_count) RW(arrival_target)
       RW(out0) RW(out1) RW(preact) RW(row_weight) RW(row_token) RW(dl_dweight) RW(scatter_local) RW(row_src) RW(row_k_slot)
-      RW(tile_stripes_done) RW(k_remaining) RW(done_per_token) RW(dbg_cycles) RW(dbg_flags) RW(remote_out) RW(remote_dw)
+      RW(tile_stripes_done) RW(k_remaining) RW(done_per_token) RW(remote_out) RW(remote_dw)
       RW(num_topk) RW(seq) RW(num_m_tiles) RW(started_flag)
       RW(tail) RW(tail_kind) RW(tail_wait) RW(fused_push) RW(fused_push_grads) RW(fused_push_routing) RW(fused_push_rows)
       RW(push_flags);
@@ -1171,13 +1275,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_property_readonly("num_ranks", &Runtime::num_ranks)
       .def_property_readonly("num_channels", &Runtime::num_channels)
       .def("launch_count", &Runtime::launch_count)
-      .def("set_debug_tensor", &Runtime::set_debug_tensor)
       .def("set_pairs_per_chunk", &Runtime::set_pairs_per_chunk)
       .def("set_active_push_warps", &Runtime::set_active_push_warps)
       .def("set_push_order", &Runtime::set_push_order)
       .def("set_router_on_tensor_cores", &Runtime::set_router_on_tensor_cores)
       .def("arena_bytes_in_use", &Runtime::arena_bytes_in_use)
       .def("arena_high_water", &Runtime::arena_high_water)
+      .def("arena_blocks_parked", &Runtime::arena_blocks_parked)
       .def("arena_capacity", &Runtime::arena_capacity)
       .def("alloc_symmetric", [](Runtime& r, const std::vector<int64_t>& sizes, py::object dtype, bool zero) {
         return r.alloc_symmetric(sizes, torch::python::detail::py_object_to_dtype(dtype), zero);

@@ -100,6 +100,28 @@ def test_arena_zero_size_and_exhaustion():
 
 
 @needs_ext
+def test_arena_deferred_release_waits_for_its_fence():
+    """A block whose tensor died while work on it may still be queued is not handed out again before its
+    fence completes; when nothing else fits, allocate() waits for the fence instead of failing."""
+    C = _ext.load()
+    a = C.ArenaProbe(0, 64 * 1024)
+    x = a.allocate(40_000)
+    a.release_deferred(x)
+    assert a.in_use() == 0 and a.parked() == 1          # logically free, physically held back
+    y = a.allocate(20_000)
+    assert y != x and not (x <= y < x + 40_000)          # served from the untouched remainder
+    a.open_fences()
+    assert a.parked() == 0
+    z = a.allocate(40_000)
+    assert z == x                                        # reusable once the fence is ready
+    a.release_deferred(z)
+    w = a.allocate(40_000)                               # only fits by waiting for z's fence
+    assert w == x and a.parked() == 0
+    a.release(w); a.release(y)
+    assert a.in_use() == 0 and a.free_blocks() == 1
+
+
+@needs_ext
 def test_arena_random_stress_keeps_blocks_disjoint():
     import random
     C = _ext.load()
