@@ -15,6 +15,14 @@ dispatch-heavy shape (4096 tokens/rank, hidden 7168, 32 experts/rank, top-8, ffn
 experts/rank, top-8 distinct experts sampled Zipf(1.2) over expert ids, ffn 2048, forward GEMM
 recomputed in backward).  ``--impl nccl_baseline`` times the library all-to-all + cuBLAS layer.
 
+Before anything is timed, a one-step ORACLE GATE compares ``out`` and ``dL/dx`` of 64 sampled tokens per
+rank with an fp32 evaluation of the layer on the gathered global weights and refuses to print a value on a
+mismatch.  The product arm runs in capacity mode by default (``--capacity-factor 1.5``: fixed receive regions
+of 1.5 x the balanced load, no host read per forward; an overflow would fail the run); ``--capacity-factor 0``
+selects exact, host-sized buffers.  After the product arm the library baseline (NCCL all-to-all + cuBLAS
+per-expert GEMMs) is timed in the same invocation on the same inputs and ``vs_baseline`` is their ratio; a
+``sustained`` block repeats the product measurement for at least two seconds of continuous steps.
+
 Timing: W (>= 3) untimed warm-up steps, then exactly K steps, the whole region bracketed by a
 barrier and a device synchronize on both sides.  Each step sits between its own pair of CUDA events
 on the launching stream and a 256 MiB buffer (larger than the 126 MB L2) is rewritten between
@@ -65,6 +73,55 @@ def reference_arm(args):
     return 0
 
 
+def oracle_gate(layer, routing, x_dev, dy_dev, group, world, rank, E, K, samples=64):
+    """One forward + backward of the first layer; ``out`` and ``dL/dx`` of ``samples`` tokens of this rank are
+    compared with an fp32 evaluation on the gathered global expert weights.  bf16 inputs, fp32 accumulation:
+    the tolerance is 2 % of the largest reference magnitude plus 2 % relative."""
+    import torch
+    import torch.distributed as dist
+
+    idx, w, in_rank = routing
+    h = x_dev.detach().requires_grad_(True)
+    out = layer.experts(h, idx, w, in_rank)
+    out.backward(dy_dev)
+    torch.cuda.synchronize()
+    for p in layer.parameters():
+        p.grad = None
+    w1, w2 = layer.w1.detach(), layer.w2.detach()
+    if world > 1:
+        w1_all = [torch.empty_like(w1) for _ in range(world)]
+        w2_all = [torch.empty_like(w2) for _ in range(world)]
+        dist.all_gather(w1_all, w1.contiguous(), group=group)
+        dist.all_gather(w2_all, w2.contiguous(), group=group)
+        w1g, w2g = torch.cat(w1_all), torch.cat(w2_all)
+    else:
+        w1g, w2g = w1, w2
+    T = x_dev.shape[0]
+    sel = torch.linspace(0, T - 1, min(samples, T)).long().to(x_dev.device) if T > 0 else torch.zeros(0, dtype=torch.long, device=x_dev.device)
+    xs = x_dev[sel].float().requires_grad_(True)
+    acc = torch.zeros(sel.numel(), x_dev.shape[1], device=x_dev.device)
+    for k in range(K):
+        e = idx[sel, k]
+        for ee in e.unique().tolist():
+            if ee < 0:
+                continue
+            m = (e == ee).nonzero().squeeze(1)
+            hh = xs[m] @ w1g[ee].float().t()
+            act = torch.nn.functional.silu(hh[:, 0::2]) * hh[:, 1::2]
+            acc = acc.index_add(0, m, (act @ w2g[ee].float().t()) * w[sel][m, k:k + 1].float())
+    acc.backward(dy_dev[sel].float())
+    got_o, want_o, got_d, want_d = out[sel].float(), acc.detach(), h.grad[sel].float(), xs.grad
+    out_scale = float(want_o.abs().max()) if sel.numel() else 1.0
+    dx_scale = float(want_d.abs().max()) if sel.numel() else 1.0
+    out_err = float((got_o - want_o).abs().max()) if sel.numel() else 0.0
+    dx_err = float((got_d - want_d).abs().max()) if sel.numel() else 0.0
+    ok = bool(((got_o - want_o).abs() <= 2e-2 * out_scale + 2e-2 * want_o.abs()).all()) and \
+        bool(((got_d - want_d).abs() <= 2e-2 * dx_scale + 2e-2 * want_d.abs()).all()) and \
+        bool(torch.isfinite(out.float()).all()) and bool(torch.isfinite(h.grad.float()).all())
+    return {"ok": ok, "tokens": int(sel.numel()), "out_max_abs_err": out_err, "dx_max_abs_err": dx_err,
+            "out_scale": out_scale, "dx_scale": dx_scale}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -75,6 +132,13 @@ def main():
     ap.add_argument("--fused", type=int, default=1)
     ap.add_argument("--ckpt-level", type=int, default=None, help="0/1/2; default: the config's (0 unless it names one)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--capacity-factor", type=float, default=None,
+                    help="fixed receive regions of this many times the balanced load (no host read per forward); "
+                         "0 = exact host-sized buffers; default 1.5 (0 for the Zipf-routed config)")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the NCCL + cuBLAS arm that fills vs_baseline")
+    ap.add_argument("--baseline-steps", type=int, default=5)
+    ap.add_argument("--sustained-seconds", type=float, default=2.0, help="0 skips the sustained block")
+    ap.add_argument("--no-gate", action="store_true", help="skip the oracle gate (debugging only)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -117,10 +181,13 @@ def main():
     torch.manual_seed(1234 + rank)
 
     buffer = None
+    if args.capacity_factor is None:
+        args.capacity_factor = 0.0 if zipf else 1.5
     if args.impl == "streamep_b200":
         # Zipf routing can send nearly every pair to one rank: size the arena for that
         buffer = make_buffer(group, T_max, H, K, E, layers_in_flight=L, world_size=world,
-                             imbalance=1.6 * world if zipf else 1.5)
+                             imbalance=1.6 * world if zipf else 1.5,
+                             capacity_factor=args.capacity_factor if args.capacity_factor > 0 else None)
         layers = [StreamMoE(H, I, E, K, buffer, fused=bool(args.fused), activation_checkpoint_level=args.ckpt_level,
                             device=dev, seed=100 + i) for i in range(L)]
     else:
@@ -159,6 +226,20 @@ def main():
 
     def launches():
         return buffer.runtime.launch_count() if buffer is not None else 0
+
+    # ---------------------------------------------------------------- oracle gate (one step, untimed)
+    gate = None
+    if not args.no_gate:
+        gate = oracle_gate(layers[0], routing[0], x_dev, dy_dev, group, world, rank, E, K)
+        ok = torch.tensor([1.0 if gate["ok"] else 0.0], device=dev)
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok[0]) == 0.0:
+            print(f"bench.py: rank {rank}: ORACLE GATE FAILED {gate}", file=sys.stderr)
+            if world > 1:
+                dist.barrier(device_ids=[local_rank])
+                dist.destroy_process_group()
+            return 3
 
     # ---------------------------------------------------------------- device-timed value
     for _ in range(max(args.warmup, 3)):
@@ -257,11 +338,59 @@ def main():
         if buffer is not None:
             buffer.check_status()
 
+    # ---------------------------------------------------------------- sustained: >= N seconds of continuous steps
+    sustained = None
+    if args.sustained_seconds > 0:
+        n_sus = max(int(args.sustained_seconds * 1e3 / max(ms, 1e-3)) + 1, args.steps)
+        barrier()
+        sampler2 = ClockSampler(local_rank).start()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_sus)]
+        for i in range(n_sus):
+            flush.zero_()
+            evs[i][0].record()
+            step_device()
+            evs[i][1].record()
+        barrier()
+        clocks2 = sampler2.stop()
+        tail = evs[n_sus // 2:]                       # the second half: clocks have settled under the power cap
+        sustained = (sum(a.elapsed_time(b) for a, b in tail) / len(tail), n_sus, clocks2)
+        if buffer is not None:
+            buffer.check_status()
+
+    # ---------------------------------------------------------------- library baseline on the same inputs
+    base_ms = None
+    if args.impl == "streamep_b200" and not args.no_baseline:
+        base_layers = [NcclBaselineMoE(H, I, E, K, group, device=dev, seed=100 + i) for i in range(L)]
+        base_params = [p for layer in base_layers for p in layer.parameters()]
+
+        def step_base():
+            h = x_dev.detach().requires_grad_(True)
+            cur = h
+            for layer, (idx, w, in_rank) in zip(base_layers, routing):
+                cur = layer.experts(cur, idx, w, in_rank)
+            cur.backward(dy_dev)
+            for p in base_params:
+                p.grad = None
+
+        for _ in range(3):
+            step_base()
+            flush.zero_()
+        barrier()
+        evb = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.baseline_steps)]
+        for i in range(args.baseline_steps):
+            flush.zero_()
+            evb[i][0].record()
+            step_base()
+            evb[i][1].record()
+        barrier()
+        base_ms = sum(a.elapsed_time(b) for a, b in evb) / args.baseline_steps
+        del base_layers, base_params
+
     # ---------------------------------------------------------------- reduce over ranks, report
-    vals = torch.tensor([ms, e2e[0] if e2e else 0.0], device=dev)
+    vals = torch.tensor([ms, e2e[0] if e2e else 0.0, sustained[0] if sustained else 0.0, base_ms or 0.0], device=dev)
     if world > 1:
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
-    ms_max, ms_e2e_max = float(vals[0]), float(vals[1])
+    ms_max, ms_e2e_max, ms_sus_max, ms_base_max = (float(v) for v in vals)
     if rank == 0:
         tokens_per_step = sum(tokens_all)
         value = tokens_per_step / (ms_max * 1e-3)
@@ -273,25 +402,46 @@ def main():
                 peaks = json.load(f)
         except OSError:
             pass
-        peak = peaks.get("bf16_tflops_sustained", 1400.0)
+        # a timed region shorter than about a second runs in the burst regime (clocks not yet pulled down by the
+        # power cap): its roofline denominator is the burst cuBLAS figure, the sustained block uses the sustained one
+        region_s = ms_max * 1e-3 * args.steps
+        peak_burst, peak_sus = peaks.get("bf16_tflops", 1590.0), peaks.get("bf16_tflops_sustained", 1400.0)
+        peak = peak_burst if region_s < 1.0 else peak_sus
         out = {
             "metric": "moe_layer_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_max, "higher_is_better": True,
             "scaling": "weak" if c["experts_total"] is None else "weak (tokens per rank fixed, total experts fixed)",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (x ~ N(0,1), random-init weights ~ N(0,0.02))",
+            "vs_baseline": (ms_base_max / ms_max) if base_ms else None, "dtype": "bf16", "data": "synthetic (x ~ N(0,1), random-init weights ~ N(0,0.02))",
             "impl": args.impl,
             "config": {"model": f"moe_layer[{args.config}] H={H} ffn={I} E={E} ({E // world}/rank) top{K} layers={L}",
                        "global_batch": tokens_per_step, "seq_len": T if len(set(tokens_all)) == 1 else tokens_all,
                        "routing": "zipf(1.2) over expert ids, top-k distinct" if zipf else "linear router on x, softmax top-k renormalised",
                        "parallelism": f"ep{world}",
                        "fused": bool(args.fused), "activation_checkpoint_level": args.ckpt_level,
+                       "sizing": (f"capacity mode, factor {args.capacity_factor} (fixed receive regions, no host read per forward)"
+                                  if buffer is not None and buffer.capacity_mode else "exact (host reads the receive sizes every forward)"),
+                       "timed_value_covers": "layer forward + backward with routing as an input (computed once, untimed); "
+                                             "the router kernel is inside e2e",
                        "l2_flush": "256 MiB buffer rewritten between timed iterations"},
             "clocks": clocks,
             "gpu_launches": int(l1 - l0),
             "tflops_per_gpu": flops / (ms_max * 1e-3) / 1e12,
-            "frac_of_measured_bf16_sustained": flops / (ms_max * 1e-3) / 1e12 / peak,
+            "frac_of_measured_bf16_peak": flops / (ms_max * 1e-3) / 1e12 / peak,
+            "roofline_denominator": f"{'burst' if region_s < 1.0 else 'sustained'} cuBLAS bf16 {peak:.0f} TFLOP/s (timed region {region_s * 1e3:.0f} ms)",
             "wall_ms_per_step_incl_flush": t_wall * 1e3 / args.steps,
         }
+        if gate is not None:
+            out["oracle_gate"] = {k: gate[k] for k in ("tokens", "out_max_abs_err", "dx_max_abs_err", "out_scale", "dx_scale")}
+        if base_ms:
+            out["baseline"] = {"impl": "nccl all_to_all_single + cuBLAS per-expert GEMMs (streamep_b200.parallel.nccl_baseline)",
+                               "ms_per_step": ms_base_max, "steps": args.baseline_steps,
+                               "value": tokens_per_step / (ms_base_max * 1e-3)}
+        if sustained:
+            out["sustained"] = {"ms_per_step": ms_sus_max, "value": tokens_per_step / (ms_sus_max * 1e-3),
+                                "steps": sustained[1], "measured_over": "second half of the steps",
+                                "seconds": ms_sus_max * 1e-3 * sustained[1], "clocks": sustained[2],
+                                "tflops_per_gpu": flops / (ms_sus_max * 1e-3) / 1e12,
+                                "frac_of_measured_bf16_sustained": flops / (ms_sus_max * 1e-3) / 1e12 / peak_sus}
         if e2e:
             out["e2e"] = {"value": tokens_per_step / (ms_e2e_max * 1e-3), "unit": "tokens/s",
                           "ms_per_step": ms_e2e_max, "h2d_bytes_per_step": e2e[1], "d2h_bytes_per_step": e2e[2],

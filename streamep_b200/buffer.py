@@ -21,7 +21,7 @@ from typing import Any, List, Optional, Sequence, Tuple
 import torch
 
 from . import _ext
-from .errors import StreamEPError, StreamEPTimeout
+from .errors import StreamEPError, StreamEPOverflow, StreamEPTimeout
 
 topk_idx_t = torch.int64
 
@@ -212,10 +212,82 @@ class Buffer:
     # ------------------------------------------------------------------ failure reporting
     def check_status(self) -> None:
         """Synchronise the device and raise :class:`StreamEPTimeout` if any bounded
-        device wait gave up since the last check.  The context stays usable."""
+        device wait gave up since the last check (:class:`StreamEPOverflow` if a
+        capacity-mode dispatch did not fit its region).  The context stays usable."""
         msg = self.runtime.poll_status(True)
         if msg:
+            if "capacity overflow" in msg:
+                raise StreamEPOverflow(f"rank {self.rank}: {msg}; {self._overflow_text()}")
             raise StreamEPTimeout(f"rank {self.rank}: {msg}")
+
+    # ------------------------------------------------------------------ capacity mode
+    def enable_capacity_mode(self, max_tokens: int, hidden: int, num_topk: int, num_experts: int, *,
+                             capacity_factor: float = 1.5, layers_in_flight: int = 1) -> None:
+        """Switch the fused layer (``stream_moe_func``) of this buffer to fixed receive regions, which removes
+        the host read of the receive sizes from every forward (the reference pays the same read:
+        csrc/stream_ep.cpp:741-759).
+
+        Collective: every rank calls it once, right after constructing the buffer, with the same arguments.
+        Each of the ``layers_in_flight`` regions holds a pool of ``capacity_factor x max_tokens x num_topk``
+        rows (the balanced load is ``max_tokens x num_topk``) plus one padding tile per local expert.  Kernels
+        then take the live sizes from device memory; a dispatch whose layout exceeds the capacity on any rank
+        is run as an EMPTY dispatch by all ranks (they all see the same counts), recorded in the status block
+        and in ``overflow_info()``, and reported by ``check_status()`` as :class:`StreamEPOverflow` - i.e. one
+        step late, without a device sync in the step itself.  Dispatches whose shape differs from the
+        configured one (more tokens, another hidden size or top-k) keep using exactly sized buffers.
+        The stand-alone ``dispatch`` keeps exact sizing unless called with ``capacity_mode=True``."""
+        import torch.distributed as dist
+
+        R = self.group_size
+        el = max(num_experts // R, 1)
+        rows = int(max_tokens * num_topk * capacity_factor) + 128 * el
+        rows_cap = (rows + 127) // 128 * 128
+        recv_cap = min(max_tokens * R, rows_cap)
+        base = self.runtime.enable_static(int(layers_in_flight), int(max_tokens), int(hidden), int(num_topk),
+                                          int(rows_cap), int(recv_cap))
+        # the regions must sit at the same arena offset on every rank
+        if self._local is not None:
+            world = self._local[0]
+            world._static_bases[self.rank] = base
+            if all(b is not None for b in world._static_bases) and len(set(world._static_bases)) != 1:
+                raise StreamEPError(f"capacity-mode regions ended up at different arena offsets: {world._static_bases}")
+        elif R > 1:
+            every = [None] * R
+            dist.all_gather_object(every, base, self.group)
+            if len(set(every)) != 1:
+                raise StreamEPError(f"capacity-mode regions ended up at different arena offsets: {every}; "
+                                    "call enable_capacity_mode right after constructing the Buffer on every rank")
+            dist.barrier(self.group)
+
+    @staticmethod
+    def capacity_mode_bytes(max_tokens: int, hidden: int, num_topk: int, num_experts: int, num_ranks: int, *,
+                            capacity_factor: float = 1.5, layers_in_flight: int = 1) -> int:
+        """Arena bytes :meth:`enable_capacity_mode` takes for these arguments (add them to ``num_nvl_bytes``)."""
+        el = max(num_experts // num_ranks, 1)
+        rows = (int(max_tokens * num_topk * capacity_factor) + 128 * el + 127) // 128 * 128
+        recv = min(max_tokens * num_ranks, rows)
+        region = rows * hidden * 2 + rows * 20 + recv * (num_topk * 4 + 24) + rows // 128 * 4 + 16 * 1024
+        grads = 2 * (rows * hidden * 2 + rows // 128 * 4 + 2048)
+        landing = 2 * max_tokens * num_topk * hidden * 2 if num_ranks > 1 else 0
+        dwt = 2 * (max_tokens * num_topk * 4 + 1024)
+        return int(layers_in_flight * region + grads + landing + dwt + (1 << 20))
+
+    @property
+    def capacity_mode(self) -> bool:
+        return self.runtime is not None and self.runtime.static_enabled()
+
+    def overflow_info(self) -> dict:
+        """Capacity-mode overflow record, read from pinned host memory (no device sync): how many dispatches
+        overflowed so far and what the last one would have needed."""
+        c, epoch, tiles, recv = self.runtime.overflow_info()
+        return {"count": int(c), "epoch": int(epoch), "needed_tiles": int(tiles), "needed_recv_tokens": int(recv)}
+
+    def _overflow_text(self) -> str:
+        info, cap = self.overflow_info(), self.runtime.static_capacity()
+        if not cap:
+            return ""
+        return (f"needed {info['needed_tiles']} tiles / {info['needed_recv_tokens']} recv tokens on the fullest rank, "
+                f"capacity is {cap[2] // 128} tiles / {cap[3]} recv tokens: raise capacity_factor")
 
     def set_timeout_ms(self, ms: int) -> None:
         self.runtime.set_timeout_ms(int(ms))
@@ -367,7 +439,7 @@ class Buffer:
         return max(1, int(n))
 
     # ------------------------------------------------------------------ dispatch
-    def _dispatch_begin(self, x, topk_idx, topk_weights, num_experts, tile_m, dispatch_seq):
+    def _dispatch_begin(self, x, topk_idx, topk_weights, num_experts, tile_m, dispatch_seq, capacity_mode=False):
         if dispatch_seq is None:
             self._next_seq += 1
             seq = self._next_seq
@@ -376,7 +448,7 @@ class Buffer:
         if topk_idx.dtype != torch.int64:
             topk_idx = topk_idx.to(torch.int64)
         st = self.runtime.dispatch_begin(x.contiguous(), topk_idx.contiguous(),
-                                         topk_weights.contiguous().float(), num_experts, tile_m, seq)
+                                         topk_weights.contiguous().float(), num_experts, tile_m, seq, bool(capacity_mode))
         return st, seq
 
     def _make_handle(self, st, is_token_in_rank, seq, tile_m) -> StreamingHandle:
@@ -397,7 +469,7 @@ class Buffer:
     def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
                  is_token_in_rank: Optional[torch.Tensor], num_experts: int, *,
                  expert_alignment: int = 1, tile_m: int = 128, dispatch_seq: Optional[int] = None,
-                 config=None, launch_push: bool = True):
+                 config=None, launch_push: bool = True, capacity_mode: bool = False):
         """Pool-layout dispatch (reference: stream_ep/buffer.py:493-610).
 
         Two kernels and one host poll: the metadata kernel (count exchange +
@@ -409,9 +481,14 @@ class Buffer:
 
         ``launch_push=False`` stops before the push kernel (the fused
         dispatch+GEMM-A kernel of ``stream_moe`` ships the rows itself).
+
+        ``capacity_mode=True`` (after :meth:`enable_capacity_mode`) receives into a fixed region without the
+        host read: the handle's tensors then span the region's capacity (``total_tiles``, ``TK_padded`` and
+        ``num_recv_tokens`` are capacities, tiles past the live count have target 0) and the live sizes are
+        the device tensor ``handle._dispatch_out.dev_sizes``.
         """
         assert expert_alignment == 1, "expert_alignment other than 1 is not supported"
-        st, seq = self._dispatch_begin(x, topk_idx, topk_weights, num_experts, tile_m, dispatch_seq)
+        st, seq = self._dispatch_begin(x, topk_idx, topk_weights, num_experts, tile_m, dispatch_seq, capacity_mode)
         cfg = self.get_dispatch_config(self.group_size) if config is None else config
         if not self._emulated:
             self.runtime.dispatch_metadata(st, 3)
@@ -443,12 +520,13 @@ class Buffer:
 
     # ------------------------------------------------------------------ dispatch_grads
     def dispatch_grads(self, handle: StreamingHandle, dL_dy: torch.Tensor, *,
-                       dispatch_seq: Optional[int] = None, config=None, launch_push: bool = True):
+                       dispatch_seq: Optional[int] = None, config=None, launch_push: bool = True,
+                       fused_buffers: bool = False):
         """Backward dispatch along the forward routing (reference:
         stream_ep/buffer.py:613-667).  Returns ``(dL_do_pool,
         bwd_dispatch_arrival_count, grads_started_event)``."""
         st = handle._dispatch_out
-        g = self.runtime.grads_begin(st)
+        g = self.runtime.grads_begin(st, fused_buffers)
         if launch_push:
             cfg = self.get_dispatch_config(self.group_size) if config is None else config
             dL_dy = dL_dy.contiguous()
@@ -532,6 +610,7 @@ class LocalWorld:
         self.num_ranks = num_ranks
         self._barrier = threading.Barrier(num_ranks)
         self._in_run = threading.local()
+        self._static_bases = [None] * num_ranks
         self.buffers: List[Buffer] = [
             Buffer(None, arena_bytes, _local=(self, r), timeout_ms=timeout_ms) for r in range(num_ranks)]
         ptrs = [b.runtime.get_local_base_ptr() for b in self.buffers]
@@ -595,7 +674,13 @@ class LocalWorld:
             if m:
                 msgs.append(f"rank {b.rank}: {m}")
         if msgs:
+            if all("capacity overflow" in m for m in msgs):
+                raise StreamEPOverflow("; ".join(msgs))
             raise StreamEPTimeout("; ".join(msgs))
+
+    def enable_capacity_mode(self, *args, **kwargs):
+        for b in self.buffers:
+            b.enable_capacity_mode(*args, **kwargs)
 
     # convenience wrappers used by the tests ------------------------------------------------------
     def dispatch(self, xs, topk_idxs, topk_weights, num_experts, tile_m=128, seqs=None):

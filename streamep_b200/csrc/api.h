@@ -35,6 +35,7 @@ struct ControlLayout {
   size_t mailbox;            // uint64[kNumKinds][2][kMaxRanks][kMailboxWords] parity-double-buffered records
   size_t inbox_counts;       // int[2][kMaxRanks][C][E_cap]                  per (src, channel, expert) pair counts
   size_t inbox_tokens;       // int[2][kMaxRanks][C][kMaxRanks]              per (src, channel, dst) token counts
+  size_t inbox_misc;         // int[2][kMaxRanks][4]                          per src: region id of a capacity-mode dispatch (-1 = exact mode)
   size_t total_bytes;
 };
 ControlLayout make_control_layout(int num_ranks, int num_channels, int num_experts_cap);
@@ -56,6 +57,14 @@ struct HostCounters {
   volatile int num_recv_tokens;
   volatile int reserved;
   volatile int recv_per_expert[kMaxExperts];
+};
+
+// Capacity mode: written by the metadata kernel when a layout does not fit; read by the host whenever it likes.
+struct HostOverflow {
+  volatile int count;          // number of dispatches that overflowed since the buffer was created
+  volatile int epoch;          // metadata epoch of the most recent one
+  volatile int needed_tiles;   // largest per-rank tile count of that dispatch
+  volatile int needed_recv;    // largest per-rank recv-token count of that dispatch
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -97,6 +106,16 @@ struct MetadataParams {
   HostCounters* host;            // mapped pinned memory (device pointer)
   StatusBlock* status;
   unsigned long long wait_budget_ns;
+  // Capacity mode (no host read of the sizes): the receive buffers are fixed regions of `tiles_cap` tiles and
+  // `recv_cap` recv tokens, the same on every rank.  The kernel checks every rank's layout against the capacity
+  // and every rank's region id against its own; on a violation every rank (they all see the same counts) turns
+  // the dispatch into an empty one and records kStatusOverflow / kStatusRegionMismatch.
+  int region_id;                 // -1: exact mode
+  int tiles_cap, recv_cap;
+  int* dev_sizes;                // [4] device: total_tiles, num_recv_tokens, overflow flag, reserved (capacity mode)
+  int* tile_id_to_expert;        // [tiles_cap] filled by the materialise launch in capacity mode
+  int* pool_arrival_target;      // [tiles_cap]
+  HostOverflow* host_overflow;   // mapped pinned memory: where the host learns of an overflow without a sync
 };
 void launch_dispatch_metadata(const MetadataParams& p, cudaStream_t stream);
 
@@ -135,6 +154,7 @@ struct PushParams {
   int kind;                      // kKindDispatch or kKindDispatchGrads
   int epoch;
   int flags;                     // bit0 publish own record, bit1 push, bit2 tail wait for own tiles
+  int static_targets;            // 1: every rank's buffers sit at the offsets of `own` (capacity mode): no records
   int pairs_per_chunk;           // pairs one warp ships between two counter releases (<= 32)
   int active_push_warps;         // push warps per CTA of the fused kernels that take chunks (0 = all)
   void* peer_base[kMaxRanks];
@@ -206,8 +226,12 @@ void launch_pool_expand(const void* recv, void* pool, const int* pool_recv_token
 // out[t, :] += sum over the pairs (t, k) owned by OTHER ranks of rows[t * K + k, :], accumulated in fp32.
 // Second half of the fused combine: expert ranks store one bf16 row per remote (token, k) pair into the
 // source rank's `rows`; pairs owned by the source rank itself were already reduced into `out`.
+// Optionally also copies the per-pair scalars peers stored into `dw_src` [T, K] to `dw_dst` (0 for skipped pairs),
+// so that a persistent landing area never has to be zeroed.  `skip_rows` (optional, device): when it reads non-zero
+// the landed rows are stale (a capacity-mode dispatch that ran empty) and `out` is left untouched.
 void launch_combine_reduce(void* out, const void* rows, const long long* topk_idx, int num_tokens, int hidden,
-                           int num_topk, int num_experts, int num_ranks, int rank, cudaStream_t stream);
+                           int num_topk, int num_experts, int num_ranks, int rank, cudaStream_t stream,
+                           const float* dw_src = nullptr, float* dw_dst = nullptr, const int* skip_rows = nullptr);
 
 struct RouterParams {
   const void* x;        // [T, H] bf16
@@ -241,6 +265,8 @@ struct TailSignal {              // end-of-kernel "all my remote writes are done
 // word `field` of the record that rank published for (`kind`, `epoch`).
 struct RemoteRef {
   int enabled, kind, epoch, field;
+  int is_static;                 // 1: the buffer sits at `offset` of every rank's arena (capacity mode), no record
+  unsigned long long offset;
 };
 
 struct GemmParams {
@@ -252,6 +278,8 @@ struct GemmParams {
   int M_out;                     // output rows per expert (VarlenK)
   int num_experts;               // local experts
   int num_m_tiles, num_n_tiles;
+  const int* num_m_tiles_dev;    // VarlenM, optional: the live tile count in device memory (<= num_m_tiles, which is
+                                 // then the capacity the tensor maps were built for)
   int total_rows;                // rows of A / outputs (TK_padded)
   const int* tile_id_to_expert;          // [tiles]            (VarlenM)
   const int* expert_pool_block_offset;   // [E + 1] tile units (VarlenK)

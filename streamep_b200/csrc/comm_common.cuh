@@ -24,6 +24,10 @@ __device__ __forceinline__ int* ctl_inbox_tokens(void* base, const ControlLayout
          ((static_cast<size_t>(parity) * kMaxRanks + src) * ctl.num_channels + c) * kMaxRanks;
 }
 
+__device__ __forceinline__ int* ctl_inbox_misc(void* base, const ControlLayout& ctl, int parity, int src) {
+  return reinterpret_cast<int*>(static_cast<char*>(base) + ctl.inbox_misc) + (static_cast<size_t>(parity) * kMaxRanks + src) * 4;
+}
+
 // Thread `p` (< num_ranks) of the calling group writes this rank's record into peer p's mailbox.
 // The 15 payload words are plain stores; the stamp is a system-scope release store.
 __device__ __forceinline__ void publish_record(const BufferRecord& rec, void* const* peer_base,

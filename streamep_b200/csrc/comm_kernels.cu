@@ -39,6 +39,7 @@ ControlLayout make_control_layout(int num_ranks, int num_channels, int num_exper
   c.mailbox = take(sizeof(unsigned long long) * kNumKinds * 2 * kMaxRanks * kMailboxWords);
   c.inbox_counts = take(sizeof(int) * 2 * kMaxRanks * num_channels * num_experts_cap);
   c.inbox_tokens = take(sizeof(int) * 2 * kMaxRanks * num_channels * kMaxRanks);
+  c.inbox_misc = take(sizeof(int) * 2 * kMaxRanks * 4);
   c.total_bytes = off;
   return c;
 }
@@ -67,6 +68,7 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
   __shared__ int s_total_tiles[kMaxRanks];
   __shared__ int s_is_last;
   __shared__ int s_ok;
+  __shared__ int s_bad;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int R = p.num_ranks, K = p.num_topk, E = p.num_experts, C = p.num_channels;
@@ -82,6 +84,24 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
     // never written, so there is nothing valid to materialise.
     const int num_send = *reinterpret_cast<const volatile int*>(p.num_send);
     if (num_send < 0) return;
+    if (p.region_id >= 0) {
+      // Capacity mode: the tile arrays cover the whole region; tiles past the live count get target 0.
+      const int live = p.dev_sizes[0];
+      for (size_t t = gid; t < static_cast<size_t>(p.tiles_cap); t += gsz) {
+        int e = 0, target = 0;
+        if (static_cast<int>(t) < live) {
+          while (e + 1 < EL && p.expert_pool_block_offset[e + 1] <= static_cast<int>(t)) ++e;
+          target = min(p.tile_m, p.expert_frequency[e] - (static_cast<int>(t) - p.expert_pool_block_offset[e]) * p.tile_m);
+        }
+        p.tile_id_to_expert[t] = e;
+        p.pool_arrival_target[t] = target;
+      }
+      if (p.dev_sizes[2] != 0) {   // the dispatch was turned into an empty one: nothing is sent anywhere
+        for (size_t i = gid; i < static_cast<size_t>(T) * K; i += gsz) p.pair_slot[i] = -1;
+        for (size_t i = gid; i < static_cast<size_t>(T) * R; i += gsz) p.send_recv_token[i] = -1;
+        return;
+      }
+    }
     for (size_t i = gid; i < static_cast<size_t>(T) * K; i += gsz) {
       const int t = static_cast<int>(i / K);
       const long long e = p.topk_idx[i];
@@ -164,6 +184,7 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
       const int peer = tid / kMaxRanks, d = tid % kMaxRanks;
       ctl_inbox_tokens(p.peer_base[peer], p.ctl, parity, p.rank, c)[d] = (d < R) ? s_u[d] : 0;
     }
+    if (c == 0 && tid < R) ctl_inbox_misc(p.peer_base[tid], p.ctl, parity, p.rank)[0] = p.region_id;
     __threadfence_system();
     __syncthreads();
     if (tid == 0) {
@@ -181,7 +202,7 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
   }
 
   // ------------------------------------------------------------------ phase B (one block)
-  if (tid == 0) s_ok = 1;
+  if (tid == 0) { s_ok = 1; s_bad = 0; }
   __syncthreads();
   if (tid < R) {
     if (!flags_wait(own, p.ctl, kKindMetadata, p.epoch, tid, p.wait_budget_ns, p.status, kKernelMetadata,
@@ -234,6 +255,41 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
     p.peer_num_recv[tid] = recv;
   }
   __syncthreads();
+  // 2b. every rank took the same region, and (capacity mode) every rank's layout fits it.  All ranks evaluate the
+  //     same numbers, so they all reach the same verdict and all turn a bad dispatch into an empty one.
+  if (tid < R) {
+    int bad = 0;
+    if (ctl_inbox_misc(own, p.ctl, parity, tid)[0] != p.region_id) bad |= 2;
+    if (p.region_id >= 0 && (s_total_tiles[tid] > p.tiles_cap || p.peer_num_recv[tid] > p.recv_cap)) bad |= 1;
+    if (bad) atomicOr(&s_bad, bad);
+  }
+  __syncthreads();
+  if (s_bad) {
+    if (tid == 0) {
+      int need_tiles = 0, need_recv = 0;
+      for (int r = 0; r < R; ++r) { need_tiles = max(need_tiles, s_total_tiles[r]); need_recv = max(need_recv, p.peer_num_recv[r]); }
+      report_note(p.status, (s_bad & 2) ? kStatusRegionMismatch : kStatusOverflow, kKernelMetadata, 1, p.rank,
+                  p.region_id, (s_bad & 2) ? p.region_id : p.tiles_cap, need_tiles);
+      *p.num_send = 0;
+      if (p.dev_sizes != nullptr) { p.dev_sizes[0] = 0; p.dev_sizes[1] = 0; p.dev_sizes[2] = 1; }
+      if (p.host_overflow != nullptr) {
+        p.host_overflow->needed_tiles = need_tiles;
+        p.host_overflow->needed_recv = need_recv;
+        p.host_overflow->epoch = p.epoch;
+        __threadfence_system();
+        p.host_overflow->count = p.host_overflow->count + 1;
+      }
+      p.expert_pool_block_offset[EL] = 0;
+      // an exact-mode host is polling for the sizes: hand it the error marker
+      p.host->total_tiles = (p.region_id >= 0) ? 0 : -1;
+      p.host->num_recv_tokens = (p.region_id >= 0) ? 0 : -1;
+      __threadfence_system();
+      p.host->epoch = p.epoch;
+    }
+    if (tid < EL) { p.expert_frequency[tid] = 0; p.expert_pool_block_offset[tid] = 0; }
+    if (tid < R) { p.peer_total_tiles[tid] = 0; p.peer_num_recv[tid] = 0; }
+    return;
+  }
   // 3. host-visible sizes first, so the host poll overlaps the rest of this kernel
   if (tid < EL) {
     p.host->recv_per_expert[tid] = s_hist[p.rank * EL + tid];
@@ -246,6 +302,7 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
     for (int s = 0; s < R; ++s) recv += s_U[s][p.rank];
     p.host->total_tiles = s_total_tiles[p.rank];
     p.host->num_recv_tokens = recv;
+    if (p.dev_sizes != nullptr) { p.dev_sizes[0] = s_total_tiles[p.rank]; p.dev_sizes[1] = recv; p.dev_sizes[2] = 0; }
   }
   __syncthreads();
   if (tid == 0) {
@@ -406,11 +463,13 @@ __global__ void fill_tile_metadata_kernel(const FillParams p) {
   const int gid = blockIdx.x * blockDim.x + threadIdx.x;
   const int stride = gridDim.x * blockDim.x;
   for (int t = gid; t < p.total_tiles; t += stride) {
-    int e = 0;
-    while (e + 1 < p.num_local_experts && p.expert_pool_block_offset[e + 1] <= t) ++e;
-    const int j = t - p.expert_pool_block_offset[e];
-    p.tile_id_to_expert[t] = e;
-    p.pool_arrival_target[t] = min(p.tile_m, p.expert_frequency[e] - j * p.tile_m);
+    if (p.tile_id_to_expert != nullptr) {   // (capacity mode fills the tile arrays in the metadata kernel)
+      int e = 0;
+      while (e + 1 < p.num_local_experts && p.expert_pool_block_offset[e + 1] <= t) ++e;
+      const int j = t - p.expert_pool_block_offset[e];
+      p.tile_id_to_expert[t] = e;
+      p.pool_arrival_target[t] = min(p.tile_m, p.expert_frequency[e] - j * p.tile_m);
+    }
     p.pool_arrival_count[t] = 0;
   }
   for (int i = gid; i < p.tk_padded; i += stride) {
@@ -448,15 +507,17 @@ __global__ void __launch_bounds__(kPushThreads, 1) dispatch_push_kernel(const Pu
   void* own = p.peer_base[p.rank];
 
   if (blockIdx.x == 0 && tid == 0 && p.started_flag != nullptr) atomicAdd(p.started_flag, 1);
-  if ((p.flags & 1) && blockIdx.x == 0 && tid < R)
+  if ((p.flags & 1) && !p.static_targets && blockIdx.x == 0 && tid < R)
     publish_record(p.own, p.peer_base, p.ctl, p.kind, p.epoch, p.rank, tid);
   if (tid == 0) s_ok = 1;
   __syncthreads();
 
   if (p.flags & 2) {
     if (tid < R) {
-      const unsigned long long* rec = fetch_record(own, p.ctl, p.kind, p.epoch, tid, p.wait_budget_ns, p.status,
-                                                   p.is_grads ? kKernelDispatchGrads : kKernelDispatch, p.rank);
+      const unsigned long long* rec = p.static_targets
+          ? reinterpret_cast<const unsigned long long*>(&p.own)
+          : fetch_record(own, p.ctl, p.kind, p.epoch, tid, p.wait_budget_ns, p.status,
+                         p.is_grads ? kKernelDispatchGrads : kKernelDispatch, p.rank);
       if (rec == nullptr) s_ok = 0;
       else resolve_push_targets(s_tg, tid, p.peer_base[tid], rec);
     }
@@ -696,18 +757,24 @@ void launch_pool_expand(const void* recv, void* pool, const int* pool_recv_token
 // Second half of the fused combine: fp32 reduction of the rows that remote expert ranks stored
 // =============================================================================================
 __global__ void combine_reduce_kernel(char* out, const char* rows, const long long* topk_idx, int num_tokens,
-                                      int hidden, int K, int e_local, int rank) {
+                                      int hidden, int K, int e_local, int rank, const float* dw_src, float* dw_dst,
+                                      const int* skip_rows) {
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const size_t row_bytes = static_cast<size_t>(hidden) * 2;
   const int vecs = hidden / 8;
+  const bool skip = skip_rows != nullptr && *skip_rows != 0;   // the dispatch ran empty: what landed earlier is stale
   for (int t = blockIdx.x * warps_per_block + warp; t < num_tokens; t += gridDim.x * warps_per_block) {
     unsigned remote = 0;
     for (int k = 0; k < K; ++k) {
       const long long e = topk_idx[static_cast<size_t>(t) * K + k];
       if (e >= 0 && static_cast<int>(e / e_local) != rank) remote |= 1u << k;
     }
-    if (remote == 0) continue;
+    if (dw_dst != nullptr && lane < K) {   // per-pair scalars the expert ranks stored for this token; 0 for skipped pairs
+      const size_t i = static_cast<size_t>(t) * K + lane;
+      dw_dst[i] = (topk_idx[i] >= 0 && !skip) ? dw_src[i] : 0.f;
+    }
+    if (remote == 0 || rows == nullptr || skip) continue;
     for (int v = lane; v < vecs; v += 32) {
       char* o = out + static_cast<size_t>(t) * row_bytes + static_cast<size_t>(v) * 16;
       const uint4 q0 = *reinterpret_cast<const uint4*>(o);
@@ -728,11 +795,13 @@ __global__ void combine_reduce_kernel(char* out, const char* rows, const long lo
   }
 }
 void launch_combine_reduce(void* out, const void* rows, const long long* topk_idx, int num_tokens, int hidden,
-                           int num_topk, int num_experts, int num_ranks, int rank, cudaStream_t stream) {
-  if (num_tokens == 0 || num_ranks == 1) return;
+                           int num_topk, int num_experts, int num_ranks, int rank, cudaStream_t stream,
+                           const float* dw_src, float* dw_dst, const int* skip_rows) {
+  if (num_tokens == 0 || (num_ranks == 1 && dw_dst == nullptr)) return;
   const int grid = min((num_tokens + 7) / 8, sm_count() * 8);
-  combine_reduce_kernel<<<grid, 256, 0, stream>>>(static_cast<char*>(out), static_cast<const char*>(rows), topk_idx,
-                                                  num_tokens, hidden, num_topk, num_experts / num_ranks, rank);
+  combine_reduce_kernel<<<grid, 256, 0, stream>>>(static_cast<char*>(out), num_ranks == 1 ? nullptr : static_cast<const char*>(rows),
+                                                  topk_idx, num_tokens, hidden, num_topk, num_experts / num_ranks, rank,
+                                                  dw_src, dw_dst, skip_rows);
 }
 
 // =============================================================================================

@@ -72,10 +72,11 @@ __device__ __forceinline__ void band_decode(int lin, int num_m, int num_n, int& 
   m_tile = m0 + (rem - n_tile * gm);
 }
 
-__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int lin) {
+// `num_m`: live number of M tiles (VarlenM; may come from device memory), ignored for VarlenK.
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int lin, int num_m) {
   TileCoord t;
   if (p.mode == kVarlenM) {
-    band_decode(lin, p.num_m_tiles, p.num_n_tiles, t.m_tile, t.n_tile);
+    band_decode(lin, num_m, p.num_n_tiles, t.m_tile, t.n_tile);
     t.expert = p.tile_id_to_expert[t.m_tile];
     t.row0 = t.m_tile * BM;
     t.k_blocks = (p.K + BK - 1) / BK;
@@ -137,7 +138,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   __shared__ float* s_remote_dw[kMaxRanks];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_tiles = (p.mode == kVarlenM ? p.num_m_tiles : p.num_experts * p.num_m_tiles) * p.num_n_tiles;
+  // Capacity mode keeps the live tile count in device memory (written by the metadata kernel earlier in the stream).
+  const int num_m = (p.mode == kVarlenM && p.num_m_tiles_dev != nullptr) ? min(*p.num_m_tiles_dev, p.num_m_tiles) : p.num_m_tiles;
+  const int total_tiles = (p.mode == kVarlenM ? num_m : p.num_experts * p.num_m_tiles) * p.num_n_tiles;
   const unsigned long long budget = p.wait_budget_ns;
 
   if (threadIdx.x == 0) {
@@ -154,20 +157,28 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tmem_relinquish();
   }
   if (PUSH) {
-    if ((pp.flags & 1) && blockIdx.x == 0 && warp == kGemmWarps && lane < pp.num_ranks)
+    if ((pp.flags & 1) && !pp.static_targets && blockIdx.x == 0 && warp == kGemmWarps && lane < pp.num_ranks)
       publish_record(pp.own, pp.peer_base, pp.ctl, pp.kind, pp.epoch, pp.rank, lane);
   }
   if ((EPI == kEpiScatter || EPI == kEpiDswiglu) && warp == 2 && lane < p.num_ranks) {
     // Resolve buffers that every rank allocated at its own arena offset from the published records.
     if (p.remote_out.enabled) {
-      const unsigned long long* rec = fetch_record(p.peer_base[p.rank], p.ctl, p.remote_out.kind, p.remote_out.epoch,
-                                                   lane, budget, p.status, kKernelGemm, p.rank);
-      s_remote_out[lane] = rec ? static_cast<char*>(p.peer_base[lane]) + rec[p.remote_out.field] : nullptr;
+      if (p.remote_out.is_static) {
+        s_remote_out[lane] = static_cast<char*>(p.peer_base[lane]) + p.remote_out.offset;
+      } else {
+        const unsigned long long* rec = fetch_record(p.peer_base[p.rank], p.ctl, p.remote_out.kind, p.remote_out.epoch,
+                                                     lane, budget, p.status, kKernelGemm, p.rank);
+        s_remote_out[lane] = rec ? static_cast<char*>(p.peer_base[lane]) + rec[p.remote_out.field] : nullptr;
+      }
     }
     if (p.remote_dw.enabled) {
-      const unsigned long long* rec = fetch_record(p.peer_base[p.rank], p.ctl, p.remote_dw.kind, p.remote_dw.epoch,
-                                                   lane, budget, p.status, kKernelGemm, p.rank);
-      s_remote_dw[lane] = rec ? reinterpret_cast<float*>(static_cast<char*>(p.peer_base[lane]) + rec[p.remote_dw.field]) : nullptr;
+      if (p.remote_dw.is_static) {
+        s_remote_dw[lane] = reinterpret_cast<float*>(static_cast<char*>(p.peer_base[lane]) + p.remote_dw.offset);
+      } else {
+        const unsigned long long* rec = fetch_record(p.peer_base[p.rank], p.ctl, p.remote_dw.kind, p.remote_dw.epoch,
+                                                     lane, budget, p.status, kKernelGemm, p.rank);
+        s_remote_dw[lane] = rec ? reinterpret_cast<float*>(static_cast<char*>(p.peer_base[lane]) + rec[p.remote_dw.field]) : nullptr;
+      }
     }
   }
   tc_fence_before_sync();
@@ -180,7 +191,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; int issued = 0; bool ok = true;
       for (int lin = blockIdx.x; lin < total_tiles && ok; lin += gridDim.x) {
-        const TileCoord t = decode_tile(p, lin);
+        const TileCoord t = decode_tile(p, lin, num_m);
         if (p.mode == kVarlenM && p.arrival_count != nullptr) {
           const int target = p.arrival_target[t.m_tile];
           const int* cnt = p.arrival_count + t.m_tile;
@@ -237,7 +248,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
     int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
     for (int lin = blockIdx.x; lin < total_tiles && ok; lin += gridDim.x) {
-      const TileCoord t = decode_tile(p, lin);
+      const TileCoord t = decode_tile(p, lin, num_m);
       if (t.k_blocks == 0) continue;   // empty expert: the epilogue writes zeros on its own
       // all 32 lanes wait; the outcome is made warp-uniform so that no lane leaves ahead of elect_one / __syncwarp
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_empty[acc], acc_phase ^ 1, budget, p.status))) { ok = false; break; }
@@ -293,7 +304,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint32_t stg = smem_u32(epi_stage + (warp - 2) * Cfg::kEpiStageBytes);
     int acc = 0; uint32_t acc_phase = 0;
     for (int lin = blockIdx.x; lin < total_tiles; lin += gridDim.x) {
-      const TileCoord t = decode_tile(p, lin);
+      const TileCoord t = decode_tile(p, lin, num_m);
       const bool empty = (t.k_blocks == 0);
       // Everything that does not need the accumulator is fetched while the tensor cores still work on this tile.
       const int n0 = t.n_tile * BN;
@@ -592,8 +603,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     if (pp.flags & 2) {
       const int pw = warp - kGemmWarps;
       if (pw == 0 && lane < pp.num_ranks) {
-        const unsigned long long* rec = fetch_record(pp.peer_base[pp.rank], pp.ctl, pp.kind, pp.epoch, lane,
-                                                     pp.wait_budget_ns, pp.status, kKernelDispatch, pp.rank);
+        const unsigned long long* rec = pp.static_targets
+            ? reinterpret_cast<const unsigned long long*>(&pp.own)
+            : fetch_record(pp.peer_base[pp.rank], pp.ctl, pp.kind, pp.epoch, lane,
+                           pp.wait_budget_ns, pp.status, kKernelDispatch, pp.rank);
         if (rec == nullptr) s_push_ok = 0;
         else resolve_push_targets(s_tg, lane, pp.peer_base[lane], rec);
       }

@@ -25,6 +25,18 @@ __device__ __forceinline__ void report_failure(StatusBlock* st, int code, int ke
   atomicExch(&st->abort, 1);
 }
 
+// Records a condition the host must hear about WITHOUT raising the abort flag: the kernels that follow keep their
+// normal course (used where every rank takes the same, consistent fallback, e.g. a capacity overflow).
+__device__ __forceinline__ void report_note(StatusBlock* st, int code, int kernel_id, int role, int rank, int where,
+                                            int expected, int observed) {
+  if (st == nullptr) return;
+  if (atomicCAS(&st->code, 0, code) == 0) {
+    st->kernel_id = kernel_id; st->role = role; st->rank = rank; st->where = where;
+    st->expected = expected; st->observed = observed;
+    __threadfence();
+  }
+}
+
 __device__ __forceinline__ bool aborted(const StatusBlock* st) {
   return st != nullptr && *reinterpret_cast<const volatile int*>(&st->abort) != 0;
 }

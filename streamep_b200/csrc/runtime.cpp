@@ -240,6 +240,10 @@ struct DispatchState {
   std::optional<EventHandle> metadata_done_event;
   BufferRecord record{};
   std::vector<at::Tensor> aux_keepalive;
+  // capacity mode (no host read of the sizes): the receive buffers are a fixed region of the arena
+  int region_id = -1;                  // -1: exact mode
+  at::Tensor dev_sizes;                // int32 [4] device: live total_tiles, live num_recv_tokens, overflow flag
+  std::shared_ptr<void> region_guard;  // keeps the region claimed while this state (or a view of the region) lives
 
   void release_o() { o = at::Tensor(); }
   void release_pool() { pool = at::Tensor(); }
@@ -247,6 +251,9 @@ struct DispatchState {
 
 struct GradsState {
   at::Tensor dl_do_pool, bwd_dispatch_arrival_count, slab;
+  at::Tensor landing, dwt;             // fused backward: landing rows [T * K, H] and per-pair dL/dweight [T, K] peers write
+  int64_t landing_off = -1, dwt_off = -1;   // their arena offsets when they are fixed regions (capacity mode), else -1
+  bool is_static = false;
   int epoch = 0;
   BufferRecord record{};
   std::optional<EventHandle> started_event;
@@ -272,6 +279,9 @@ struct GemmArgs {
   // remote scatter / remote dL/dweight return: (record kind, epoch, word) naming the buffer on every rank
   std::vector<int> remote_out;
   std::vector<int> remote_dw;
+  // capacity mode: the buffer sits at this arena offset on every rank (no record look-up); -1 = use the record
+  int64_t remote_out_offset = -1, remote_dw_offset = -1;
+  std::optional<at::Tensor> num_m_tiles_dev;        // VarlenM: live tile count in device memory (capacity mode)
   int num_topk = 0;
   int64_t seq = 0;
   int num_m_tiles = -1;                             // VarlenM: total tiles (defaults to len(tile_id_to_expert))
@@ -282,6 +292,27 @@ struct GemmArgs {
   std::shared_ptr<DispatchState> fused_push_routing;
   at::Tensor fused_push_rows;
   int push_flags = 7;
+};
+
+// Fixed regions of the arena for the capacity mode of the fused layer.  Every rank builds the same plan with the
+// same arguments right after constructing its runtime, so every region sits at the same arena offset on every
+// rank and no buffer record has to be exchanged per dispatch.
+struct StaticPlan {
+  int num_regions = 0, hidden = 0, topk = 0;
+  int64_t tokens_cap = 0, rows_cap = 0, tiles_cap = 0, recv_cap = 0;
+  // byte offsets of the arrays inside one forward region
+  size_t o_pool = 0, o_w = 0, o_rt = 0, o_ks = 0, o_src = 0, o_r2s = 0, o_klt = 0, o_klr = 0, o_cnt = 0, o_rsrc = 0, o_done = 0;
+  size_t region_bytes = 0;
+  size_t base_off = 0;                    // arena offset of the whole block
+  std::vector<size_t> region_off;         // forward regions (one per layer whose forward state is alive)
+  size_t bwd_pool_off[2] = {0, 0}, bwd_cnt_off[2] = {0, 0};   // backward: gradient pool + its tile counters
+  size_t landing_off[2] = {0, 0};         // rows other ranks computed for this rank's tokens, [tokens_cap * topk, hidden]
+  size_t dwt_off[2] = {0, 0};             // per-pair dL/dweight other ranks return, [tokens_cap, topk] fp32
+  size_t total_bytes = 0;
+  at::Tensor block;                       // owns the arena block
+  std::mutex mu;
+  std::vector<char> busy;
+  uint64_t landing_calls = 0, bwd_calls = 0;
 };
 
 class Runtime {
@@ -340,6 +371,8 @@ class Runtime {
     arena_guard_.reset();
     if (scratch_ != nullptr) cudaFree(scratch_);
     if (host_ != nullptr) cudaFreeHost(host_);
+    if (host_overflow_ != nullptr) cudaFreeHost(host_overflow_);
+    host_overflow_ = nullptr; static_.reset();
     scratch_ = nullptr; host_ = nullptr;
   }
 
@@ -426,6 +459,78 @@ class Runtime {
     return static_cast<const char*>(t.data_ptr()) - static_cast<char*>(base_);
   }
 
+  // ---- capacity mode ---------------------------------------------------------------------------
+  // Carves the fixed regions out of the arena.  Collective by convention: every rank calls it with the same
+  // arguments at the same point of its allocation history; the returned arena offset must agree on all ranks
+  // (the Python layer checks that).  `num_regions` = layers whose forward state is alive at the same time.
+  int64_t enable_static(int num_regions, int64_t tokens_cap, int hidden, int topk, int64_t rows_cap, int64_t recv_cap) {
+    SEP_ASSERT(!static_, "capacity mode is already enabled on this buffer");
+    SEP_ASSERT(num_regions >= 1 && tokens_cap >= 1 && hidden % 8 == 0 && topk >= 1 && topk <= kMaxTopK, "bad capacity-mode arguments");
+    SEP_ASSERT(rows_cap >= kTileM && rows_cap % kTileM == 0 && recv_cap >= 1, "rows_cap must be a positive multiple of 128, recv_cap positive");
+    auto pl = std::make_shared<StaticPlan>();
+    pl->num_regions = num_regions; pl->hidden = hidden; pl->topk = topk;
+    pl->tokens_cap = tokens_cap; pl->rows_cap = rows_cap; pl->tiles_cap = rows_cap / kTileM; pl->recv_cap = recv_cap;
+    auto al = [](size_t b) { return (b + 1023) / 1024 * 1024; };
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off += al(bytes); return o; };
+    const size_t R = rows_cap, Tr = recv_cap, K = topk, H = hidden;
+    pl->o_pool = take(R * H * 2); pl->o_w = take(R * 4); pl->o_rt = take(R * 4); pl->o_ks = take(R * 4); pl->o_src = take(R * 8);
+    pl->o_r2s = take(Tr * K * 4); pl->o_klt = take(Tr * 4); pl->o_klr = take(Tr * 4); pl->o_cnt = take(pl->tiles_cap * 4);
+    pl->o_rsrc = take(Tr * 8); pl->o_done = take(Tr * 8);
+    pl->region_bytes = off;
+    off = 0;
+    for (int i = 0; i < num_regions; ++i) pl->region_off.push_back(take(pl->region_bytes));
+    for (int i = 0; i < 2; ++i) { pl->bwd_pool_off[i] = take(R * H * 2); pl->bwd_cnt_off[i] = take(pl->tiles_cap * 4); }
+    if (num_ranks_ > 1)
+      for (int i = 0; i < 2; ++i) pl->landing_off[i] = take(static_cast<size_t>(tokens_cap) * K * H * 2);
+    for (int i = 0; i < 2; ++i) pl->dwt_off[i] = take(static_cast<size_t>(tokens_cap) * K * 4);
+    pl->total_bytes = off;
+    size_t base = 0;
+    pl->block = alloc_symmetric({static_cast<int64_t>(pl->total_bytes)}, at::kByte, false, &base);
+    pl->base_off = base;
+    for (auto& o : pl->region_off) o += base;
+    for (int i = 0; i < 2; ++i) { pl->bwd_pool_off[i] += base; pl->bwd_cnt_off[i] += base; pl->landing_off[i] += base; pl->dwt_off[i] += base; }
+    pl->busy.assign(num_regions, 0);
+    // backward tile counters start at zero; later uses are re-zeroed at the end of the backward that used them
+    for (int i = 0; i < 2; ++i)
+      SEP_CUDA_CHECK(cudaMemsetAsync(static_cast<char*>(base_) + pl->bwd_cnt_off[i], 0, pl->tiles_cap * 4, stream()));
+    SEP_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&host_overflow_), sizeof(HostOverflow), cudaHostAllocMapped));
+    std::memset(reinterpret_cast<void*>(host_overflow_), 0, sizeof(HostOverflow));
+    SEP_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&host_overflow_dev_), host_overflow_, 0));
+    SEP_CUDA_CHECK(cudaStreamSynchronize(stream()));
+    static_ = pl;
+    return static_cast<int64_t>(base);
+  }
+  bool static_enabled() const { return static_ != nullptr; }
+  // True when a dispatch of this shape can use the fixed regions.
+  bool static_fits(int64_t tokens, int hidden, int topk) const {
+    return static_ && tokens <= static_->tokens_cap && hidden == static_->hidden && topk == static_->topk;
+  }
+  std::vector<int64_t> static_capacity() const {
+    if (!static_) return {};
+    return {static_->num_regions, static_->tokens_cap, static_->rows_cap, static_->recv_cap, static_cast<int64_t>(static_->total_bytes)};
+  }
+  // {count of overflowed dispatches, epoch of the last one, tiles it needed, recv tokens it needed}; no device sync.
+  std::vector<int64_t> overflow_info() const {
+    if (host_overflow_ == nullptr) return {0, 0, 0, 0};
+    return {host_overflow_->count, host_overflow_->epoch, host_overflow_->needed_tiles, host_overflow_->needed_recv};
+  }
+  // A non-owning tensor over a fixed region; `guard` (may be null) rides along in its deleter.
+  at::Tensor region_view(size_t off, const std::vector<int64_t>& sizes, at::ScalarType dtype, std::shared_ptr<void> guard) {
+    at::Tensor keep = static_->block;
+    return at::from_blob(static_cast<char*>(base_) + off, sizes, [keep, guard](void*) {},
+                         at::TensorOptions().dtype(dtype).device(at::kCUDA, device_));
+  }
+  // The landing buffer of the next fused GEMM (+) combine on this rank: two alternate.  A buffer is written by
+  // peers during call c and read here right after; its next writers (call c + 2) have by then passed the
+  // all-rank completion handshake of call c + 1, which this rank only joins after its read of call c.
+  std::pair<at::Tensor, int64_t> next_landing(int64_t tokens, int hidden, int topk) {
+    SEP_ASSERT(static_fits(tokens, hidden, topk), "shape does not fit the capacity-mode regions");
+    if (num_ranks_ == 1) return {at::empty({0, hidden}, at::TensorOptions().dtype(at::kBFloat16).device(at::kCUDA, device_)), 0};
+    const size_t off = static_->landing_off[static_->landing_calls++ & 1];
+    return {region_view(off, {tokens * topk, static_cast<int64_t>(hidden)}, at::kBFloat16, nullptr), static_cast<int64_t>(off)};
+  }
+
   // ---- status --------------------------------------------------------------------------------
   // Reads the device status block (synchronises the device). Returns an empty string when clean.
   std::string poll_status(bool reset) {
@@ -435,9 +540,11 @@ class Runtime {
     if (h.code == 0 && h.abort == 0) return "";
     if (reset) SEP_CUDA_CHECK(cudaMemset(status_, 0, sizeof(StatusBlock)));
     static const char* names[] = {"ok", "barrier timeout", "buffer-record timeout", "tile gate timeout",
-                                  "token gate timeout", "GEMM pipeline timeout", "tail wait timeout", "bad index"};
+                                  "token gate timeout", "GEMM pipeline timeout", "tail wait timeout", "bad index",
+                                  "capacity overflow (where = region, expected = tile capacity, observed = tiles needed; the dispatch was run as an empty one)",
+                                  "ranks disagree on the capacity-mode region of a dispatch"};
     std::ostringstream os;
-    os << names[(h.code >= 0 && h.code < 8) ? h.code : 0] << " (code " << h.code << ") in kernel " << h.kernel_id
+    os << names[(h.code >= 0 && h.code < 10) ? h.code : 0] << " (code " << h.code << ") in kernel " << h.kernel_id
        << " role " << h.role << " on rank " << h.rank << ": where=" << h.where << " expected=" << h.expected
        << " observed=" << h.observed;
     return os.str();
@@ -458,9 +565,10 @@ class Runtime {
   }
 
   // ---- dispatch: phase 0, inputs + sender-side scratch ----------------------------------------
+  // `capacity_mode`: receive into a fixed region (enable_static) instead of exactly sized fresh buffers.
   std::shared_ptr<DispatchState> dispatch_begin(const at::Tensor& x, const at::Tensor& topk_idx,
                                                 const at::Tensor& topk_weights, int num_experts, int tile_m,
-                                                int64_t seq) {
+                                                int64_t seq, bool capacity_mode = false) {
     SEP_ASSERT(available_, "Buffer.sync has not completed");
     SEP_ASSERT(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "x must be a contiguous [T, H] bf16 CUDA tensor");
     SEP_ASSERT(topk_idx.dim() == 2 && topk_idx.is_contiguous() && topk_idx.scalar_type() == at::kLong, "topk_idx must be contiguous [T, K] int64");
@@ -477,8 +585,10 @@ class Runtime {
     st->meta_epoch = ++epochs_[kKindMetadata];
     const int64_t T = st->num_tokens, K = st->num_topk, R = num_ranks_, C = num_channels_, E = num_experts, EL = E / R;
     // One int32 slab for all small tensors (each torch::empty costs microseconds on the host).
+    const int64_t tiles_cap = capacity_mode ? static_->tiles_cap : 0;
+    if (capacity_mode) SEP_ASSERT(static_fits(T, st->hidden, st->num_topk), "this dispatch does not fit the capacity-mode regions (tokens, hidden or top-k differ)");
     const int64_t n_i32 = T * K * 3 + T * R * 3 + (T * R + 3) / 4 + R * C + 2 * C * E + C * R + 2 * R + EL + (EL + 1) +
-                          2 * C * R * EL + R * R + R * C + 96;
+                          2 * C * R * EL + R * R + R * C + 2 * tiles_cap + 104;
     st->sender_slab = at::empty({n_i32}, x.options().dtype(at::kInt));
     int64_t off = 0;
     auto take = [&](std::vector<int64_t> shape) {
@@ -496,6 +606,20 @@ class Runtime {
     st->expert_frequency = take({EL}); st->expert_pool_block_offset = take({EL + 1});
     st->base_pool = take({C, R, EL}); st->seen_per_substream = take({C, R, EL});
     st->rank_prefix_matrix = take({R, R}); st->recv_channel_prefix_matrix = take({R, C});
+    if (capacity_mode) {
+      st->tile_id_to_expert = take({tiles_cap}); st->pool_arrival_target = take({tiles_cap});
+      st->dev_sizes = take({4});
+      // claim the lowest free region: ranks that run the same program pick the same one (the metadata kernel checks)
+      std::shared_ptr<StaticPlan> pl = static_;
+      int id = -1;
+      {
+        std::lock_guard<std::mutex> g(pl->mu);
+        for (int i = 0; i < pl->num_regions && id < 0; ++i) if (!pl->busy[i]) { pl->busy[i] = 1; id = i; }
+      }
+      SEP_ASSERT(id >= 0, "every capacity-mode region is in use: enable capacity mode with as many regions as layers keep forward state alive");
+      st->region_id = id;
+      st->region_guard = std::shared_ptr<void>(nullptr, [pl, id](void*) { std::lock_guard<std::mutex> g(pl->mu); pl->busy[id] = 0; });
+    }
     SEP_ASSERT(off <= n_i32, "sender slab overflow");
     return st;
   }
@@ -524,6 +648,28 @@ class Runtime {
     p.recv_channel_prefix_matrix = st->recv_channel_prefix_matrix.data_ptr<int>();
     p.blocks_done = counters_ + 0;
     p.host = host_dev_; p.status = status_; p.wait_budget_ns = budget_ns_;
+    p.region_id = st->region_id;
+    if (st->region_id >= 0) {
+      const StaticPlan& pl = *static_;
+      p.tiles_cap = static_cast<int>(pl.tiles_cap); p.recv_cap = static_cast<int>(pl.recv_cap);
+      p.dev_sizes = st->dev_sizes.data_ptr<int>();
+      p.tile_id_to_expert = st->tile_id_to_expert.data_ptr<int>(); p.pool_arrival_target = st->pool_arrival_target.data_ptr<int>();
+      p.host_overflow = host_overflow_dev_;
+      if (phase_mask & 1) {
+        // Defaults of everything peers write into this region, for the whole capacity (a few MB of small arrays),
+        // BEFORE this rank's count exchange: a peer pushes only after it has seen this rank's exchange flag.
+        char* rb = static_cast<char*>(base_) + pl.region_off[st->region_id];
+        FillParams f{};
+        f.total_tiles = p.tiles_cap; f.tile_m = st->tile_m; f.num_local_experts = st->num_experts / num_ranks_;
+        f.tk_padded = static_cast<int>(pl.rows_cap); f.num_recv_tokens = p.recv_cap; f.num_topk = st->num_topk;
+        f.pool_topk_weight = reinterpret_cast<float*>(rb + pl.o_w); f.pool_recv_token = reinterpret_cast<int*>(rb + pl.o_rt);
+        f.pool_k_slot = reinterpret_cast<int*>(rb + pl.o_ks); f.pool_src = reinterpret_cast<int2*>(rb + pl.o_src);
+        f.recv_token_to_slots = reinterpret_cast<int*>(rb + pl.o_r2s); f.k_local_total = reinterpret_cast<int*>(rb + pl.o_klt);
+        f.k_local_remaining = reinterpret_cast<int*>(rb + pl.o_klr); f.pool_arrival_count = reinterpret_cast<int*>(rb + pl.o_cnt);
+        f.recv_src = reinterpret_cast<int2*>(rb + pl.o_rsrc); f.y_done_per_token = reinterpret_cast<long long*>(rb + pl.o_done);
+        ++launches_; launch_fill_tile_metadata(f, stream());
+      }
+    }
     ++launches_; launch_dispatch_metadata(p, stream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
@@ -533,6 +679,7 @@ class Runtime {
   // and does not use it).  `defer_views`: create only the tensors the first GEMM launch needs; the caller
   // creates the rest with dispatch_finish_views() once that launch is queued, off the GPU's critical path.
   void dispatch_allocate(const std::shared_ptr<DispatchState>& st, bool need_o = true, bool defer_views = false) {
+    if (st->region_id >= 0) { dispatch_allocate_static(st, need_o); return; }
     // The metadata kernel writes the sizes to mapped pinned memory; the epoch word goes last.
     const auto t0 = std::chrono::steady_clock::now();
     bool timed_out = false;
@@ -608,6 +755,35 @@ class Runtime {
     st->metadata_done_event = EventHandle(stream());
   }
 
+  // Capacity mode: no host read.  The handle's tensors are views of the whole region (`total_tiles`, `TK_padded`
+  // and `num_recv_tokens` are the capacities); the live counts stay on the device in `dev_sizes`.
+  void dispatch_allocate_static(const std::shared_ptr<DispatchState>& st, bool need_o) {
+    const StaticPlan& pl = *static_;
+    const size_t ro = pl.region_off[st->region_id];
+    const int64_t R = pl.rows_cap, Tr = pl.recv_cap, K = st->num_topk, H = st->hidden, tiles = pl.tiles_cap;
+    st->total_tiles = static_cast<int>(tiles); st->num_recv_tokens = static_cast<int>(Tr);
+    st->recv_per_expert.clear();
+    auto g = st->region_guard;
+    st->pool = region_view(ro + pl.o_pool, {R, H}, at::kBFloat16, g);
+    st->pool_topk_weight = region_view(ro + pl.o_w, {R}, at::kFloat, g);
+    st->pool_recv_token = region_view(ro + pl.o_rt, {R}, at::kInt, g);
+    st->pool_k_slot = region_view(ro + pl.o_ks, {R}, at::kInt, g);
+    st->pool_src = region_view(ro + pl.o_src, {R, 2}, at::kInt, g);
+    st->recv_token_to_slots = region_view(ro + pl.o_r2s, {Tr, K}, at::kInt, g);
+    st->k_local_total = region_view(ro + pl.o_klt, {Tr}, at::kInt, g);
+    st->k_local_remaining = region_view(ro + pl.o_klr, {Tr}, at::kInt, g);
+    st->pool_arrival_count = region_view(ro + pl.o_cnt, {tiles}, at::kInt, g);
+    st->recv_src = region_view(ro + pl.o_rsrc, {Tr, 2}, at::kInt, g);
+    st->y_done_per_token = region_view(ro + pl.o_done, {Tr}, at::kLong, g);
+    st->o = need_o ? alloc_symmetric({Tr, H}, at::kBFloat16, true) : at::empty({0, H}, st->x.options());
+    BufferRecord& r = st->record;
+    r.pool = ro + pl.o_pool; r.pool_topk_weight = ro + pl.o_w; r.pool_recv_token = ro + pl.o_rt; r.pool_k_slot = ro + pl.o_ks;
+    r.pool_src = ro + pl.o_src; r.recv_token_to_slots = ro + pl.o_r2s; r.k_local_total = ro + pl.o_klt;
+    r.k_local_remaining = ro + pl.o_klr; r.arrival_count = ro + pl.o_cnt; r.recv_src = ro + pl.o_rsrc;
+    st->push_epoch = ++epochs_[kKindDispatch];
+    st->metadata_done_event = EventHandle(stream());
+  }
+
   // The i-th array of the per-dispatch slab (order: pool_topk_weight, pool_recv_token, pool_k_slot, pool_src,
   // recv_token_to_slots, k_local_total, k_local_remaining, pool_arrival_count, recv_src, y_done_per_token).
   at::Tensor slab_view(const DispatchState& st, int i) const {
@@ -652,6 +828,7 @@ class Runtime {
     p.is_grads = is_grads ? 1 : 0; p.kind = kind; p.epoch = epoch; p.flags = flags;
     p.pairs_per_chunk = pairs_per_chunk_; p.active_push_warps = active_push_warps_;
     fill_peers(p.peer_base); p.ctl = ctl_; p.own = rec;
+    p.static_targets = st.region_id >= 0 ? 1 : 0;   // (a backward along a capacity-mode forward uses fixed regions too)
     p.own_arrival_count = own_count; p.own_arrival_target = st.pool_arrival_target.data_ptr<int>();
     p.own_total_tiles = st.total_tiles;
     p.started_flag = gate_flags_ + (is_grads ? 1 : 0);
@@ -670,18 +847,51 @@ class Runtime {
   }
 
   // ---- dispatch_grads --------------------------------------------------------------------------
-  std::shared_ptr<GradsState> grads_begin(const std::shared_ptr<DispatchState>& st) {
+  // `fused_buffers`: also provide the landing rows and the per-pair dL/dweight matrix of the fused backward.
+  std::shared_ptr<GradsState> grads_begin(const std::shared_ptr<DispatchState>& st, bool fused_buffers = false) {
     auto g = std::make_shared<GradsState>();
-    const int64_t tiles = st->total_tiles, TKp = tiles * st->tile_m;
+    const int64_t tiles = st->total_tiles, TKp = tiles * st->tile_m, T = st->num_tokens, K = st->num_topk, H = st->hidden;
     size_t off_pool = 0, off_cnt = 0;
-    g->dl_do_pool = alloc_symmetric({TKp, static_cast<int64_t>(st->hidden)}, at::kBFloat16, false, &off_pool);
-    g->bwd_dispatch_arrival_count = alloc_symmetric({tiles}, at::kInt, true, &off_cnt);
+    if (st->region_id >= 0) {
+      // Capacity mode: two fixed gradient regions alternate.  A region used by backward call b is written again by
+      // peers in call b + 2, after they passed the completion handshake of call b + 1, which this rank joins only
+      // after everything of call b (dW GEMMs reading the gradient pool, the re-zeroing of the counters) is queued.
+      StaticPlan& pl = *static_;
+      const int par = static_cast<int>(pl.bwd_calls++ & 1);
+      g->is_static = true;
+      off_pool = pl.bwd_pool_off[par]; off_cnt = pl.bwd_cnt_off[par];
+      g->dl_do_pool = region_view(off_pool, {TKp, H}, at::kBFloat16, nullptr);
+      g->bwd_dispatch_arrival_count = region_view(off_cnt, {tiles}, at::kInt, nullptr);
+      if (fused_buffers) {
+        auto lo = next_landing(T, st->hidden, st->num_topk);
+        g->landing = lo.first; g->landing_off = lo.second;
+        g->dwt_off = static_cast<int64_t>(pl.dwt_off[par]);
+        g->dwt = region_view(pl.dwt_off[par], {T, K}, at::kFloat, nullptr);
+      }
+    } else {
+      g->dl_do_pool = alloc_symmetric({TKp, H}, at::kBFloat16, false, &off_pool);
+      g->bwd_dispatch_arrival_count = alloc_symmetric({tiles}, at::kInt, true, &off_cnt);
+      if (fused_buffers) {
+        g->landing = alloc_symmetric({num_ranks_ > 1 ? T * K : 0, H}, at::kBFloat16, false);
+        g->dwt = alloc_symmetric({T, K}, at::kFloat, true);
+      }
+    }
     g->record = BufferRecord{};
     g->record.pool = off_pool;
     g->record.arrival_count = off_cnt;
+    if (fused_buffers && !g->is_static) {
+      g->record.aux0 = g->landing.numel() ? symmetric_offset(g->landing) : 0;
+      g->record.aux1 = g->dwt.numel() ? symmetric_offset(g->dwt) : 0;
+    }
     g->epoch = ++epochs_[kKindDispatchGrads];
     g->started_event = EventHandle(stream());
     return g;
+  }
+  // Capacity mode, end of a backward: the gradient tile counters go back to zero for the call after next.  Queue it
+  // behind the kernel that ends with the all-rank completion handshake (A_bwd), i.e. after every rank's push.
+  void grads_finish(const std::shared_ptr<GradsState>& g) {
+    if (!g->is_static || g->bwd_dispatch_arrival_count.numel() == 0) return;
+    SEP_CUDA_CHECK(cudaMemsetAsync(g->bwd_dispatch_arrival_count.data_ptr(), 0, g->bwd_dispatch_arrival_count.nbytes(), stream()));
   }
   void grads_push(const std::shared_ptr<DispatchState>& st, const std::shared_ptr<GradsState>& g, const at::Tensor& dl_dy,
                   int flags, int num_blocks) {
@@ -784,6 +994,7 @@ class Runtime {
       SEP_ASSERT(static_cast<int64_t>(p.num_m_tiles) * BM_ <= rows || a.epilogue == kEpiStoreF32, "tile list longer than A");
       p.num_n_tiles = (N + BN - 1) / BN;
       p.tile_id_to_expert = a.tile_id_to_expert->data_ptr<int>();
+      if (a.num_m_tiles_dev.has_value()) p.num_m_tiles_dev = a.num_m_tiles_dev->data_ptr<int>();
       if (rows == 0) { launch_without_tiles(a); return; }
       ta = make_tmap(a.a.data_ptr(), K, rows, 1, K, rows * K, 64, BM_);
       if (a.b_mn_major) tb = make_tmap(a.b.data_ptr(), N, K, E, N, K * N, 64, 64);
@@ -831,6 +1042,8 @@ class Runtime {
     };
     set_ref(p.remote_out, a.remote_out);
     set_ref(p.remote_dw, a.remote_dw);
+    if (a.remote_out_offset >= 0) { p.remote_out.enabled = 1; p.remote_out.is_static = 1; p.remote_out.offset = a.remote_out_offset; }
+    if (a.remote_dw_offset >= 0) { p.remote_dw.enabled = 1; p.remote_dw.is_static = 1; p.remote_dw.offset = a.remote_dw_offset; }
     if (a.epilogue == kEpiScatter || a.epilogue == kEpiDswiglu) SEP_ASSERT(p.row_token != nullptr, "this epilogue needs pool_recv_token");
     if (a.epilogue == kEpiScatter) {
       SEP_ASSERT(a.scatter_local.has_value(), "scatter needs a local destination");   // may be empty (a rank without tokens)
@@ -925,13 +1138,21 @@ class Runtime {
   // (allocation, fill, three launches) instead of ~25 Python-level calls keeps the idle gap short.
   // Returns {out, postact, preact (may be undefined)}.
   std::vector<at::Tensor> fused_forward(const std::shared_ptr<DispatchState>& st, const at::Tensor& w1, const at::Tensor& w2,
-                                        const at::Tensor& landing, bool store_preact, int tile_n_a, int tile_n_y,
+                                        const at::Tensor& landing_in, bool store_preact, int tile_n_a, int tile_n_y,
                                         int num_sms_a, int num_sms_y) {
     // Queued behind the metadata kernel, so the output is zeroed while the host waits for the sizes.
     auto opts = st->x.options();
+    const bool cap = st->region_id >= 0;
     at::Tensor out = at::zeros({static_cast<int64_t>(st->num_tokens), w2.size(1)}, opts);
     dispatch_allocate(st, /*need_o=*/false, /*defer_views=*/true);
-    dispatch_set_aux(st, 0, landing);
+    at::Tensor landing = landing_in;
+    int64_t landing_off = -1;
+    if (cap) {          // fixed landing region, the same offset on every rank: no record word needed
+      auto lo = next_landing(st->num_tokens, st->hidden, st->num_topk);
+      landing = lo.first; landing_off = lo.second;
+    } else {
+      dispatch_set_aux(st, 0, landing);
+    }
     const int64_t TKp = static_cast<int64_t>(st->total_tiles) * st->tile_m, I = w2.size(2);
     at::Tensor postact = at::empty({TKp, I}, opts);
     at::Tensor preact = store_preact ? at::empty({TKp, 2 * I}, opts) : at::Tensor();
@@ -941,17 +1162,20 @@ class Runtime {
     a.out0 = postact; if (store_preact) a.out1 = preact;
     a.arrival_count = st->pool_arrival_count; a.arrival_target = st->pool_arrival_target;
     a.fused_push = st; a.push_flags = 3;
+    if (cap) a.num_m_tiles_dev = st->dev_sizes;
     grouped_gemm(a);
-    dispatch_finish_views(st);          // host work in the shadow of kernel A
+    if (!cap) dispatch_finish_views(st);          // host work in the shadow of kernel A
     GemmArgs y;
     y.mode = kVarlenM; y.epilogue = kEpiScatter; y.block_n = tile_n_y; y.num_ctas = num_sms_y;
     y.a = postact; y.b = w2; y.tile_id_to_expert = st->tile_id_to_expert;
     y.row_weight = st->pool_topk_weight; y.row_token = st->pool_recv_token; y.scatter_local = out;
-    y.remote_out = {kKindDispatch, st->push_epoch, 10};
+    if (cap) { y.remote_out_offset = landing_off; y.num_m_tiles_dev = st->dev_sizes; }
+    else y.remote_out = {kKindDispatch, st->push_epoch, 10};
     y.row_src = st->pool_src; y.row_k_slot = st->pool_k_slot; y.num_topk = st->num_topk;
     y.tail = true; y.tail_kind = kKindGemmYTail; y.tail_wait = true;
     grouped_gemm(y);
-    combine_reduce(out, landing, st->topk_idx, st->num_experts);
+    combine_reduce(out, landing, st->topk_idx, st->num_experts, std::nullopt, std::nullopt,
+                   cap ? std::optional<at::Tensor>(st->dev_sizes) : std::nullopt);
     return {out, postact, preact};
   }
 
@@ -965,6 +1189,7 @@ class Runtime {
                                          int num_sms_y_bwd, int num_sms_a_bwd) {
     const int64_t tiles = st->total_tiles, TKp = tiles * st->tile_m, T = st->num_tokens, K = st->num_topk;
     const int64_t H = w2.size(1), I = w2.size(2);
+    const bool cap = st->region_id >= 0;
     auto opts = st->x.options();
     at::Tensor dswiglu_in = at::empty({TKp, 2 * I}, opts), postact_dw2 = at::empty({TKp, I}, opts);
     at::Tensor dW1 = at::empty_like(w1), dW2 = at::empty_like(w2);
@@ -972,11 +1197,7 @@ class Runtime {
     at::Tensor zeros = at::zeros({nt + TKp}, opts.dtype(at::kInt));
     at::Tensor stripes = zeros.narrow(0, 0, nt), dl_dweight = zeros.narrow(0, nt, TKp).view(at::kFloat);
     at::Tensor dx = at::zeros({T, H}, opts);
-    at::Tensor landing = alloc_symmetric({num_ranks_ > 1 ? T * K : 0, H}, at::kBFloat16, false);
-    at::Tensor dwt = alloc_symmetric({T, K}, at::kFloat, true);
-    auto g = grads_begin(st);
-    grads_set_aux(g, 0, landing);
-    grads_set_aux(g, 1, dwt);
+    auto g = grads_begin(st, /*fused_buffers=*/true);
     at::Tensor pool = rows_saved;
     if (level == 2) pool = TKp > 0 ? pool_expand(rows_saved, st->pool_recv_token, TKp) : at::empty({0, H}, opts);
     at::Tensor preact;
@@ -988,6 +1209,7 @@ class Runtime {
         GemmArgs r;
         r.mode = kVarlenM; r.epilogue = kEpiStore; r.block_n = tile_n_a;
         r.a = pool; r.b = w1; r.tile_id_to_expert = st->tile_id_to_expert; r.out0 = preact;
+        if (cap) r.num_m_tiles_dev = st->dev_sizes;
         grouped_gemm(r);
       }
     }
@@ -997,7 +1219,8 @@ class Runtime {
     y.preact = preact; y.out0 = dswiglu_in; y.out1 = postact_dw2;
     y.row_weight = st->pool_topk_weight; y.row_token = st->pool_recv_token; y.dl_dweight = dl_dweight;
     y.arrival_count = g->bwd_dispatch_arrival_count; y.arrival_target = st->pool_arrival_target;
-    y.remote_dw = {kKindDispatchGrads, g->epoch, 11};
+    if (cap) { y.remote_dw_offset = g->dwt_off; y.num_m_tiles_dev = st->dev_sizes; }
+    else y.remote_dw = {kKindDispatchGrads, g->epoch, 11};
     y.row_src = st->pool_src; y.row_k_slot = st->pool_k_slot; y.num_topk = static_cast<int>(K); y.tile_stripes_done = stripes;
     y.fused_push_grads = g; y.fused_push_routing = st; y.fused_push_rows = dl_dy; y.push_flags = 3;
     grouped_gemm(y);
@@ -1005,11 +1228,21 @@ class Runtime {
     a.mode = kVarlenM; a.epilogue = kEpiScatter; a.block_n = tile_n_a_bwd; a.b_mn_major = true; a.num_ctas = num_sms_a_bwd;
     a.a = dswiglu_in; a.b = w1; a.tile_id_to_expert = st->tile_id_to_expert;
     a.row_token = st->pool_recv_token; a.scatter_local = dx;
-    a.remote_out = {kKindDispatchGrads, g->epoch, 10};
+    if (cap) { a.remote_out_offset = g->landing_off; a.num_m_tiles_dev = st->dev_sizes; }
+    else a.remote_out = {kKindDispatchGrads, g->epoch, 10};
     a.row_src = st->pool_src; a.row_k_slot = st->pool_k_slot; a.num_topk = static_cast<int>(K);
     a.tail = true; a.tail_kind = kKindGemmABwdTail; a.tail_wait = true;
     grouped_gemm(a);
-    combine_reduce(dx, landing, st->topk_idx, st->num_experts);
+    at::Tensor dwt = g->dwt;
+    if (cap) {
+      // the per-pair dL/dweight landed in a fixed region that the call after next reuses: copy it out (with zeros
+      // for skipped pairs) in the same pass that folds the landed rows into dx
+      dwt = at::empty({T, K}, opts.dtype(at::kFloat));
+      combine_reduce(dx, g->landing, st->topk_idx, st->num_experts, g->dwt, dwt, st->dev_sizes);
+      grads_finish(g);
+    } else {
+      combine_reduce(dx, g->landing, st->topk_idx, st->num_experts);
+    }
     mark_local_phase();
     if (tiles > 0) {
       GemmArgs d2;
@@ -1034,13 +1267,25 @@ class Runtime {
                          stream());
     SEP_CUDA_CHECK(cudaGetLastError());
   }
-  void combine_reduce(const at::Tensor& out, const at::Tensor& rows, const at::Tensor& topk_idx, int num_experts) {
+  // `dw_src` / `dw_dst`: also copy the per-pair scalars peers stored in `dw_src` [T, K] to `dw_dst` (0 for skipped
+  // pairs).  `sizes` (capacity mode): the dispatch's device-side sizes; when its overflow flag is set the dispatch ran
+  // empty and the landed rows are stale, so `out` is left as it is (zeros).
+  void combine_reduce(const at::Tensor& out, const at::Tensor& rows, const at::Tensor& topk_idx, int num_experts,
+                      const std::optional<at::Tensor>& dw_src = std::nullopt, const std::optional<at::Tensor>& dw_dst = std::nullopt,
+                      const std::optional<at::Tensor>& sizes = std::nullopt) {
     SEP_ASSERT(out.is_contiguous() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.size(1) % 8 == 0, "out must be contiguous [T, H] bf16");
     SEP_ASSERT(topk_idx.scalar_type() == at::kLong && topk_idx.is_contiguous() && topk_idx.size(0) == out.size(0), "topk_idx must be contiguous [T, K] int64");
-    if (out.size(0) == 0 || num_ranks_ == 1) return;
-    SEP_ASSERT(rows.numel() == out.size(0) * topk_idx.size(1) * out.size(1), "rows must be [T * K, H]");
-    ++launches_; launch_combine_reduce(out.data_ptr(), rows.data_ptr(), reinterpret_cast<const long long*>(topk_idx.data_ptr<int64_t>()),
-                          out.size(0), out.size(1), topk_idx.size(1), num_experts, num_ranks_, rank_, stream());
+    const bool copy_dw = dw_dst.has_value() && dw_dst->defined();
+    if (out.size(0) == 0 || (num_ranks_ == 1 && !copy_dw)) return;
+    if (num_ranks_ > 1) SEP_ASSERT(rows.numel() == out.size(0) * topk_idx.size(1) * out.size(1), "rows must be [T * K, H]");
+    if (copy_dw) SEP_ASSERT(dw_src.has_value() && dw_src->scalar_type() == at::kFloat && dw_dst->scalar_type() == at::kFloat &&
+                            dw_src->numel() == topk_idx.numel() && dw_dst->numel() == topk_idx.numel() && topk_idx.size(1) <= 32,
+                            "per-pair scalars must be fp32 [T, K] with K <= 32");
+    ++launches_; launch_combine_reduce(out.data_ptr(), num_ranks_ > 1 ? rows.data_ptr() : nullptr,
+                          reinterpret_cast<const long long*>(topk_idx.data_ptr<int64_t>()),
+                          out.size(0), out.size(1), topk_idx.size(1), num_experts, num_ranks_, rank_, stream(),
+                          copy_dw ? dw_src->data_ptr<float>() : nullptr, copy_dw ? dw_dst->data_ptr<float>() : nullptr,
+                          sizes.has_value() ? sizes->data_ptr<int>() + 2 : nullptr);
     SEP_CUDA_CHECK(cudaGetLastError());
   }
   at::Tensor pool_compress(const at::Tensor& pool, const at::Tensor& pool_recv_token, int64_t num_recv) {
@@ -1138,6 +1383,9 @@ class Runtime {
   int* counters_ = nullptr;
   HostCounters* host_ = nullptr;
   HostCounters* host_dev_ = nullptr;
+  HostOverflow* host_overflow_ = nullptr;
+  HostOverflow* host_overflow_dev_ = nullptr;
+  std::shared_ptr<StaticPlan> static_;
   unsigned long long budget_ns_ = 0;
   int64_t timeout_ms_ = 0;
   int epochs_[kNumKinds];
@@ -1233,6 +1481,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       RO(pool) RO(pool_topk_weight) RO(pool_recv_token) RO(pool_k_slot) RO(pool_src) RO(recv_token_to_slots)
       RO(k_local_total) RO(k_local_remaining) RO(pool_arrival_count) RO(recv_src) RO(y_done_per_token) RO(o)
       RO(total_tiles) RO(num_recv_tokens) RO(recv_per_expert) RO(metadata_done_event) RO(push_epoch) RO(meta_epoch)
+      RO(region_id) RO(dev_sizes)
 #undef RO
       .def("release_o", &DispatchState::release_o)
       .def("release_pool", &DispatchState::release_pool);
@@ -1241,6 +1490,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readonly("dl_do_pool", &GradsState::dl_do_pool)
       .def_readonly("bwd_dispatch_arrival_count", &GradsState::bwd_dispatch_arrival_count)
       .def_readonly("started_event", &GradsState::started_event)
+      .def_readonly("landing", &GradsState::landing).def_readonly("dwt", &GradsState::dwt)
+      .def_readonly("landing_off", &GradsState::landing_off).def_readonly("dwt_off", &GradsState::dwt_off)
+      .def_readonly("is_static", &GradsState::is_static)
       .def_readonly("epoch", &GradsState::epoch);
 
   py::class_<CombineState, std::shared_ptr<CombineState>>(m, "CombineState")
@@ -1253,7 +1505,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       RW(mode) RW(epilogue) RW(block_n) RW(num_ctas) RW(a_mn_major) RW(b_mn_major) RW(a) RW(b)
       RW(tile_id_to_expert) RW(expert_pool_block_offset) RW(expert_frequency) RW(arrival_count) RW(arrival_target)
       RW(out0) RW(out1) RW(preact) RW(row_weight) RW(row_token) RW(dl_dweight) RW(scatter_local) RW(row_src) RW(row_k_slot)
-      RW(tile_stripes_done) RW(k_remaining) RW(done_per_token) RW(remote_out) RW(remote_dw)
+      RW(tile_stripes_done) RW(k_remaining) RW(done_per_token) RW(remote_out) RW(remote_dw) RW(remote_out_offset) RW(remote_dw_offset) RW(num_m_tiles_dev)
       RW(num_topk) RW(seq) RW(num_m_tiles) RW(started_flag)
       RW(tail) RW(tail_kind) RW(tail_wait) RW(fused_push) RW(fused_push_grads) RW(fused_push_routing) RW(fused_push_rows)
       RW(push_flags);
@@ -1292,12 +1544,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("gate_wait_started", &Runtime::gate_wait_started)
       .def("gate_bump_issued", &Runtime::gate_bump_issued)
       .def("gate_flag_tensor", &Runtime::gate_flag_tensor)
-      .def("dispatch_begin", &Runtime::dispatch_begin)
+      .def("dispatch_begin", &Runtime::dispatch_begin, py::arg("x"), py::arg("topk_idx"), py::arg("topk_weights"),
+           py::arg("num_experts"), py::arg("tile_m"), py::arg("seq"), py::arg("capacity_mode") = false)
+      .def("enable_static", &Runtime::enable_static)
+      .def("static_enabled", &Runtime::static_enabled)
+      .def("static_fits", &Runtime::static_fits)
+      .def("static_capacity", &Runtime::static_capacity)
+      .def("overflow_info", &Runtime::overflow_info)
+      .def("next_landing", &Runtime::next_landing)
+      .def("grads_finish", &Runtime::grads_finish)
       .def("dispatch_metadata", &Runtime::dispatch_metadata)
       .def("dispatch_allocate", &Runtime::dispatch_allocate, py::arg("state"), py::arg("need_o") = true, py::arg("defer_views") = false)
       .def("dispatch_finish_views", &Runtime::dispatch_finish_views)
       .def("dispatch_push", &Runtime::dispatch_push)
-      .def("grads_begin", &Runtime::grads_begin)
+      .def("grads_begin", &Runtime::grads_begin, py::arg("state"), py::arg("fused_buffers") = false)
       .def("dispatch_set_aux", &Runtime::dispatch_set_aux)
       .def("grads_set_aux", &Runtime::grads_set_aux)
       .def("grads_push", &Runtime::grads_push)
@@ -1313,7 +1573,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("fused_forward", &Runtime::fused_forward)
       .def("fused_backward", &Runtime::fused_backward)
       .def("tile_producer", &Runtime::tile_producer)
-      .def("combine_reduce", &Runtime::combine_reduce)
+      .def("combine_reduce", &Runtime::combine_reduce, py::arg("out"), py::arg("rows"), py::arg("topk_idx"), py::arg("num_experts"),
+           py::arg("dw_src") = std::nullopt, py::arg("dw_dst") = std::nullopt, py::arg("sizes") = std::nullopt)
       .def("pool_compress", &Runtime::pool_compress)
       .def("pool_expand", &Runtime::pool_expand)
       .def("router", &Runtime::router);

@@ -15,6 +15,8 @@ enum StatusCode : int {
   kStatusTimeoutPipeline = 5,      // an mbarrier inside a GEMM pipeline
   kStatusTimeoutTail = 6,          // end-of-kernel completion wait
   kStatusBadIndex = 7,             // bounds check (debug builds of the index math)
+  kStatusOverflow = 8,             // capacity mode: a rank's pool layout does not fit the fixed regions
+  kStatusRegionMismatch = 9,       // capacity mode: the ranks did not pick the same region for this dispatch
 };
 
 struct StatusBlock {

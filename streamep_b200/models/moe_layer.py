@@ -20,17 +20,31 @@ from ..stream_moe import StreamHolder, TileConfig, make_streams, stream_moe_func
 
 def make_buffer(group, num_tokens: int, hidden: int, num_topk: int, num_experts: int, *,
                 layers_in_flight: int = 1, world_size: Optional[int] = None, imbalance: float = 1.5,
-                timeout_ms: Optional[int] = None) -> Buffer:
+                timeout_ms: Optional[int] = None, capacity_factor: Optional[float] = None) -> Buffer:
     """Size and construct the symmetric buffer for ``layers_in_flight`` layers whose forward
     state is alive at the same time (reference: ``make_buffer`` in
-    stream_ep/stream_moe/profile_pipeline.py)."""
+    stream_ep/stream_moe/profile_pipeline.py).
+
+    ``capacity_factor`` (e.g. 1.5) switches the fused layer to fixed receive regions of that many times the
+    balanced load, which removes the per-forward host read of the receive sizes
+    (:meth:`Buffer.enable_capacity_mode`); ``None`` keeps exact, dropless sizing."""
     ws = world_size if world_size is not None else (group.size() if group is not None else 1)
-    arena = Buffer.get_arena_size_hint(num_tokens, hidden, num_topk, ws, max(num_experts // ws, 1),
-                                       layers_in_flight=layers_in_flight, imbalance=imbalance)
+    if capacity_factor is not None:
+        # the fixed regions hold the pools; the rest of the arena only serves the occasional exact-mode call
+        arena = Buffer.capacity_mode_bytes(num_tokens, hidden, num_topk, num_experts, ws, capacity_factor=capacity_factor,
+                                           layers_in_flight=layers_in_flight) + (64 << 20)
+    else:
+        arena = Buffer.get_arena_size_hint(num_tokens, hidden, num_topk, ws, max(num_experts // ws, 1),
+                                           layers_in_flight=layers_in_flight, imbalance=imbalance)
     if group is None:
         from ..buffer import LocalWorld
-        return LocalWorld(1, arena_bytes=arena, timeout_ms=timeout_ms or 10000).buffers[0]
-    return Buffer(group, arena, timeout_ms=timeout_ms)
+        buf = LocalWorld(1, arena_bytes=arena, timeout_ms=timeout_ms or 10000).buffers[0]
+    else:
+        buf = Buffer(group, arena, timeout_ms=timeout_ms)
+    if capacity_factor is not None:
+        buf.enable_capacity_mode(num_tokens, hidden, num_topk, num_experts, capacity_factor=capacity_factor,
+                                 layers_in_flight=layers_in_flight)
+    return buf
 
 
 class StreamMoE(nn.Module):

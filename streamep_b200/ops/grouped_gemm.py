@@ -70,7 +70,8 @@ def streaming_moe_a(pool: torch.Tensor, w1: torch.Tensor, tile_id_to_expert: tor
                     pool_arrival_count: Optional[torch.Tensor] = None,
                     pool_arrival_target: Optional[torch.Tensor] = None,
                     tile_n: Optional[int] = None, num_sms: Optional[int] = None, buffer=None,
-                    fused_dispatch=None, push_flags: int = 3, num_tiles: Optional[int] = None):
+                    fused_dispatch=None, push_flags: int = 3, num_tiles: Optional[int] = None,
+                    live_tiles: Optional[torch.Tensor] = None):
     """``postact[TKp, I] = swiglu(pool[TKp, H] @ w1[e]^T)`` tile by tile.
 
     ``w1`` is ``[E_local, 2I, H]`` with gate/up rows interleaved.  With
@@ -103,13 +104,15 @@ def streaming_moe_a(pool: torch.Tensor, w1: torch.Tensor, tile_id_to_expert: tor
     if fused_dispatch is not None:
         a.fused_push = fused_dispatch
         a.push_flags = push_flags
+    if live_tiles is not None and num_tiles is None:
+        a.num_m_tiles_dev = live_tiles
     _rt(buffer).grouped_gemm(a)
     return postact_a, preact_a
 
 
 def grouped_gemm_preact(pool: torch.Tensor, w1: torch.Tensor, tile_id_to_expert: torch.Tensor, *,
                         out: Optional[torch.Tensor] = None, tile_n: Optional[int] = None,
-                        num_sms: Optional[int] = None, buffer=None):
+                        num_sms: Optional[int] = None, live_tiles: Optional[torch.Tensor] = None, buffer=None):
     """``preact[TKp, 2I] = pool @ w1[e]^T`` (activation-checkpoint recompute)."""
     rows = pool.shape[0]
     two_i = w1.shape[1]
@@ -118,6 +121,8 @@ def grouped_gemm_preact(pool: torch.Tensor, w1: torch.Tensor, tile_id_to_expert:
     a = _args()
     a.mode, a.epilogue, a.block_n = VARLEN_M, EPI_STORE, pick_block_n(two_i, tile_n)
     a.a, a.b, a.tile_id_to_expert, a.out0 = pool, w1, tile_id_to_expert, out
+    if live_tiles is not None:
+        a.num_m_tiles_dev = live_tiles
     if num_sms:
         a.num_ctas = num_sms
     _rt(buffer).grouped_gemm(a)
@@ -125,11 +130,17 @@ def grouped_gemm_preact(pool: torch.Tensor, w1: torch.Tensor, tile_id_to_expert:
 
 
 def _scatter_common(a, *, o, pool_recv_token, tile_stripes_done, k_local_remaining, done_per_token, seq,
-                    remote_offsets, pool_src, pool_k_slot, num_topk, tail_kind, tail_wait):
+                    remote_offsets, pool_src, pool_k_slot, num_topk, tail_kind, tail_wait, remote_static_offset=-1,
+                    live_tiles=None):
     a.row_token = pool_recv_token
     a.scatter_local = o
+    if live_tiles is not None:
+        a.num_m_tiles_dev = live_tiles
     if remote_offsets is not None:
-        a.remote_out = [int(v) for v in remote_offsets]
+        if remote_static_offset is not None and remote_static_offset >= 0:
+            a.remote_out_offset = int(remote_static_offset)   # capacity mode: same arena offset on every rank
+        else:
+            a.remote_out = [int(v) for v in remote_offsets]
         a.row_src, a.row_k_slot, a.num_topk = pool_src, pool_k_slot, int(num_topk)
         a.tail, a.tail_kind, a.tail_wait = True, tail_kind, tail_wait
     else:
@@ -148,7 +159,8 @@ def streaming_moe_y(postact_a: torch.Tensor, w2: torch.Tensor, tile_id_to_expert
                     remote_out_offsets: Optional[Sequence[int]] = None, pool_src: Optional[torch.Tensor] = None,
                     pool_k_slot: Optional[torch.Tensor] = None, num_topk: int = 0,
                     tail_wait: bool = True, started_flag: bool = False,
-                    tile_n: Optional[int] = None, num_sms: Optional[int] = None, buffer=None):
+                    tile_n: Optional[int] = None, num_sms: Optional[int] = None, buffer=None,
+                    remote_static_offset: int = -1, live_tiles: Optional[torch.Tensor] = None):
     """``y = postact @ w2[e]^T`` scaled by the slot's top-k weight and reduced
     with 16-byte bf16x2 ``red.add`` into
 
@@ -173,7 +185,8 @@ def streaming_moe_y(postact_a: torch.Tensor, w2: torch.Tensor, tile_id_to_expert
     _scatter_common(a, o=o, pool_recv_token=pool_recv_token, tile_stripes_done=tile_n_stripes_done,
                     k_local_remaining=k_local_remaining, done_per_token=y_done_per_token, seq=combine_seq,
                     remote_offsets=remote_out_offsets, pool_src=pool_src, pool_k_slot=pool_k_slot, num_topk=num_topk,
-                    tail_kind=KIND_GEMM_Y_TAIL, tail_wait=tail_wait)
+                    tail_kind=KIND_GEMM_Y_TAIL, tail_wait=tail_wait, remote_static_offset=remote_static_offset,
+                    live_tiles=live_tiles)
     if num_sms:
         a.num_ctas = num_sms
     _rt(buffer).grouped_gemm(a)
@@ -188,7 +201,8 @@ def streaming_moe_a_bwd(dL_dswiglu_in: torch.Tensor, w1: torch.Tensor, tile_id_t
                         remote_out_offsets: Optional[Sequence[int]] = None, pool_src: Optional[torch.Tensor] = None,
                         pool_k_slot: Optional[torch.Tensor] = None, num_topk: int = 0,
                         tail_wait: bool = True, started_flag: bool = False,
-                        tile_n: Optional[int] = None, num_sms: Optional[int] = None, buffer=None):
+                        tile_n: Optional[int] = None, num_sms: Optional[int] = None, buffer=None,
+                        remote_static_offset: int = -1, live_tiles: Optional[torch.Tensor] = None):
     """``dpool = dL_dswiglu_in[TKp, 2I] @ w1[e]`` (NN GEMM, K = 2I) reduced into
     ``dL_dx_per_r[r]`` locally or into the source rank's ``dL_dx`` remotely
     (fused combine_grads).  No per-slot weight: it is already folded into
@@ -203,7 +217,8 @@ def streaming_moe_a_bwd(dL_dswiglu_in: torch.Tensor, w1: torch.Tensor, tile_id_t
     _scatter_common(a, o=dL_dx_per_r, pool_recv_token=pool_recv_token, tile_stripes_done=tile_n_stripes_done,
                     k_local_remaining=bwd_k_local_remaining, done_per_token=bwd_a_done_per_token,
                     seq=dispatch_seq, remote_offsets=remote_out_offsets, pool_src=pool_src, pool_k_slot=pool_k_slot,
-                    num_topk=num_topk, tail_kind=KIND_GEMM_A_BWD_TAIL, tail_wait=tail_wait)
+                    num_topk=num_topk, tail_kind=KIND_GEMM_A_BWD_TAIL, tail_wait=tail_wait,
+                    remote_static_offset=remote_static_offset, live_tiles=live_tiles)
     if num_sms:
         a.num_ctas = num_sms
     _rt(buffer).grouped_gemm(a)
@@ -222,7 +237,8 @@ def streaming_moe_y_bwd(dL_do_pool: torch.Tensor, w2: torch.Tensor, preact_a: to
                         num_topk: int = 0, tile_n_stripes_done: Optional[torch.Tensor] = None,
                         fused_dispatch_grads=None, fused_routing=None, fused_rows: Optional[torch.Tensor] = None,
                         push_flags: int = 3, num_tiles: Optional[int] = None,
-                        tile_n: Optional[int] = None, num_sms: Optional[int] = None, buffer=None):
+                        tile_n: Optional[int] = None, num_sms: Optional[int] = None, buffer=None,
+                        remote_static_offset: int = -1, live_tiles: Optional[torch.Tensor] = None):
     """``g = dL_do_pool[TKp, H] @ w2[e]`` (NN GEMM, K = H) followed by the SwiGLU
     backward on the saved ``preact_a``:
 
@@ -254,8 +270,13 @@ def streaming_moe_y_bwd(dL_do_pool: torch.Tensor, w2: torch.Tensor, preact_a: to
         a.num_m_tiles = num_tiles
     if arrival_count is not None:
         a.arrival_count, a.arrival_target = arrival_count, arrival_target
+    if live_tiles is not None and num_tiles is None:
+        a.num_m_tiles_dev = live_tiles
     if remote_dw_offsets is not None:
-        a.remote_dw = [int(v) for v in remote_dw_offsets]
+        if remote_static_offset is not None and remote_static_offset >= 0:
+            a.remote_dw_offset = int(remote_static_offset)
+        else:
+            a.remote_dw = [int(v) for v in remote_dw_offsets]
         a.row_src, a.row_k_slot, a.num_topk = pool_src, pool_k_slot, num_topk
         a.tile_stripes_done = tile_n_stripes_done
     if fused_dispatch_grads is not None:
@@ -316,8 +337,12 @@ def router_topk(x: torch.Tensor, w_gate: torch.Tensor, top_k: int, num_ranks: in
     return (idx, w, in_rank, probs) if return_probs else (idx, w, in_rank)
 
 
-def combine_reduce(out: torch.Tensor, landed_rows: torch.Tensor, topk_idx: torch.Tensor, num_experts: int, buffer=None):
+def combine_reduce(out: torch.Tensor, landed_rows: torch.Tensor, topk_idx: torch.Tensor, num_experts: int,
+                   dw_src: Optional[torch.Tensor] = None, dw_dst: Optional[torch.Tensor] = None,
+                   sizes: Optional[torch.Tensor] = None, buffer=None):
     """``out[t] += sum_k landed_rows[t * K + k]`` over the pairs owned by other ranks, in fp32
-    (second half of the fused combine; a no-op for a single rank)."""
-    _rt(buffer).combine_reduce(out, landed_rows, topk_idx.contiguous(), int(num_experts))
+    (second half of the fused combine; a no-op for a single rank).  With ``dw_src`` / ``dw_dst`` the same pass
+    copies the per-pair scalars peers stored in ``dw_src [T, K]`` to ``dw_dst`` (0 for skipped pairs).
+    ``sizes``: the device-side sizes of a capacity-mode dispatch; rows are ignored when its overflow flag is set."""
+    _rt(buffer).combine_reduce(out, landed_rows, topk_idx.contiguous(), int(num_experts), dw_src, dw_dst, sizes)
     return out

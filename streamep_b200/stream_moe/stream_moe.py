@@ -111,8 +111,11 @@ def moe_forward(ctx, streams, buffer, x, topk_idx, topk_weights, is_token_in_ran
         with torch.cuda.stream(comp):
             _nvtx_push(f"fwd_fused_{_NVTX_FWD}")
             K = topk_idx.shape[1]
-            landing = buffer.alloc_symmetric([T * K if buffer.group_size > 1 else 0, H], torch.bfloat16)
-            st, seq = buffer._dispatch_begin(x, topk_idx, topk_weights, num_experts, cfg.tile_m, None)
+            # capacity mode (Buffer.enable_capacity_mode): fixed receive regions, no host read of the sizes
+            cap = rt.static_fits(T, H, K)
+            landing = x.new_empty(0, H) if cap else \
+                buffer.alloc_symmetric([T * K if buffer.group_size > 1 else 0, H], torch.bfloat16)
+            st, seq = buffer._dispatch_begin(x, topk_idx, topk_weights, num_experts, cfg.tile_m, None, cap)
             rt.dispatch_metadata(st, 3)
             try:
                 out, postact, preact = rt.fused_forward(st, w1c, w2c, landing, level == 0, cfg.tile_n_a, cfg.tile_n_y,
@@ -132,11 +135,15 @@ def moe_forward(ctx, streams, buffer, x, topk_idx, topk_weights, is_token_in_ran
             _nvtx_push(f"fwd_dispatch_{_NVTX_FWD}")
             # rows that other ranks compute for this rank's tokens land here, one per (token, k)
             K = topk_idx.shape[1]
-            landing = buffer.alloc_symmetric([T * K if buffer.group_size > 1 else 0, H], torch.bfloat16)
+            cap = rt.static_fits(T, H, K)
             _, handle, _ = buffer.dispatch(x, topk_idx, topk_weights, is_token_in_rank, num_experts,
-                                           tile_m=cfg.tile_m, launch_push=False)
+                                           tile_m=cfg.tile_m, launch_push=False, capacity_mode=cap)
             st = handle._dispatch_out
-            rt.dispatch_set_aux(st, 0, landing)
+            if cap:
+                landing, landing_off = rt.next_landing(T, H, K)
+            else:
+                landing, landing_off = buffer.alloc_symmetric([T * K if buffer.group_size > 1 else 0, H], torch.bfloat16), -1
+                rt.dispatch_set_aux(st, 0, landing)
             _nvtx_pop()
         TKp = handle.TK_padded
         postact = torch.empty(TKp, I, dtype=x.dtype, device=x.device)
@@ -150,10 +157,11 @@ def moe_forward(ctx, streams, buffer, x, topk_idx, topk_weights, is_token_in_ran
             _nvtx_push(f"fwd_combine_{_NVTX_FWD}")
             gg.streaming_moe_y(postact, w2c, handle.tile_id_to_expert, handle.pool_topk_weight,
                                handle.pool_recv_token, o=out, remote_out_offsets=(KIND_DISPATCH, st.push_epoch, AUX0),
+                               remote_static_offset=landing_off, live_tiles=st.dev_sizes if cap else None,
                                pool_src=handle.pool_src, pool_k_slot=handle.pool_k_slot, num_topk=K,
                                tail_wait=not buffer._emulated, tile_n=cfg.tile_n_y, num_sms=cfg.num_sms_y, buffer=buffer)
             buffer._phase()
-            gg.combine_reduce(out, landing, st.topk_idx, num_experts, buffer=buffer)
+            gg.combine_reduce(out, landing, st.topk_idx, num_experts, sizes=st.dev_sizes if cap else None, buffer=buffer)
             buffer._phase()     # (emulated ranks) nobody reuses a landing buffer before every reduce is enqueued
             del landing
             _nvtx_pop()
@@ -214,7 +222,7 @@ def _launch_fused_a(buffer, handle, w1, postact, preact, cfg):
     st = handle._dispatch_out
     common = dict(postact_a=postact, preact_a=preact, pool_arrival_count=handle.pool_arrival_count,
                   pool_arrival_target=handle.pool_arrival_target, tile_n=cfg.tile_n_a, num_sms=cfg.num_sms_a,
-                  buffer=buffer, fused_dispatch=st)
+                  buffer=buffer, fused_dispatch=st, live_tiles=st.dev_sizes if st.region_id >= 0 else None)
     if not buffer._emulated:
         gg.streaming_moe_a(handle.pool, w1, handle.tile_id_to_expert, push_flags=3, **common)
         return
@@ -286,22 +294,23 @@ def moe_backward(ctx, dL_dy):
         preact = sv.preact
         if preact is None:
             preact = gg.grouped_gemm_preact(pool, sv.w1, handle.tile_id_to_expert, tile_n=cfg.tile_n_a,
+                                            live_tiles=st.dev_sizes if st.region_id >= 0 else None,
                                             buffer=buffer) if tiles > 0 else pool.new_empty(0, 2 * I)
         return pool, preact
 
     if fused:
         with torch.cuda.stream(comp):
             dx = torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
-            landing = buffer.alloc_symmetric([T * K if buffer.group_size > 1 else 0, H], torch.bfloat16)
-            dwt = buffer.alloc_symmetric([T, K], torch.float32, zero=True)
-            dl_do_pool, bwd_count, _ = buffer.dispatch_grads(handle, dL_dy, launch_push=False)
+            dl_do_pool, bwd_count, _ = buffer.dispatch_grads(handle, dL_dy, launch_push=False, fused_buffers=True)
             g = handle._grads_state
-            rt.grads_set_aux(g, 0, landing)
-            rt.grads_set_aux(g, 1, dwt)
+            landing, dwt = g.landing, g.dwt
+            cap = g.is_static
+            live = st.dev_sizes if cap else None
             pool, preact = rebuild_inputs()
             ykw = dict(dL_dswiglu_in=dswiglu_in, postact_a_for_dW2=postact_dw2, dL_dweight=dl_dweight,
                        arrival_count=bwd_count, arrival_target=handle.pool_arrival_target,
-                       remote_dw_offsets=(KIND_DISPATCH_GRADS, g.epoch, AUX1), pool_src=handle.pool_src,
+                       remote_dw_offsets=(KIND_DISPATCH_GRADS, g.epoch, AUX1), remote_static_offset=g.dwt_off,
+                       live_tiles=live, pool_src=handle.pool_src,
                        pool_k_slot=handle.pool_k_slot, num_topk=K, tile_n_stripes_done=stripes_y,
                        fused_dispatch_grads=g, fused_routing=st, fused_rows=dL_dy, tile_n=cfg.tile_n_y_bwd,
                        num_sms=cfg.num_sms_y_bwd, buffer=buffer)
@@ -316,11 +325,18 @@ def moe_backward(ctx, dL_dy):
                 gg.streaming_moe_y_bwd(*yargs, push_flags=0, **ykw)
             gg.streaming_moe_a_bwd(dswiglu_in, sv.w1, handle.tile_id_to_expert, handle.pool_recv_token,
                                    dL_dx_per_r=dx, remote_out_offsets=(KIND_DISPATCH_GRADS, g.epoch, AUX0),
+                                   remote_static_offset=g.landing_off, live_tiles=live,
                                    pool_src=handle.pool_src, pool_k_slot=handle.pool_k_slot, num_topk=K,
                                    tail_wait=not buffer._emulated, tile_n=cfg.tile_n_a_bwd,
                                    num_sms=cfg.num_sms_a_bwd, buffer=buffer)
             buffer._phase()
-            gg.combine_reduce(dx, landing, st.topk_idx, st.num_experts, buffer=buffer)
+            if cap:     # copy the per-pair dL/dweight out of its fixed region in the same pass
+                dwt_out = torch.empty(T, K, dtype=torch.float32, device=dev)
+                gg.combine_reduce(dx, landing, st.topk_idx, st.num_experts, dw_src=dwt, dw_dst=dwt_out, sizes=live, buffer=buffer)
+                dwt = dwt_out
+                rt.grads_finish(g)
+            else:
+                gg.combine_reduce(dx, landing, st.topk_idx, st.num_experts, buffer=buffer)
             buffer._phase()
             del landing
             _launch_dw(buffer, handle, cfg, dl_do_pool, postact_dw2, dswiglu_in, pool, dW1, dW2)
