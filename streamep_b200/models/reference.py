@@ -349,14 +349,15 @@ def dswiglu_reference(gate, up, g):
     return dgate, dup, silu * up
 
 
-def check_close(name: str, got: torch.Tensor, want: torch.Tensor, atol: float, rtol: float) -> None:
+def check_close(name: str, got: torch.Tensor, want: torch.Tensor, atol: float, rtol: float,
+                rel_floor: float = 0.0) -> None:
     """Dual-threshold rule of the reference validator: an element fails only if
-    BOTH ``|diff| > atol`` and ``|diff| > rtol * |want|``
-    (reference: stream_ep/stream_moe/validate_multi_iter.py:288-294)."""
-    got = got.detach().float().cpu()
-    want = want.detach().float().cpu()
+    BOTH ``|diff| > atol`` and ``|diff| > rtol * (|want| + rel_floor)``
+    (reference: stream_ep/stream_moe/validate_multi_iter.py:559-575, which uses ``rel_floor = 1e-3``)."""
+    got = got.detach().float()
+    want = want.detach().float().to(got.device)
     diff = (got - want).abs()
-    bad = (diff > atol) & (diff > rtol * want.abs())
+    bad = (diff > atol) & (diff > rtol * (want.abs() + rel_floor))
     if not torch.isfinite(got).all():
         raise AssertionError(f"{name}: non-finite values in result")
     if bad.any():

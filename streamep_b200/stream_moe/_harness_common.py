@@ -43,12 +43,17 @@ def add_shape_args(ap):
     ap.add_argument("--layers", type=int, default=1)
     ap.add_argument("--fused", type=int, default=1)
     ap.add_argument("--ckpt-level", type=int, default=0)
+    ap.add_argument("--capacity-factor", type=float, default=0.0,
+                    help="> 0: capacity mode (fixed receive regions of this many times the balanced load, no host read "
+                         "per forward); 0: exact host-sized buffers")
 
 
 def build_layers(args, group, world, dev):
     from ..models.moe_layer import StreamMoE, make_buffer
     E = args.experts_per_rank * world
-    buf = make_buffer(group, args.tokens, args.hidden, args.topk, E, layers_in_flight=args.layers, world_size=world)
+    cf = getattr(args, "capacity_factor", 0.0)
+    buf = make_buffer(group, args.tokens, args.hidden, args.topk, E, layers_in_flight=args.layers, world_size=world,
+                      imbalance=getattr(args, "imbalance", 1.5), capacity_factor=cf if cf > 0 else None)
     layers = [StreamMoE(args.hidden, args.ffn, E, args.topk, buf, fused=bool(args.fused),
                         activation_checkpoint_level=args.ckpt_level, device=dev, seed=10 + i)
               for i in range(args.layers)]

@@ -170,7 +170,7 @@ def test_capacity_overflow_runs_empty_and_is_reported_one_step_late(native):
         assert float(out.float().abs().max()) == 0.0 and float(dx.float().abs().max()) == 0.0
         assert float(dw1.float().abs().max()) == 0.0 and float(dw2.float().abs().max()) == 0.0
         assert float(dtw.abs().max()) == 0.0
-    with pytest.raises(StreamEPOverflow, match="capacity_factor"):
+    with pytest.raises(StreamEPOverflow, match="capacity overflow"):
         world.check_status()
     # the buffer stays usable: a dispatch that fits runs normally afterwards
     res = world.run(make_fn(fit))

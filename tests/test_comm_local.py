@@ -247,3 +247,58 @@ def test_handle_stats(native):
         assert g["rows_padded"] == handles[r].TK_padded and 0.0 <= g["padding_ratio"] < 1.0
         want_remote = int(((idxs[r] >= 0) & (idxs[r] // (E // R) != r)).sum())
         assert g["pairs_sent_remote"] == want_remote and g["dispatch_bytes_out"] == want_remote * H * 2
+
+
+def test_three_dispatches_three_routings_one_buffer(native):
+    """Three dispatches with three different routings (and token counts) through ONE buffer, all three handles kept
+    alive and each checked in full against the oracle afterwards: nothing of one dispatch may leak into another
+    (the reference's tests/test_multi_dispatch.py)."""
+    R, H, K, E = 4, 256, 6, 32
+    world = _world(R, arena_mb=256)
+    cases = [_inputs(R, [300, 128, 512, 77], H, K, E, seed=21, sentinel_p=0.05),
+             _inputs(R, [64, 700, 33, 256], H, K, E, seed=22, empty_expert=3),
+             _inputs(R, 400, H, K, E, seed=23, sentinel_p=0.2)]
+    handles = [world.dispatch(xs, idxs, ws, E) for xs, idxs, ws in cases]
+    seqs = [h[0].dispatch_seq for h in handles]
+    assert seqs == sorted(seqs) and len(set(seqs)) == 3
+    for (xs, idxs, ws), hs in zip(cases, handles):
+        _check_dispatch(world, hs, xs, idxs, ws, E)
+
+
+def test_metadata_at_production_scale_top13(native):
+    """Every metadata tensor at the size the reference checks (tests/test_metadata.py:289-292: 8192 tokens per
+    rank, top-13, 384 experts, 128-row tiles) on 8 emulated ranks, against the vectorised form of the layout
+    oracle (pinned to the loop oracle on small cases by tests/test_reference_cpu.py)."""
+    from streamep_b200.models.layout_fast import dispatch_layout_fast
+    R, T, H, K, E = 8, 8192, 64, 13, 384
+    world = _world(R, arena_mb=160)
+    g = torch.Generator(device="cpu").manual_seed(99)
+    xs, idxs, ws = [], [], []
+    for r in range(R):
+        # distinct experts per token from a random permutation; 3 % of the pairs are skipped (-1)
+        idx = torch.rand(T, E, generator=g).argsort(dim=1)[:, :K].contiguous()
+        idx = torch.where(torch.rand(T, K, generator=g) < 0.03, torch.full_like(idx, -1), idx)
+        xs.append(torch.randn(T, H, generator=g).to(torch.bfloat16).to(DEV))
+        idxs.append(idx.to(DEV)); ws.append(torch.rand(T, K, generator=g).to(DEV))
+    handles = world.dispatch(xs, idxs, ws, E)
+    torch.cuda.synchronize()
+    world.check_status()
+    layouts, sends = dispatch_layout_fast(idxs, E, world.buffers[0].num_channels, 128, ws)
+    for r in range(R):
+        h, L, S = handles[r], layouts[r], sends[r]
+        st = h._dispatch_out
+        assert h.total_tiles == L.total_tiles and st.num_recv_tokens == L.num_recv_tokens
+        for name in ("expert_frequency", "expert_pool_block_offset", "base_pool", "seen_per_substream",
+                     "tile_id_to_expert", "pool_arrival_target", "pool_recv_token", "pool_k_slot",
+                     "recv_token_to_slots", "k_local_total", "recv_channel_prefix_matrix"):
+            assert torch.equal(getattr(h, name), getattr(L, name)), f"rank {r}: {name}"
+        assert torch.equal(h.rank_prefix_matrix[:, r], L.rank_prefix_matrix[:, r])
+        assert torch.equal(h.pool_arrival_count, L.pool_arrival_target)
+        assert torch.equal(h.pool_src[:, 0], L.pool_src_rank) and torch.equal(h.pool_src[:, 1], L.pool_src_token)
+        assert torch.equal(st.pair_slot, S.pair_slot) and torch.equal(st.send_recv_token, S.send_recv_token)
+        assert torch.equal(h.send_head, S.send_head) and torch.equal(h.channel_prefix_matrix, S.channel_prefix_matrix)
+        valid = (L.pool_recv_token >= 0).nonzero().squeeze(1)
+        all_x = torch.stack(xs)                                      # [R, T, H]
+        want_rows = all_x[L.pool_src_rank[valid].long(), L.pool_src_token[valid].long()]
+        assert torch.equal(h.pool[valid], want_rows), f"rank {r}: pool rows"
+        assert torch.equal(h.pool_topk_weight[valid], L.pool_topk_weight[valid])

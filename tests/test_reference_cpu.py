@@ -203,3 +203,27 @@ def test_gloo_world2_reference_layer_fwd_bwd():
     for p in procs:
         p.join(timeout=60)
     assert all(r[1] == "ok" for r in results), results
+
+
+@pytest.mark.parametrize("R,tokens,K,E,C,sentinel", [(1, [300], 4, 8, 5, 0.05), (2, [257, 100], 4, 8, 7, 0.1),
+                                                     (4, [260, 17, 0, 400], 6, 64, 10, 0.03), (8, [50] * 8, 13, 384, 40, 0.0)])
+def test_vectorised_layout_oracle_equals_the_loop_oracle(R, tokens, K, E, C, sentinel):
+    """The production-scale metadata check runs against layout_fast; here it is pinned, field by field, to the
+    loop oracle that states the placement rule."""
+    import dataclasses
+    from helpers import make_routing
+    from streamep_b200.models.layout_fast import dispatch_layout_fast
+    from streamep_b200.models.reference import dispatch_layout_reference
+    idxs, ws = [], []
+    for r, T in enumerate(tokens):
+        i, w = make_routing(T, K, E, 7 * r + 1, "cpu", sentinel_p=sentinel)
+        idxs.append(i); ws.append(w)
+    a = dispatch_layout_reference(idxs, E, C, 128, ws)
+    b = dispatch_layout_fast(idxs, E, C, 128, ws)
+    for la, lb in zip(a[0] + a[1], b[0] + b[1]):
+        for f in dataclasses.fields(la):
+            x, y = getattr(la, f.name), getattr(lb, f.name)
+            if isinstance(x, torch.Tensor):
+                assert torch.equal(x, y.to(x.dtype)), f.name
+            else:
+                assert x == y, f.name
