@@ -110,7 +110,7 @@ def comm_checks(buf, rank, R, dev):
         report(f"dispatch_grads + combine_grads (rep {rep})", grads, rank)
 
 
-def layer_checks(buf, rank, R, dev, lopsided=False):
+def layer_checks(buf, rank, R, dev, lopsided=False, tag0=""):
     """Layer forward + backward against the global fp32 oracle.  ``lopsided``: the last rank has no tokens
     and every pair goes to rank 0's experts, so every other rank receives nothing (empty pools, no tiles)
     but still takes part in every collective."""
@@ -139,8 +139,8 @@ def layer_checks(buf, rank, R, dev, lopsided=False):
     streams = make_streams()
     s = lambda t: max(float(t.abs().max()), 1e-6)   # noqa: E731
 
-    tag = "lopsided " if lopsided else ""
-    for fused in (True, False):
+    tag = tag0 + ("lopsided " if lopsided else "")
+    for fused in ((True,) if buf.capacity_mode else (True, False)):
         for level in ((0, 2) if lopsided else (0, 1, 2)):
             def run():
                 x = x0.clone().requires_grad_(True)
@@ -211,6 +211,17 @@ def main():
         layer_checks(buf, rank, world, dev, lopsided=True)
     if args.scenario in ("all", "missing_rank"):
         missing_rank_check(buf, rank, world, dev)
+    if args.scenario in ("all", "capacity"):
+        # the same layer checks on fixed receive regions (no host read per forward); the lopsided case sends every
+        # pair to rank 0, so the regions are sized for the whole group's pairs
+        cbuf = Buffer(dist.group.WORLD, Buffer.capacity_mode_bytes(700 + 64 * world, 512, 4, 4 * world, world,
+                                                                   capacity_factor=float(world) + 0.5) + (256 << 20),
+                      timeout_ms=5000)
+        cbuf.enable_capacity_mode(700 + 64 * world, 512, 4, 4 * world, capacity_factor=float(world) + 0.5)
+        layer_checks(cbuf, rank, world, dev, tag0="capacity mode: ")
+        layer_checks(cbuf, rank, world, dev, lopsided=True, tag0="capacity mode: ")
+        report("capacity mode: no dispatch overflowed", lambda: cbuf.overflow_info()["count"] == 0 or (_ for _ in ()).throw(
+            AssertionError(str(cbuf.overflow_info()))), rank)
     dist.barrier(device_ids=[local])
     torch.cuda.synchronize()
     if rank == 0:
