@@ -110,7 +110,7 @@ def oracle_gate(layer, routing, x_dev, dy_dev, group, world, rank, E, K, samples
             act = torch.nn.functional.silu(hh[:, 0::2]) * hh[:, 1::2]
             acc = acc.index_add(0, m, (act @ w2g[ee].float().t()) * w[sel][m, k:k + 1].float())
     acc.backward(dy_dev[sel].float())
-    got_o, want_o, got_d, want_d = out[sel].float(), acc.detach(), h.grad[sel].float(), xs.grad
+    got_o, want_o, got_d, want_d = out.detach()[sel].float(), acc.detach(), h.grad[sel].float(), xs.grad.detach()
     out_scale = float(want_o.abs().max()) if sel.numel() else 1.0
     dx_scale = float(want_d.abs().max()) if sel.numel() else 1.0
     out_err = float((got_o - want_o).abs().max()) if sel.numel() else 0.0
@@ -341,7 +341,10 @@ def main():
     # ---------------------------------------------------------------- sustained: >= N seconds of continuous steps
     sustained = None
     if args.sustained_seconds > 0:
-        n_sus = max(int(args.sustained_seconds * 1e3 / max(ms, 1e-3)) + 1, args.steps)
+        ms_all = torch.tensor([ms], device=dev)
+        if world > 1:
+            dist.all_reduce(ms_all, op=dist.ReduceOp.MAX)     # every rank must run the same number of steps
+        n_sus = max(int(args.sustained_seconds * 1e3 / max(float(ms_all[0]), 1e-3)) + 1, args.steps)
         barrier()
         sampler2 = ClockSampler(local_rank).start()
         evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_sus)]

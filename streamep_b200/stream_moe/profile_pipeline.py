@@ -67,6 +67,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--fused", type=int, default=1)
     ap.add_argument("--ckpt-level", type=int, default=0)
+    ap.add_argument("--capacity-factor", type=float, default=0.0,
+                    help="> 0: capacity mode (fixed receive regions, no host read per forward); 0: exact sizing")
     ap.add_argument("--out", default=None)
     ap.add_argument("--with-router", action="store_true", help="profile the module call (router + experts) and a scalar loss")
     args = ap.parse_args()
@@ -86,7 +88,8 @@ def main():
     T, H, I, K = args.tokens, args.hidden, args.ffn, args.topk
     E = args.experts_per_rank * world
     torch.manual_seed(1 + rank)
-    buf = make_buffer(group, T, H, K, E, layers_in_flight=args.layers, world_size=world)
+    buf = make_buffer(group, T, H, K, E, layers_in_flight=args.layers, world_size=world,
+                      capacity_factor=args.capacity_factor if args.capacity_factor > 0 else None)
     layers = [StreamMoE(H, I, E, K, buf, fused=bool(args.fused), activation_checkpoint_level=args.ckpt_level,
                         device=dev, seed=10 + i) for i in range(args.layers)]
     x = torch.randn(T, H, device=dev).to(torch.bfloat16)
@@ -153,7 +156,8 @@ def main():
         lines = []
         total = 0.0
         lines.append(f"config: tokens/rank={T} hidden={H} ffn={I} experts={E} ({args.experts_per_rank}/rank) top{K} "
-                     f"layers={args.layers} world={world} fused={args.fused} ckpt_level={args.ckpt_level}")
+                     f"layers={args.layers} world={world} fused={args.fused} ckpt_level={args.ckpt_level} "
+                     f"capacity_factor={args.capacity_factor}")
         from ..utils.roofline import layer_rooflines, load_peaks
         peaks = load_peaks()
         roof = layer_rooflines(T, H, I, K, world, peaks, experts_per_rank=args.experts_per_rank,
