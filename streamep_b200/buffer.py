@@ -194,6 +194,9 @@ class Buffer:
         warps = os.environ.get("STREAM_EP_PUSH_WARPS")
         if warps:
             self.runtime.set_active_push_warps(int(warps))
+        ctas = os.environ.get("STREAM_EP_PUSH_CTAS")
+        if ctas:
+            self.runtime.set_push_ctas(int(ctas))
 
     # ------------------------------------------------------------------ lifecycle
     def destroy(self):

@@ -156,7 +156,10 @@ struct PushParams {
   int flags;                     // bit0 publish own record, bit1 push, bit2 tail wait for own tiles
   int static_targets;            // 1: every rank's buffers sit at the offsets of `own` (capacity mode): no records
   int pairs_per_chunk;           // pairs one warp ships between two counter releases (<= 32)
+  int head_pairs_per_chunk;      // the first `head_chunks` chunks are this small, so that the first tiles complete early
+  int head_chunks;               // (0 = every chunk has pairs_per_chunk pairs)
   int active_push_warps;         // push warps per CTA of the fused kernels that take chunks (0 = all)
+  int push_ctas;                 // fused kernels: this many CTAs only push and the others only multiply (0 = every CTA does both)
   void* peer_base[kMaxRanks];
   ControlLayout ctl;
   BufferRecord own;              // offsets of this rank's freshly allocated buffers (grads: only `pool`
@@ -319,7 +322,13 @@ struct GemmParams {
   int rank;
   StatusBlock* status;
   unsigned long long wait_budget_ns;
+  // Optional per-CTA time stamps, [gridDim.x][kTimingCols] int64 of %globaltimer nanoseconds (null = off):
+  // 0 kernel start, 1 ns the operand pipeline stood still for tile gates, 2 first tile ready, 3 tiles this CTA had
+  // finished when its push ended, 4 first push chunk
+  // claimed, 5 last push chunk done, 6 kernel end, 7 tiles this CTA multiplied.
+  long long* timing;
 };
+constexpr int kTimingCols = 8;
 
 // tmap_a / tmap_b: 128-byte CUtensorMap blobs (3-D, bf16, 128-byte swizzle) built by the host.
 // tmap_o0 / tmap_o1: output maps for the TMA-store epilogues (store, swiglu, dswiglu); box 32 rows x one

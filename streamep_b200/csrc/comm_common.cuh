@@ -107,6 +107,22 @@ __device__ __forceinline__ void resolve_push_targets(PushTargets& tg, int p, voi
   tg.recv_src[p] = reinterpret_cast<int2*>(b + rec[9]);
 }
 
+// Chunking of the send list.  All push warps of a rank claim chunks from one counter, so at any time (warps x chunk
+// bytes) are in flight and nothing completes before a whole chunk is through.  The first `head_chunks` chunks are
+// therefore small (the consumers' first tiles complete after a short time); later chunks are larger, because every
+// chunk ends with a release that waits for the warp's outstanding remote stores.
+__device__ __forceinline__ int push_num_chunks(const PushParams& p, int num_send) {
+  const int head_pairs = min(num_send, p.head_chunks * p.head_pairs_per_chunk);
+  const int head = p.head_pairs_per_chunk > 0 ? (head_pairs + p.head_pairs_per_chunk - 1) / p.head_pairs_per_chunk : 0;
+  return head + (num_send - head_pairs + p.pairs_per_chunk - 1) / p.pairs_per_chunk;
+}
+__device__ __forceinline__ void push_chunk_range(const PushParams& p, int num_send, int chunk, int& p0, int& p1) {
+  const int head_pairs = min(num_send, p.head_chunks * p.head_pairs_per_chunk);
+  const int head = p.head_pairs_per_chunk > 0 ? (head_pairs + p.head_pairs_per_chunk - 1) / p.head_pairs_per_chunk : 0;
+  if (chunk < head) { p0 = chunk * p.head_pairs_per_chunk; p1 = min(p0 + p.head_pairs_per_chunk, head_pairs); }
+  else { p0 = head_pairs + (chunk - head) * p.pairs_per_chunk; p1 = min(p0 + p.pairs_per_chunk, num_send); }
+}
+
 // One warp ships the pairs at positions [pos_begin, pos_end) of the send list (at most 32).  Lane j
 // owns pair j of the chunk for the scalar work; the row copies are done by the whole warp, one pair
 // after another.

@@ -523,16 +523,16 @@ __global__ void __launch_bounds__(kPushThreads, 1) dispatch_push_kernel(const Pu
     }
     __syncthreads();
     if (s_ok) {
-      const int ppc = p.pairs_per_chunk;
       const int num_send = *p.num_send;
-      const int num_chunks = (num_send + ppc - 1) / ppc;
+      const int num_chunks = push_num_chunks(p, num_send);
       for (;;) {
         int chunk = 0;
         if (lane == 0) chunk = atomicAdd(p.work_counter, 1);
         chunk = __shfl_sync(0xffffffffu, chunk, 0);
         if (chunk >= num_chunks) break;
-        const int p0 = chunk * ppc;
-        push_chunk(p, s_tg, p0, min(p0 + ppc, num_send), lane);
+        int p0, p1;
+        push_chunk_range(p, num_send, chunk, p0, p1);
+        push_chunk(p, s_tg, p0, p1, lane);
       }
     }
   }

@@ -30,8 +30,14 @@ constexpr int BM = 128;          // rows per tile == pool tile_m
 constexpr int BK = 64;           // bf16 elements per k-block: one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kGemmWarps = 10;   // 0: TMA producer, 1: MMA issuer + TMEM owner, 2..9: epilogue
+// The kernels that consume tiles as a dispatch completes them (A and Y_bwd) carry one more warp whose lane 0 polls
+// the tile gates AHEAD of the TMA producer.  A gate poll is an acquire load at system scope, microseconds long
+// while NVLink traffic is landing; done by the producer itself it stalls the operand pipeline once per tile.
+constexpr bool has_gate_warp(int epi) { return epi == kEpiSwiglu || epi == kEpiDswiglu; }
+constexpr int base_warps(int epi) { return kGemmWarps + (has_gate_warp(epi) ? 1 : 0); }
 // extra warps of the fused variants; the dSwiGLU epilogue keeps two preact segments in registers, so it gets fewer
-constexpr int push_warps(int epi) { return epi == kEpiDswiglu ? 6 : 10; }
+// (Y_bwd: 16 warps x 128 registers, A: 20 warps x 96 registers fill the register file)
+constexpr int push_warps(int epi) { return epi == kEpiDswiglu ? 5 : 9; }
 constexpr int kMaxDevices = 64;  // per-device host-side tables (kernel attributes, no-alloc scratch address)
 constexpr int kEpiThreads = 256; // two threads per accumulator row: each takes half of the tile's columns
 
@@ -115,7 +121,7 @@ __device__ __forceinline__ bool epi_vote_any(bool pred) {
 }
 
 template <int BN, bool A_MN, bool B_MN, int EPI, bool PUSH>
-__global__ void __launch_bounds__((kGemmWarps + (PUSH ? push_warps(EPI) : 0)) * 32, 1)
+__global__ void __launch_bounds__((base_warps(EPI) + (PUSH ? push_warps(EPI) : 0)) * 32, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_o0, const __grid_constant__ CUtensorMap tmap_o1,
                     const GemmParams p, const PushParams pp) {
@@ -134,6 +140,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   int* s_flag = reinterpret_cast<int*>(tmem_slot + 1);     // epilogue broadcast word
   __shared__ PushTargets s_tg;
   __shared__ int s_push_ok;
+  __shared__ int s_gates_open;   // how many of this CTA's tiles have an open gate (-1: the gate warp gave up)
+  __shared__ int s_tiles_done;   // tiles whose epilogue finished (read by the time stamps only)
   __shared__ char* s_remote_out[kMaxRanks];
   __shared__ float* s_remote_dw[kMaxRanks];
 
@@ -142,6 +150,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int num_m = (p.mode == kVarlenM && p.num_m_tiles_dev != nullptr) ? min(*p.num_m_tiles_dev, p.num_m_tiles) : p.num_m_tiles;
   const int total_tiles = (p.mode == kVarlenM ? num_m : p.num_experts * p.num_m_tiles) * p.num_n_tiles;
   const unsigned long long budget = p.wait_budget_ns;
+  // Fused push, two ways of sharing the GPU.  Mixed (push_ctas == 0): every CTA multiplies and its extra warps push.
+  // Dedicated (push_ctas > 0): the last push_ctas CTAs only push, with all their warps, and the others only multiply.
+  // Remote stores that wait for NVLink credit back up in an SM's load/store path, where the epilogue warps of
+  // the same SM queue behind them: with the push on SMs of its own the GEMM runs at its stand-alone rate.
+  const int num_push_ctas = PUSH ? min(max(pp.push_ctas, 0), static_cast<int>(gridDim.x) - 1) : 0;
+  const int lin_stride = static_cast<int>(gridDim.x) - num_push_ctas;
+  const bool is_push_cta = PUSH && static_cast<int>(blockIdx.x) >= lin_stride;
+  const int first_lin = is_push_cta ? 0x7fffffff : static_cast<int>(blockIdx.x);
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_a);
@@ -151,13 +167,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     mbar_fence_init();
     if (blockIdx.x == 0 && p.started_flag != nullptr) atomicAdd(p.started_flag, 1);
     if (PUSH) s_push_ok = 1;
+    s_gates_open = 0;
+    s_tiles_done = 0;
+    if (p.timing != nullptr) {
+      long long* tm = p.timing + static_cast<size_t>(blockIdx.x) * kTimingCols;
+      tm[0] = static_cast<long long>(globaltimer_ns());
+      tm[1] = 0; tm[2] = 0; tm[3] = 0; tm[4] = 0; tm[5] = 0; tm[7] = 0;
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
     tmem_relinquish();
   }
   if (PUSH) {
-    if ((pp.flags & 1) && !pp.static_targets && blockIdx.x == 0 && warp == kGemmWarps && lane < pp.num_ranks)
+    if ((pp.flags & 1) && !pp.static_targets && blockIdx.x == 0 && warp == base_warps(EPI) && lane < pp.num_ranks)
       publish_record(pp.own, pp.peer_base, pp.ctl, pp.kind, pp.epoch, pp.rank, lane);
   }
   if ((EPI == kEpiScatter || EPI == kEpiDswiglu) && warp == 2 && lane < p.num_ranks) {
@@ -186,22 +209,64 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (is_push_cta) {
+    // ------------------------------------------------------------------ push-only CTA: every warp ships rows
+    if (pp.flags & 2) {
+      if (warp == 0 && lane < pp.num_ranks) {
+        const unsigned long long* rec = pp.static_targets
+            ? reinterpret_cast<const unsigned long long*>(&pp.own)
+            : fetch_record(pp.peer_base[pp.rank], pp.ctl, pp.kind, pp.epoch, lane,
+                           pp.wait_budget_ns, pp.status, kKernelDispatch, pp.rank);
+        if (rec == nullptr) s_push_ok = 0;
+        else resolve_push_targets(s_tg, lane, pp.peer_base[lane], rec);
+      }
+      __syncthreads();
+      if (s_push_ok) {
+        const int num_send = *pp.num_send;
+        const int num_chunks = push_num_chunks(pp, num_send);
+        if (p.timing != nullptr && threadIdx.x == 0)
+          p.timing[static_cast<size_t>(blockIdx.x) * kTimingCols + 4] = static_cast<long long>(globaltimer_ns());
+        for (;;) {
+          int chunk = 0;
+          if (lane == 0) chunk = atomicAdd(pp.work_counter, 1);
+          chunk = __shfl_sync(0xffffffffu, chunk, 0);
+          if (chunk >= num_chunks) break;
+          int p0, p1;
+          push_chunk_range(pp, num_send, chunk, p0, p1);
+          push_chunk(pp, s_tg, p0, p1, lane);
+        }
+        if (p.timing != nullptr && lane == 0)
+          atomicMax(reinterpret_cast<unsigned long long*>(p.timing + static_cast<size_t>(blockIdx.x) * kTimingCols + 5), globaltimer_ns());
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int stage = 0; uint32_t phase = 0; int issued = 0; bool ok = true;
-      for (int lin = blockIdx.x; lin < total_tiles && ok; lin += gridDim.x) {
+      int stage = 0; uint32_t phase = 0; int issued = 0; bool ok = true; int my_tile = 0;
+      for (int lin = first_lin; lin < total_tiles && ok; lin += lin_stride) {
         const TileCoord t = decode_tile(p, lin, num_m);
         if (p.mode == kVarlenM && p.arrival_count != nullptr) {
-          const int target = p.arrival_target[t.m_tile];
-          const int* cnt = p.arrival_count + t.m_tile;
-          // with one rank every writer of the counter is on this GPU: device scope is enough and cheaper
-          const bool local_only = p.num_ranks == 1;
-          if (!spin_until([&] { return (local_only ? ld_acquire_gpu(cnt) : ld_acquire_sys(cnt)) == target; }, budget, p.status)) {
-            report_failure(p.status, kStatusTimeoutTileGate, kKernelGemm, 0, p.rank, t.m_tile, target, ld_acquire_sys(cnt));
-            ok = false; break;
+          const unsigned long long gate_t0 = p.timing != nullptr ? globaltimer_ns() : 0ull;
+          bool open;
+          if constexpr (has_gate_warp(EPI)) {
+            // the gate warp polls the counters ahead of this thread and publishes how far it got
+            open = spin_until([&] { const int g = ld_acquire_cta_shared(&s_gates_open); return g < 0 || g > my_tile; }, budget, p.status) &&
+                   ld_acquire_cta_shared(&s_gates_open) > my_tile;
+          } else {
+            const int target = p.arrival_target[t.m_tile];
+            const int* cnt = p.arrival_count + t.m_tile;
+            const bool local_only = p.num_ranks == 1;
+            open = spin_until([&] { return (local_only ? ld_acquire_gpu(cnt) : ld_acquire_sys(cnt)) == target; }, budget, p.status);
+            if (!open) report_failure(p.status, kStatusTimeoutTileGate, kKernelGemm, 0, p.rank, t.m_tile, target, ld_acquire_sys(cnt));
           }
+          if (!open) { ok = false; break; }
           fence_proxy_async();   // rows were written through the generic proxy (possibly by a peer GPU)
+          if (p.timing != nullptr) {
+            long long* tm = p.timing + static_cast<size_t>(blockIdx.x) * kTimingCols;
+            tm[1] += static_cast<long long>(globaltimer_ns() - gate_t0);   // time the operand pipeline stood still for gates
+            tm[7] += 1;
+          }
+          ++my_tile;
         }
         for (int kb = 0; kb < t.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, budget, p.status)) {
@@ -247,7 +312,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // ------------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
     int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
-    for (int lin = blockIdx.x; lin < total_tiles && ok; lin += gridDim.x) {
+    for (int lin = first_lin; lin < total_tiles && ok; lin += lin_stride) {
       const TileCoord t = decode_tile(p, lin, num_m);
       if (t.k_blocks == 0) continue;   // empty expert: the epilogue writes zeros on its own
       // all 32 lanes wait; the outcome is made warp-uniform so that no lane leaves ahead of elect_one / __syncwarp
@@ -303,7 +368,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     constexpr int kChunksPerHalf = BN / 64;
     const uint32_t stg = smem_u32(epi_stage + (warp - 2) * Cfg::kEpiStageBytes);
     int acc = 0; uint32_t acc_phase = 0;
-    for (int lin = blockIdx.x; lin < total_tiles; lin += gridDim.x) {
+    for (int lin = first_lin; lin < total_tiles; lin += lin_stride) {
       const TileCoord t = decode_tile(p, lin, num_m);
       const bool empty = (t.k_blocks == 0);
       // Everything that does not need the accumulator is fetched while the tensor cores still work on this tile.
@@ -567,6 +632,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         mbar_arrive(&tmem_empty[acc]);
         acc ^= 1; if (acc == 0) acc_phase ^= 1;
       }
+      if (p.timing != nullptr && epi_tid == 0) *reinterpret_cast<volatile int*>(&s_tiles_done) += 1;
       if (EPI == kEpiDswiglu) {
         if (tok >= 0 && p.dl_dweight != nullptr) red_add_f32(p.dl_dweight + grow, dw_acc);
       }
@@ -598,10 +664,32 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     if (lane == 0) bulk_wait_all();     // every bulk store this warp issued has been performed
     if (p.tail.enabled) __threadfence_system();
+  } else if (has_gate_warp(EPI) && warp == kGemmWarps) {
+    // ------------------------------------------------------------------ gate warp: polls tile gates ahead of the producer
+    if (lane == 0 && p.mode == kVarlenM && p.arrival_count != nullptr) {
+      const bool local_only = p.num_ranks == 1;   // every writer of the counters is on this GPU: device scope is enough
+      int n = 0;
+      for (int lin = first_lin; lin < total_tiles; lin += lin_stride) {
+        const TileCoord t = decode_tile(p, lin, num_m);
+        const int target = p.arrival_target[t.m_tile];
+        const int* cnt = p.arrival_count + t.m_tile;
+        if (!spin_until([&] { return (local_only ? ld_acquire_gpu(cnt) : ld_acquire_sys(cnt)) == target; }, budget, p.status)) {
+          report_failure(p.status, kStatusTimeoutTileGate, kKernelGemm, 0, p.rank, t.m_tile, target, ld_acquire_sys(cnt));
+          st_release_cta_shared(&s_gates_open, -1);
+          break;
+        }
+        if (p.timing != nullptr) {
+          long long* tm = p.timing + static_cast<size_t>(blockIdx.x) * kTimingCols;
+          const long long now = static_cast<long long>(globaltimer_ns());
+          if (n == 0) tm[2] = now;
+        }
+        st_release_cta_shared(&s_gates_open, ++n);
+      }
+    }
   } else if (PUSH) {
-    // ------------------------------------------------------------------ dispatch push warps
-    if (pp.flags & 2) {
-      const int pw = warp - kGemmWarps;
+    // ------------------------------------------------------------------ dispatch push warps (mixed mode)
+    if ((pp.flags & 2) && num_push_ctas == 0) {
+      const int pw = warp - base_warps(EPI);
       if (pw == 0 && lane < pp.num_ranks) {
         const unsigned long long* rec = pp.static_targets
             ? reinterpret_cast<const unsigned long long*>(&pp.own)
@@ -612,16 +700,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
       asm volatile("bar.sync 2, %0;" :: "r"(push_warps(EPI) * 32) : "memory");
       if (s_push_ok && (pp.active_push_warps <= 0 || pw < pp.active_push_warps)) {
-        const int ppc = pp.pairs_per_chunk;
         const int num_send = *pp.num_send;
-        const int num_chunks = (num_send + ppc - 1) / ppc;
+        const int num_chunks = push_num_chunks(pp, num_send);
+        if (p.timing != nullptr && pw == 0 && lane == 0)
+          p.timing[static_cast<size_t>(blockIdx.x) * kTimingCols + 4] = static_cast<long long>(globaltimer_ns());
         for (;;) {
           int chunk = 0;
           if (lane == 0) chunk = atomicAdd(pp.work_counter, 1);
           chunk = __shfl_sync(0xffffffffu, chunk, 0);
           if (chunk >= num_chunks) break;
-          const int p0 = chunk * ppc;
-          push_chunk(pp, s_tg, p0, min(p0 + ppc, num_send), lane);
+          int p0, p1;
+          push_chunk_range(pp, num_send, chunk, p0, p1);
+          push_chunk(pp, s_tg, p0, p1, lane);
+        }
+        if (p.timing != nullptr && lane == 0) {
+          long long* tm = p.timing + static_cast<size_t>(blockIdx.x) * kTimingCols;
+          const unsigned long long now = globaltimer_ns();
+          if (atomicMax(reinterpret_cast<unsigned long long*>(tm + 5), now) < now)   // this warp is the CTA's last one so far
+            tm[3] = *reinterpret_cast<volatile int*>(&s_tiles_done);
         }
       }
     }
@@ -630,6 +726,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   // ---------------------------------------------------------------------- teardown
   tc_fence_before_sync();
   __syncthreads();
+  if (p.timing != nullptr && threadIdx.x == 0)
+    p.timing[static_cast<size_t>(blockIdx.x) * kTimingCols + 6] = static_cast<long long>(globaltimer_ns());
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
@@ -675,7 +773,7 @@ static cudaError_t launch_instance(const GemmParams& p, const CUtensorMap& ta, c
     if (e != cudaSuccess) return e;
     configured[dev].store(true, std::memory_order_release);
   }
-  const int threads = (kGemmWarps + (PUSH ? push_warps(EPI) : 0)) * 32;
+  const int threads = (base_warps(EPI) + (PUSH ? push_warps(EPI) : 0)) * 32;
   kernel<<<num_ctas, threads, smem, stream>>>(ta, tb, to0, to1, p, pp);
   return cudaSuccess;
 }

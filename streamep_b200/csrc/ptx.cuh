@@ -86,6 +86,15 @@ __device__ __forceinline__ void red_relaxed_sys_add_f32(float* p, float v) {
 __device__ __forceinline__ void red_add_f32(float* p, float v) {
   asm volatile("red.global.add.f32 [%0], %1;" :: "l"(p), "f"(v) : "memory");
 }
+// CTA-scope hand-over of a word in shared memory between two warps of a CTA
+__device__ __forceinline__ int ld_acquire_cta_shared(const int* p) {
+  int v;
+  asm volatile("ld.acquire.cta.shared::cta.s32 %0, [%1];" : "=r"(v) : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(p))) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_cta_shared(int* p, int v) {
+  asm volatile("st.release.cta.shared::cta.s32 [%0], %1;" :: "r"(static_cast<uint32_t>(__cvta_generic_to_shared(p))), "r"(v) : "memory");
+}
 __device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
 // Orders generic-proxy accesses (plain ld/st, also the ones a peer GPU made and this thread

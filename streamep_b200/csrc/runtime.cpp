@@ -327,6 +327,12 @@ class Runtime {
     // the tiles it touched.  Small chunks let remote tiles complete progressively; with one rank only the
     // signalling overhead matters and larger chunks measured faster.
     pairs_per_chunk_ = num_ranks == 1 ? 16 : 8;
+    // Several ranks (measured on 8 GPUs with the kernels' per-CTA time stamps): remote stores that wait for NVLink
+    // credit back up in an SM's load/store path and starve the epilogue warps of the same SM, so a push spread over
+    // all SMs nearly serialises with the GEMM.  28 SMs that only push (about 20 GB/s of remote stores each) keep the
+    // links busy while the other SMs multiply at their stand-alone rate.  The send list is walked tile by tile
+    // (order 1) and its first chunks are small, so the consumers' first tiles complete after ~30 us instead of ~130.
+    if (num_ranks > 1) { push_ctas_ = 28; push_order_ = 1; head_pairs_per_chunk_ = 2; head_chunks_ = 3000; }
     ctl_ = make_control_layout(num_ranks, num_channels, num_experts_cap);
     arena_bytes_ = static_cast<size_t>(arena_bytes) + ctl_.total_bytes;
     arena_bytes_ = (arena_bytes_ + (2u << 20) - 1) / (2u << 20) * (2u << 20);
@@ -422,8 +428,25 @@ class Runtime {
   // kernels that synchronise at system scope, which measured markedly slower while a PCIe copy was in flight.
   void mark_local_phase() { local_phase_ = std::make_shared<EventHandle>(stream()); }
   std::optional<EventHandle> local_phase_event() const { return local_phase_ ? std::optional<EventHandle>(*local_phase_) : std::nullopt; }
+  // Per-CTA time stamps of the GEMM kernels (see GemmParams::timing).  Returns the tensor the launches that follow
+  // fill: int64 [10, num_sms, 8], first index = epilogue kind (0 store, 1 SwiGLU, 2 scatter, 3 dSwiGLU, 4 fp32 store),
+  // + 5 for the launches with a fused push.  Each launch overwrites the rows of its kind.  `on = false` stops it.
+  at::Tensor set_kernel_timing(bool on) {
+    if (!on) { timing_ = at::Tensor(); return timing_; }
+    timing_ = at::zeros({10, num_sms(), kTimingCols}, at::TensorOptions().dtype(at::kLong).device(at::kCUDA, device_));
+    return timing_;
+  }
   void set_push_order(int n) { SEP_ASSERT(n == 0 || n == 1, "push order must be 0 or 1"); push_order_ = n; }
   void set_active_push_warps(int n) { SEP_ASSERT(n >= 0 && n <= 16, "active push warps must be 0..16"); active_push_warps_ = n; }
+  // Fused dispatch + GEMM kernels: `n` CTAs only push (all their warps) and the rest only multiply; 0 = every CTA
+  // does both (the default with one rank, where the push is a local copy).
+  void set_push_ctas(int n) { SEP_ASSERT(n >= 0 && n < 128, "push CTAs out of range"); push_ctas_ = n; }
+  int get_push_ctas() const { return push_ctas_; }
+  // The first `chunks` chunks of every push carry `pairs` pairs each (0 chunks = off).
+  void set_push_head(int pairs, int chunks) {
+    SEP_ASSERT(pairs >= 1 && pairs <= 32 && chunks >= 0, "head chunks: 1..32 pairs, a non-negative count");
+    head_pairs_per_chunk_ = pairs; head_chunks_ = chunks;
+  }
   void set_pairs_per_chunk(int n) { SEP_ASSERT(n >= 1 && n <= 32, "pairs per chunk must be 1..32"); pairs_per_chunk_ = n; }
   // Blocks whose tensors died count as free here even while the arena still holds them back for queued work.
   int64_t arena_bytes_in_use() const { return static_cast<int64_t>(arena_->bytes_in_use()); }
@@ -827,6 +850,8 @@ class Runtime {
     p.num_ranks = num_ranks_; p.rank = rank_; p.tile_m = st.tile_m;
     p.is_grads = is_grads ? 1 : 0; p.kind = kind; p.epoch = epoch; p.flags = flags;
     p.pairs_per_chunk = pairs_per_chunk_; p.active_push_warps = active_push_warps_;
+    p.head_pairs_per_chunk = head_pairs_per_chunk_; p.head_chunks = head_chunks_;
+    p.push_ctas = push_ctas_;
     fill_peers(p.peer_base); p.ctl = ctl_; p.own = rec;
     p.static_targets = st.region_id >= 0 ? 1 : 0;   // (a backward along a capacity-mode forward uses fixed regions too)
     p.own_arrival_count = own_count; p.own_arrival_target = st.pool_arrival_target.data_ptr<int>();
@@ -1034,6 +1059,10 @@ class Runtime {
     if (a.k_remaining.has_value()) p.k_remaining = a.k_remaining->data_ptr<int>();
     if (a.done_per_token.has_value()) p.done_per_token = reinterpret_cast<long long*>(a.done_per_token->data_ptr<int64_t>());
     p.seq = a.seq; p.num_topk = a.num_topk;
+    if (timing_.defined()) {   // one block of rows per kind of launch: epilogue index, +5 when a push is fused in
+      const int kind = a.epilogue + ((a.fused_push || a.fused_push_grads) ? 5 : 0);
+      p.timing = reinterpret_cast<long long*>(timing_.data_ptr<int64_t>()) + static_cast<int64_t>(kind) * num_sms() * kTimingCols;
+    }
     p.num_ranks = num_ranks_; fill_peers(p.peer_base); p.ctl = ctl_;
     auto set_ref = [](RemoteRef& r, const std::vector<int>& v) {
       if (v.empty()) return;
@@ -1099,6 +1128,7 @@ class Runtime {
       ppp = &pp;
     }
     if (ppp == nullptr) n_ctas = static_cast<int>(std::min<int64_t>(n_ctas, std::max<int64_t>(total, 1)));
+    if (n_ctas > num_sms()) p.timing = nullptr;   // the stamp tensor has one row per SM
     ++launches_;
     cudaError_t setup_error = cudaSuccess;
     const bool launched = launch_grouped_gemm(p, &ta, &tb, have_o0 ? &to0 : nullptr, have_o1 ? &to1 : nullptr, ppp, n_ctas,
@@ -1391,11 +1421,14 @@ class Runtime {
   int epochs_[kNumKinds];
   int64_t launches_ = 0;
   int pairs_per_chunk_ = 8;
+  int head_pairs_per_chunk_ = 2, head_chunks_ = 0;
+  int push_ctas_ = 0;
   int active_push_warps_ = 0;
   bool router_on_tensor_cores_ = true;
   at::Tensor router_tiles_;            // zeros: every M tile of the router GEMM belongs to "expert" 0
   int push_order_ = 0;
   std::shared_ptr<EventHandle> local_phase_;
+  at::Tensor timing_;
   int gate_issued_[8];
   bool available_ = false, destroyed_ = false;
 };
@@ -1527,7 +1560,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_property_readonly("num_ranks", &Runtime::num_ranks)
       .def_property_readonly("num_channels", &Runtime::num_channels)
       .def("launch_count", &Runtime::launch_count)
+      .def("set_kernel_timing", &Runtime::set_kernel_timing)
       .def("set_pairs_per_chunk", &Runtime::set_pairs_per_chunk)
+      .def("set_push_head", &Runtime::set_push_head)
+      .def("set_push_ctas", &Runtime::set_push_ctas)
+      .def("get_push_ctas", &Runtime::get_push_ctas)
       .def("set_active_push_warps", &Runtime::set_active_push_warps)
       .def("set_push_order", &Runtime::set_push_order)
       .def("set_router_on_tensor_cores", &Runtime::set_router_on_tensor_cores)
