@@ -197,6 +197,9 @@ class Buffer:
         ctas = os.environ.get("STREAM_EP_PUSH_CTAS")
         if ctas:
             self.runtime.set_push_ctas(int(ctas))
+        bulk = os.environ.get("STREAM_EP_BULK_PUSH")
+        if bulk:
+            self.runtime.set_bulk_push(bulk not in ("0", "false", "False"))
 
     # ------------------------------------------------------------------ lifecycle
     def destroy(self):

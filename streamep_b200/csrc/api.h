@@ -159,6 +159,7 @@ struct PushParams {
   int head_pairs_per_chunk;      // the first `head_chunks` chunks are this small, so that the first tiles complete early
   int head_chunks;               // (0 = every chunk has pairs_per_chunk pairs)
   int active_push_warps;         // push warps per CTA of the fused kernels that take chunks (0 = all)
+  int bulk_push;                 // push-only CTAs copy rows through the bulk-copy engine (shared-memory ring) instead of ld/st
   int push_ctas;                 // fused kernels: this many CTAs only push and the others only multiply (0 = every CTA does both)
   void* peer_base[kMaxRanks];
   ControlLayout ctl;

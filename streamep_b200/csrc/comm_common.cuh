@@ -125,9 +125,19 @@ __device__ __forceinline__ void push_chunk_range(const PushParams& p, int num_se
 
 // One warp ships the pairs at positions [pos_begin, pos_end) of the send list (at most 32).  Lane j
 // owns pair j of the chunk for the scalar work; the row copies are done by the whole warp, one pair
-// after another.
+// after another (plain 16-byte loads and peer stores), or - `ring` != 0, push-only CTAs - by lane 0 through the
+// bulk-copy engine: row pieces of up to kPushPieceBytes are loaded into a two-slot shared-memory ring and stored
+// from there into the owner's pool, the next piece's load in flight while the current one is stored.
+constexpr uint32_t kPushPieceBytes = 4096;
+struct PushRing {
+  uint32_t smem;        // shared-memory address of this warp's two slots (2 x kPushPieceBytes, 128-byte aligned), 0 = none
+  uint64_t* bar;        // two mbarriers of this warp (count 1), initialised by the caller
+  uint32_t phase;       // bit s = parity the next wait on slot s expects
+  bool ok;              // false after a bounded wait on a load gave up
+};
+
 __device__ __forceinline__ void push_chunk(const PushParams& p, const PushTargets& tg, int pos_begin,
-                                           int pos_end, int lane) {
+                                           int pos_end, int lane, PushRing* ring = nullptr) {
   const int K = p.num_topk, R = p.num_ranks;
   const int e_local = p.num_experts / R;
   const size_t row_bytes = static_cast<size_t>(p.hidden) * 2;
@@ -142,6 +152,66 @@ __device__ __forceinline__ void push_chunk(const PushParams& p, const PushTarget
     slot = p.pair_slot[pair];
     dst = static_cast<int>(e / e_local);
   }
+  if (ring != nullptr && ring->smem != 0) {
+    const int pieces = static_cast<int>((row_bytes + kPushPieceBytes - 1) / kPushPieceBytes);
+    const int total = n * pieces;
+    const char* src_next = nullptr; char* dst_next = nullptr; uint32_t bytes_next = 0;
+    auto piece = [&](int i, const char*& src, char*& dstp, uint32_t& bytes) {
+      const int j = i / pieces, q = i - j * pieces;
+      const int tj = __shfl_sync(0xffffffffu, t, j);
+      const int sj = __shfl_sync(0xffffffffu, slot, j);
+      const int dj = __shfl_sync(0xffffffffu, dst, j);
+      const size_t off = static_cast<size_t>(q) * kPushPieceBytes;
+      src = static_cast<const char*>(p.x) + static_cast<size_t>(tj) * row_bytes + off;
+      dstp = tg.pool[dj] + static_cast<size_t>(sj) * row_bytes + off;
+      bytes = static_cast<uint32_t>(min(static_cast<size_t>(kPushPieceBytes), row_bytes - off));
+    };
+    if (total > 0) {
+      piece(0, src_next, dst_next, bytes_next);
+      if (lane == 0) {
+        bulk_wait_read();                                  // both slots are free again (stores of the previous chunk)
+        mbar_arrive_expect_tx(&ring->bar[0], bytes_next);
+        bulk_load_1d(ring->smem, src_next, bytes_next, &ring->bar[0]);
+      }
+    }
+    for (int i = 0; i < total; ++i) {
+      const int s = i & 1;
+      char* dst_cur = dst_next; const uint32_t bytes_cur = bytes_next;
+      if (i + 1 < total) piece(i + 1, src_next, dst_next, bytes_next);   // (shuffles: all lanes)
+      int ok = 1;
+      if (lane == 0) {
+        if (i + 1 < total) {
+          bulk_wait_read();                                // the other slot's store (piece i - 1) has read its data
+          mbar_arrive_expect_tx(&ring->bar[s ^ 1], bytes_next);
+          bulk_load_1d(ring->smem + (s ^ 1) * kPushPieceBytes, src_next, bytes_next, &ring->bar[s ^ 1]);
+        }
+        if (mbar_wait(&ring->bar[s], (ring->phase >> s) & 1u, p.wait_budget_ns, p.status)) {
+          ring->phase ^= 1u << s;
+          bulk_store_1d(dst_cur, ring->smem + s * kPushPieceBytes, bytes_cur);
+          bulk_commit();
+        } else {
+          // give up: report, let the load that is still in flight land (bounded), and ship nothing more
+          report_failure(p.status, kStatusTimeoutPipeline, p.is_grads ? kKernelDispatchGrads : kKernelDispatch, 3, p.rank, i, 0, 0);
+          const unsigned long long t0 = globaltimer_ns();
+          while (!mbar_try_wait(&ring->bar[s], (ring->phase >> s) & 1u) && globaltimer_ns() - t0 < 2000000ull) {}
+          if (i + 1 < total)
+            while (!mbar_try_wait(&ring->bar[s ^ 1], (ring->phase >> (s ^ 1)) & 1u) && globaltimer_ns() - t0 < 4000000ull) {}
+          ring->ok = false;
+          ok = 0;
+        }
+      }
+      if (!__shfl_sync(0xffffffffu, ok, 0)) {               // warp-uniform exit; the chunk's tiles are NOT released
+        if (lane == 0) bulk_wait_all();
+        __syncwarp();
+        return;
+      }
+    }
+    if (lane == 0) {
+      bulk_wait_all();          // every store of this chunk has been performed ...
+      fence_proxy_async();      // ... and is ordered before the generic-proxy release below
+    }
+    __syncwarp();
+  } else {
   for (int j = 0; j < n; ++j) {
     const int tj = __shfl_sync(0xffffffffu, t, j);
     const int sj = __shfl_sync(0xffffffffu, slot, j);
@@ -168,6 +238,7 @@ __device__ __forceinline__ void push_chunk(const PushParams& p, const PushTarget
     }
     for (; v < vec_per_row; v += 32)
       st_na_v4(dst_row + static_cast<size_t>(v) * 16, ld_nc_v4(src_row + static_cast<size_t>(v) * 16));
+  }
   }
   if (!p.is_grads && lane < n) {
     const int r = p.send_recv_token[static_cast<size_t>(t) * R + dst];

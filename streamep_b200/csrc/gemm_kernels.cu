@@ -142,6 +142,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   __shared__ int s_push_ok;
   __shared__ int s_gates_open;   // how many of this CTA's tiles have an open gate (-1: the gate warp gave up)
   __shared__ int s_tiles_done;   // tiles whose epilogue finished (read by the time stamps only)
+  __shared__ uint64_t s_push_bar[32][2];   // push-only CTAs: two bulk-load barriers per warp
   __shared__ char* s_remote_out[kMaxRanks];
   __shared__ float* s_remote_dw[kMaxRanks];
 
@@ -220,6 +221,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (rec == nullptr) s_push_ok = 0;
         else resolve_push_targets(s_tg, lane, pp.peer_base[lane], rec);
       }
+      // The operand ring of the GEMM is unused here: every warp takes two 4 KB slots of it for bulk copies
+      // (global -> shared -> owner's pool through the copy engine, see push_chunk).
+      PushRing ring{};
+      ring.bar = s_push_bar[warp];
+      ring.ok = true;
+      if (pp.bulk_push && (warp + 1) * 2 * static_cast<int>(kPushPieceBytes) <= Cfg::kStages * Cfg::kStageBytes) {
+        ring.smem = smem_u32(stage_base) + warp * 2 * kPushPieceBytes;
+        if (lane == 0) { mbar_init(&ring.bar[0], 1); mbar_init(&ring.bar[1], 1); mbar_fence_init(); }
+      }
       __syncthreads();
       if (s_push_ok) {
         const int num_send = *pp.num_send;
@@ -228,12 +238,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           p.timing[static_cast<size_t>(blockIdx.x) * kTimingCols + 4] = static_cast<long long>(globaltimer_ns());
         for (;;) {
           int chunk = 0;
-          if (lane == 0) chunk = atomicAdd(pp.work_counter, 1);
+          if (lane == 0) chunk = ring.ok ? atomicAdd(pp.work_counter, 1) : 0x7fffffff;
           chunk = __shfl_sync(0xffffffffu, chunk, 0);
           if (chunk >= num_chunks) break;
           int p0, p1;
           push_chunk_range(pp, num_send, chunk, p0, p1);
-          push_chunk(pp, s_tg, p0, p1, lane);
+          push_chunk(pp, s_tg, p0, p1, lane, &ring);
         }
         if (p.timing != nullptr && lane == 0)
           atomicMax(reinterpret_cast<unsigned long long*>(p.timing + static_cast<size_t>(blockIdx.x) * kTimingCols + 5), globaltimer_ns());

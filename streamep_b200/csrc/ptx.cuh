@@ -226,6 +226,18 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, ui
       :: "r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
 }
 
+// Untiled bulk copies (both addresses 16-byte aligned, size a multiple of 16 bytes; no multicast).
+// global -> shared, completion counted in bytes on an mbarrier of this CTA:
+__device__ __forceinline__ void bulk_load_1d(uint32_t smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :: "r"(smem_dst), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// shared -> global (this GPU's memory or a peer's), tracked by bulk async-groups:
+__device__ __forceinline__ void bulk_store_1d(void* gmem_dst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               :: "l"(gmem_dst), "r"(smem_src), "r"(bytes) : "memory");
+}
+
 // Bulk tensor store shared -> global (clipped at the tensor's bounds), tracked by bulk async-groups.
 __device__ __forceinline__ void tma_store_3d(const void* tmap, const void* smem_src, int x, int y, int z) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"

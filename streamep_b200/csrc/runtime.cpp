@@ -327,12 +327,15 @@ class Runtime {
     // the tiles it touched.  Small chunks let remote tiles complete progressively; with one rank only the
     // signalling overhead matters and larger chunks measured faster.
     pairs_per_chunk_ = num_ranks == 1 ? 16 : 8;
-    // Several ranks (measured on 8 GPUs with the kernels' per-CTA time stamps): remote stores that wait for NVLink
-    // credit back up in an SM's load/store path and starve the epilogue warps of the same SM, so a push spread over
-    // all SMs nearly serialises with the GEMM.  28 SMs that only push (about 20 GB/s of remote stores each) keep the
-    // links busy while the other SMs multiply at their stand-alone rate.  The send list is walked tile by tile
-    // (order 1) and its first chunks are small, so the consumers' first tiles complete after ~30 us instead of ~130.
-    if (num_ranks > 1) { push_ctas_ = 28; push_order_ = 1; head_pairs_per_chunk_ = 2; head_chunks_ = 3000; }
+    // Several ranks (measured with the kernels' per-CTA time stamps): remote stores that wait for NVLink credit back
+    // up in an SM's load/store path and starve the epilogue warps of the same SM, so a push spread over all SMs
+    // slows the GEMM to a third while it lasts.  On 8 ranks, 28 SMs that only push (about 20 GB/s each) keep the
+    // links busy while the other 120 multiply at their stand-alone rate (dispatch (+) GEMM-A 680 -> 570-590 us,
+    // dispatch_grads (+) GEMM-Y_bwd 510 -> 435-460 us); on 2 and 4 ranks, where less of the push is remote, the
+    // two ways measured the same and every CTA keeps doing both.  The send list is walked tile by tile (order 1)
+    // and its first chunks are small: the consumers' first tiles complete after ~30 us instead of ~130.
+    if (num_ranks > 1) { push_order_ = 1; head_pairs_per_chunk_ = 2; head_chunks_ = 3000; }
+    if (num_ranks > 4) push_ctas_ = 28;
     ctl_ = make_control_layout(num_ranks, num_channels, num_experts_cap);
     arena_bytes_ = static_cast<size_t>(arena_bytes) + ctl_.total_bytes;
     arena_bytes_ = (arena_bytes_ + (2u << 20) - 1) / (2u << 20) * (2u << 20);
@@ -442,6 +445,8 @@ class Runtime {
   // does both (the default with one rank, where the push is a local copy).
   void set_push_ctas(int n) { SEP_ASSERT(n >= 0 && n < 128, "push CTAs out of range"); push_ctas_ = n; }
   int get_push_ctas() const { return push_ctas_; }
+  // Push-only CTAs move rows with the bulk-copy engine (global -> shared -> owner's pool) instead of loads and stores.
+  void set_bulk_push(bool on) { bulk_push_ = on; }
   // The first `chunks` chunks of every push carry `pairs` pairs each (0 chunks = off).
   void set_push_head(int pairs, int chunks) {
     SEP_ASSERT(pairs >= 1 && pairs <= 32 && chunks >= 0, "head chunks: 1..32 pairs, a non-negative count");
@@ -851,7 +856,7 @@ class Runtime {
     p.is_grads = is_grads ? 1 : 0; p.kind = kind; p.epoch = epoch; p.flags = flags;
     p.pairs_per_chunk = pairs_per_chunk_; p.active_push_warps = active_push_warps_;
     p.head_pairs_per_chunk = head_pairs_per_chunk_; p.head_chunks = head_chunks_;
-    p.push_ctas = push_ctas_;
+    p.push_ctas = push_ctas_; p.bulk_push = bulk_push_ ? 1 : 0;
     fill_peers(p.peer_base); p.ctl = ctl_; p.own = rec;
     p.static_targets = st.region_id >= 0 ? 1 : 0;   // (a backward along a capacity-mode forward uses fixed regions too)
     p.own_arrival_count = own_count; p.own_arrival_target = st.pool_arrival_target.data_ptr<int>();
@@ -1423,6 +1428,7 @@ class Runtime {
   int pairs_per_chunk_ = 8;
   int head_pairs_per_chunk_ = 2, head_chunks_ = 0;
   int push_ctas_ = 0;
+  bool bulk_push_ = false;
   int active_push_warps_ = 0;
   bool router_on_tensor_cores_ = true;
   at::Tensor router_tiles_;            // zeros: every M tile of the router GEMM belongs to "expert" 0
@@ -1565,6 +1571,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_push_head", &Runtime::set_push_head)
       .def("set_push_ctas", &Runtime::set_push_ctas)
       .def("get_push_ctas", &Runtime::get_push_ctas)
+      .def("set_bulk_push", &Runtime::set_bulk_push)
       .def("set_active_push_warps", &Runtime::set_active_push_warps)
       .def("set_push_order", &Runtime::set_push_order)
       .def("set_router_on_tensor_cores", &Runtime::set_router_on_tensor_cores)

@@ -137,10 +137,16 @@ def main():
     if args.out and rank == 0:
         os.makedirs(args.out, exist_ok=True)
         handler = torch.profiler.tensorboard_trace_handler(args.out)
-    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU], on_trace_ready=handler) as prof:
-        for _ in range(args.steps):
+    # two steps inside the profiler are thrown away: starting it takes a different time on every rank, and a rank
+    # that is ahead would book that difference as time inside its first kernel that waits for peers
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU], on_trace_ready=handler,
+                 schedule=torch.profiler.schedule(wait=1, warmup=1, active=args.steps)) as prof:
+        for i in range(args.steps + 2):
+            if i == 2:
+                sync()
             step()
-        torch.cuda.synchronize()
+            torch.cuda.synchronize()
+            prof.step()
     sync()
     buf.check_status()
     if rank == 0:
