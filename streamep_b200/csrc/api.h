@@ -323,6 +323,13 @@ struct GemmParams {
   int rank;
   StatusBlock* status;
   unsigned long long wait_budget_ns;
+  // VarlenK, optional second problem in the same launch (dW1 and dW2 together: one tail instead of two) and dynamic
+  // tile claim.  Tiles of problem 2 follow those of problem 1 in the linear order; its operands, output and sizes:
+  int N2, M_out2, num_m_tiles2, num_n_tiles2;      // num_m_tiles2 == 0: no second problem
+  // tile_counter != null: CTAs claim tiles with atomicAdd(tile_counter) instead of striding by the grid size, so
+  // tiles of unequal length (experts of unequal row counts) and the last wave balance out.  Two ints, zero on
+  // entry, reset by the kernel: [0] next tile, [1] CTAs done.
+  int* tile_counter;
   // Optional per-CTA time stamps, [gridDim.x][kTimingCols] int64 of %globaltimer nanoseconds (null = off):
   // 0 kernel start, 1 ns the operand pipeline stood still for tile gates, 2 first tile ready, 3 tiles this CTA had
   // finished when its push ended, 4 first push chunk
@@ -337,9 +344,10 @@ constexpr int kTimingCols = 8;
 // Returns false, launching nothing, when no kernel instance exists for the mode / layout / epilogue combination.
 // `setup_error` (optional) receives the error of the per-device kernel set-up (shared-memory attribute); when it is
 // not cudaSuccess nothing was launched either.
+// `maps2`: three more 128-byte maps (A, B, output) of the second VarlenK problem, or null.
 bool launch_grouped_gemm(const GemmParams& p, const void* tmap_a, const void* tmap_b, const void* tmap_o0,
                          const void* tmap_o1, const PushParams* fused_push, int num_ctas, cudaStream_t stream,
-                         cudaError_t* setup_error = nullptr);
+                         cudaError_t* setup_error = nullptr, const void* maps2 = nullptr);
 size_t grouped_gemm_smem_bytes(int block_n);
 
 }  // namespace sep

@@ -39,6 +39,7 @@ constexpr int base_warps(int epi) { return kGemmWarps + (has_gate_warp(epi) ? 1 
 // (Y_bwd: 16 warps x 128 registers, A: 20 warps x 96 registers fill the register file)
 constexpr int push_warps(int epi) { return epi == kEpiDswiglu ? 5 : 9; }
 constexpr int kMaxDevices = 64;  // per-device host-side tables (kernel attributes, no-alloc scratch address)
+constexpr int kTileQueue = 8;    // dynamic tile claim: tiles the TMA thread may be ahead of the epilogue
 constexpr int kEpiThreads = 256; // two threads per accumulator row: each takes half of the tile's columns
 
 template <int BN> struct GemmCfg {
@@ -56,7 +57,10 @@ size_t grouped_gemm_smem_bytes(int block_n) {
   return block_n == 256 ? GemmCfg<256>::kSmemBytes : GemmCfg<128>::kSmemBytes;
 }
 
+struct SecondMaps { CUtensorMap a, b, o; };   // operands and output of the second VarlenK problem
+
 struct TileCoord {
+  int prob;        // VarlenK: 0 / 1 = first / second problem of the launch
   int m_tile, n_tile, expert;
   int row0;        // first row of A (VarlenM: m_tile * BM; VarlenK: first pool row of the expert)
   int k_blocks;    // number of BK blocks to accumulate
@@ -81,6 +85,7 @@ __device__ __forceinline__ void band_decode(int lin, int num_m, int num_n, int& 
 // `num_m`: live number of M tiles (VarlenM; may come from device memory), ignored for VarlenK.
 __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int lin, int num_m) {
   TileCoord t;
+  t.prob = 0;
   if (p.mode == kVarlenM) {
     band_decode(lin, num_m, p.num_n_tiles, t.m_tile, t.n_tile);
     t.expert = p.tile_id_to_expert[t.m_tile];
@@ -88,9 +93,12 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int lin, i
     t.k_blocks = (p.K + BK - 1) / BK;
     t.k_tail = 0;
   } else {
-    const int per_e = p.num_m_tiles * p.num_n_tiles;
+    int nm = p.num_m_tiles, nn = p.num_n_tiles;
+    const int first = p.num_experts * nm * nn;
+    if (lin >= first) { t.prob = 1; lin -= first; nm = p.num_m_tiles2; nn = p.num_n_tiles2; }
+    const int per_e = nm * nn;
     t.expert = lin / per_e;
-    band_decode(lin - t.expert * per_e, p.num_m_tiles, p.num_n_tiles, t.m_tile, t.n_tile);
+    band_decode(lin - t.expert * per_e, nm, nn, t.m_tile, t.n_tile);
     t.row0 = p.expert_pool_block_offset[t.expert] * BM;
     const int len = p.expert_frequency[t.expert];
     t.k_blocks = (len + BK - 1) / BK;
@@ -124,7 +132,7 @@ template <int BN, bool A_MN, bool B_MN, int EPI, bool PUSH>
 __global__ void __launch_bounds__((base_warps(EPI) + (PUSH ? push_warps(EPI) : 0)) * 32, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_o0, const __grid_constant__ CUtensorMap tmap_o1,
-                    const GemmParams p, const PushParams pp) {
+                    const GemmParams p, const PushParams pp, const __grid_constant__ SecondMaps maps2) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ unsigned char smem_dyn[];
   // 128-byte swizzle atoms are 1024 bytes: align the operand ring accordingly.
@@ -143,13 +151,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   __shared__ int s_gates_open;   // how many of this CTA's tiles have an open gate (-1: the gate warp gave up)
   __shared__ int s_tiles_done;   // tiles whose epilogue finished (read by the time stamps only)
   __shared__ uint64_t s_push_bar[32][2];   // push-only CTAs: two bulk-load barriers per warp
+  __shared__ int s_q[kTileQueue];          // dynamic tile claim: claimed tile ids ...
+  __shared__ int s_q_head, s_q_tail;       // ... how many were claimed, how many the epilogue has finished
   __shared__ char* s_remote_out[kMaxRanks];
   __shared__ float* s_remote_dw[kMaxRanks];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Capacity mode keeps the live tile count in device memory (written by the metadata kernel earlier in the stream).
   const int num_m = (p.mode == kVarlenM && p.num_m_tiles_dev != nullptr) ? min(*p.num_m_tiles_dev, p.num_m_tiles) : p.num_m_tiles;
-  const int total_tiles = (p.mode == kVarlenM ? num_m : p.num_experts * p.num_m_tiles) * p.num_n_tiles;
+  const int total_tiles = p.mode == kVarlenM ? num_m * p.num_n_tiles
+                                             : p.num_experts * (p.num_m_tiles * p.num_n_tiles + p.num_m_tiles2 * p.num_n_tiles2);
+  // Tile feed.  Static: CTA b takes tiles b, b + stride, ...  Dynamic (VarlenK with a counter): the TMA thread claims
+  // the next tile and hands it to the MMA and epilogue warps through a small queue in shared memory.
+  const bool dyn = p.mode == kVarlenK && p.tile_counter != nullptr;
   const unsigned long long budget = p.wait_budget_ns;
   // Fused push, two ways of sharing the GPU.  Mixed (push_ctas == 0): every CTA multiplies and its extra warps push.
   // Dedicated (push_ctas > 0): the last push_ctas CTAs only push, with all their warps, and the others only multiply.
@@ -170,6 +184,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     if (PUSH) s_push_ok = 1;
     s_gates_open = 0;
     s_tiles_done = 0;
+    s_q_head = 0; s_q_tail = 0;
     if (p.timing != nullptr) {
       long long* tm = p.timing + static_cast<size_t>(blockIdx.x) * kTimingCols;
       tm[0] = static_cast<long long>(globaltimer_ns());
@@ -253,8 +268,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; int issued = 0; bool ok = true; int my_tile = 0;
-      for (int lin = first_lin; lin < total_tiles && ok; lin += lin_stride) {
+      for (int it = 0; ok; ++it) {
+        int lin;
+        if (dyn) {
+          // claim the next tile; wait for a free queue entry first (the epilogue is at most kTileQueue tiles behind)
+          if (!spin_until([&] { return it - ld_acquire_cta_shared(&s_q_tail) < kTileQueue; }, budget, p.status)) {
+            report_failure(p.status, kStatusTimeoutPipeline, kKernelGemm, 4, p.rank, it, 0, 0);
+            ok = false;
+            lin = total_tiles;
+          } else {
+            lin = atomicAdd(p.tile_counter, 1);
+          }
+          s_q[it % kTileQueue] = lin;
+          st_release_cta_shared(&s_q_head, it + 1);
+        } else {
+          lin = first_lin + it * lin_stride;
+        }
+        if (lin >= total_tiles || lin < 0) break;
         const TileCoord t = decode_tile(p, lin, num_m);
+        const CUtensorMap* ta = t.prob ? &maps2.a : &tmap_a;
+        const CUtensorMap* tb = t.prob ? &maps2.b : &tmap_b;
         if (p.mode == kVarlenM && p.arrival_count != nullptr) {
           const unsigned long long gate_t0 = p.timing != nullptr ? globaltimer_ns() : 0ull;
           bool open;
@@ -290,18 +323,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (A_MN) {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
-              tma_load_3d(sa + j * (BK * 128), &tmap_a, &full_bar[stage], t.m_tile * BM + j * 64, t.row0 + k0, 0);
+              tma_load_3d(sa + j * (BK * 128), ta, &full_bar[stage], t.m_tile * BM + j * 64, t.row0 + k0, 0);
           } else {
-            tma_load_3d(sa, &tmap_a, &full_bar[stage], k0, t.row0, 0);
+            tma_load_3d(sa, ta, &full_bar[stage], k0, t.row0, 0);
           }
           if (B_MN) {
             const int kz = (p.mode == kVarlenM) ? k0 : t.row0 + k0;
             const int ez = (p.mode == kVarlenM) ? t.expert : 0;
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_3d(sb + j * (BK * 128), &tmap_b, &full_bar[stage], t.n_tile * BN + j * 64, kz, ez);
+              tma_load_3d(sb + j * (BK * 128), tb, &full_bar[stage], t.n_tile * BN + j * 64, kz, ez);
           } else {
-            tma_load_3d(sb, &tmap_b, &full_bar[stage], k0, t.n_tile * BN, t.expert);
+            tma_load_3d(sb, tb, &full_bar[stage], k0, t.n_tile * BN, t.expert);
           }
           ++issued;
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
@@ -322,7 +355,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // ------------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
     int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
-    for (int lin = first_lin; lin < total_tiles && ok; lin += lin_stride) {
+    for (int it = 0; ok; ++it) {
+      int lin;
+      if (dyn) {
+        if (!__all_sync(0xffffffffu, spin_until([&] { return ld_acquire_cta_shared(&s_q_head) > it; }, budget, p.status))) { ok = false; break; }
+        lin = s_q[it % kTileQueue];
+      } else {
+        lin = first_lin + it * lin_stride;
+      }
+      if (lin >= total_tiles || lin < 0) break;
       const TileCoord t = decode_tile(p, lin, num_m);
       if (t.k_blocks == 0) continue;   // empty expert: the epilogue writes zeros on its own
       // all 32 lanes wait; the outcome is made warp-uniform so that no lane leaves ahead of elect_one / __syncwarp
@@ -378,8 +419,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     constexpr int kChunksPerHalf = BN / 64;
     const uint32_t stg = smem_u32(epi_stage + (warp - 2) * Cfg::kEpiStageBytes);
     int acc = 0; uint32_t acc_phase = 0;
-    for (int lin = first_lin; lin < total_tiles; lin += lin_stride) {
+    for (int it = 0;; ++it) {
+      int lin;
+      if (dyn) {
+        // every epilogue thread reads the queue itself; the give-up decision is taken together (see below)
+        const bool got = spin_until([&] { return ld_acquire_cta_shared(&s_q_head) > it; }, budget, p.status);
+        if (epi_vote_any(!got)) break;
+        lin = s_q[it % kTileQueue];
+      } else {
+        lin = first_lin + it * lin_stride;
+      }
+      if (lin >= total_tiles || lin < 0) break;
       const TileCoord t = decode_tile(p, lin, num_m);
+      const CUtensorMap* to0 = t.prob ? &maps2.o : &tmap_o0;
+      const int prob_n = t.prob ? p.N2 : p.N;       // output width of this tile's problem
       const bool empty = (t.k_blocks == 0);
       // Everything that does not need the accumulator is fetched while the tensor cores still work on this tile.
       const int n0 = t.n_tile * BN;
@@ -437,7 +490,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll 1
       for (int c = c_begin; c < c_begin + kChunksPerHalf; ++c) {
         const int n = n0 + c * 32;
-        if (n >= p.N) break;
+        if (n >= prob_n) break;
         if (EPI == kEpiDswiglu) {
           // hand this chunk's preact rows to their threads, then request the next chunk (software pipeline)
 #pragma unroll
@@ -482,7 +535,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                          pack_bf16x2(__uint_as_float(r[q * 8 + 6]), __uint_as_float(r[q * 8 + 7])));
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) { tma_store_3d(&tmap_o0, epi_stage + (warp - 2) * Cfg::kEpiStageBytes, n, warp_row0, zc); bulk_commit(); }
+          if (lane == 0) { tma_store_3d(to0, epi_stage + (warp - 2) * Cfg::kEpiStageBytes, n, warp_row0, zc); bulk_commit(); }
         } else if (EPI == kEpiSwiglu) {
           // columns (2i, 2i+1) = (gate_i, up_i); preact tile at +0 (64-byte rows), postact tile at +2048 (32-byte rows)
           if (p.out1 != nullptr) {
@@ -643,6 +696,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         acc ^= 1; if (acc == 0) acc_phase ^= 1;
       }
       if (p.timing != nullptr && epi_tid == 0) *reinterpret_cast<volatile int*>(&s_tiles_done) += 1;
+      if (dyn) {                    // this queue entry may be reused once every epilogue thread is done with the tile
+        epi_bar_sync();
+        if (epi_tid == 0) st_release_cta_shared(&s_q_tail, it + 1);
+      }
       if (EPI == kEpiDswiglu) {
         if (tok >= 0 && p.dl_dweight != nullptr) red_add_f32(p.dl_dweight + grow, dw_acc);
       }
@@ -742,6 +799,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
+  if (dyn && threadIdx.x == 0) {     // the last CTA puts the claim counter back to zero for the next launch
+    __threadfence();
+    if (atomicAdd(p.tile_counter + 1, 1) == static_cast<int>(gridDim.x) - 1) { p.tile_counter[0] = 0; p.tile_counter[1] = 0; }
+  }
   if (threadIdx.x == 0) {
     int* done_ctr = p.tail.enabled ? p.tail.ctas_done : (PUSH ? pp.blocks_done : nullptr);
     if (done_ctr != nullptr) {
@@ -769,6 +830,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 // ---------------------------------------------------------------------------------------------
 // Host dispatch over the template instances
 // ---------------------------------------------------------------------------------------------
+// maps of the second problem for the launch in progress on this host thread (null: none)
+static thread_local const SecondMaps* t_maps2 = nullptr;
+
 template <int BN, bool A_MN, bool B_MN, int EPI, bool PUSH>
 static cudaError_t launch_instance(const GemmParams& p, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to0,
                             const CUtensorMap& to1, const PushParams& pp, int num_ctas, cudaStream_t stream) {
@@ -784,7 +848,9 @@ static cudaError_t launch_instance(const GemmParams& p, const CUtensorMap& ta, c
     configured[dev].store(true, std::memory_order_release);
   }
   const int threads = (base_warps(EPI) + (PUSH ? push_warps(EPI) : 0)) * 32;
-  kernel<<<num_ctas, threads, smem, stream>>>(ta, tb, to0, to1, p, pp);
+  SecondMaps none;
+  if (t_maps2 == nullptr) { none.a = ta; none.b = tb; none.o = to0; }
+  kernel<<<num_ctas, threads, smem, stream>>>(ta, tb, to0, to1, p, pp, t_maps2 != nullptr ? *t_maps2 : none);
   return cudaSuccess;
 }
 
@@ -817,7 +883,8 @@ static bool dispatch_layout(const GemmParams& p, const CUtensorMap& ta, const CU
 
 bool launch_grouped_gemm(const GemmParams& p, const void* tmap_a, const void* tmap_b, const void* tmap_o0,
                          const void* tmap_o1, const PushParams* fused_push, int num_ctas, cudaStream_t stream,
-                         cudaError_t* setup_error) {
+                         cudaError_t* setup_error, const void* maps2) {
+  t_maps2 = static_cast<const SecondMaps*>(maps2);
   const CUtensorMap& ta = *static_cast<const CUtensorMap*>(tmap_a);
   const CUtensorMap& tb = *static_cast<const CUtensorMap*>(tmap_b);
   const CUtensorMap& to0 = *static_cast<const CUtensorMap*>(tmap_o0 ? tmap_o0 : tmap_a);
@@ -832,6 +899,7 @@ bool launch_grouped_gemm(const GemmParams& p, const void* tmap_a, const void* tm
     ok = (p.block_n == 256) ? dispatch_layout<256, false>(p, ta, tb, to0, to1, none, num_ctas, stream, err)
                             : dispatch_layout<128, false>(p, ta, tb, to0, to1, none, num_ctas, stream, err);
   }
+  t_maps2 = nullptr;
   if (setup_error != nullptr) *setup_error = err;
   return ok;
 }

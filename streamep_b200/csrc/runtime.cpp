@@ -271,6 +271,10 @@ struct GemmArgs {
   int mode = kVarlenM, epilogue = kEpiStore, block_n = 256, num_ctas = 0;
   bool a_mn_major = false, b_mn_major = false;
   at::Tensor a, b;                                  // operands
+  // VarlenK: a second problem (A2 [rows, M2], B2 [rows, N2] -> out2 [E, M2, N2]) multiplied in the same launch, and
+  // dynamic tile claim (CTAs take the next tile from a counter instead of striding by the grid size)
+  std::optional<at::Tensor> a2, b2, out2;
+  bool dynamic_tiles = false;
   std::optional<at::Tensor> tile_id_to_expert, expert_pool_block_offset, expert_frequency;
   std::optional<at::Tensor> arrival_count, arrival_target;
   std::optional<at::Tensor> out0, out1, preact, row_weight, row_token, dl_dweight;
@@ -1008,8 +1012,8 @@ class Runtime {
     p.mode = a.mode; p.epilogue = a.epilogue; p.block_n = a.block_n;
     p.a_mn_major = a.a_mn_major; p.b_mn_major = a.b_mn_major;
     p.rank = rank_; p.status = status_; p.wait_budget_ns = budget_ns_;
-    CUtensorMap ta, tb, to0, to1;
-    bool have_o0 = false, have_o1 = false;
+    CUtensorMap ta, tb, to0, to1, maps2[3];
+    bool have_o0 = false, have_o1 = false, have_maps2 = false;
     const int BN = a.block_n;
     if (a.mode == kVarlenM) {
       // A: [rows, K] row-major; B: weights [E, N, K] (K-major) or [E, K, N] (MN-major)
@@ -1041,9 +1045,24 @@ class Runtime {
       p.expert_pool_block_offset = a.expert_pool_block_offset->data_ptr<int>();
       p.expert_frequency = a.expert_frequency->data_ptr<int>();
       p.out_expert_stride = M * N;
-      if (rows == 0) { a.out0->zero_(); return; }
+      if (a.a2.has_value()) {
+        SEP_ASSERT(a.b2.has_value() && a.out2.has_value() && a.a2->dim() == 2 && a.b2->dim() == 2 && a.a2->size(0) == rows &&
+                   a.b2->size(0) == rows && a.a2->is_contiguous() && a.b2->is_contiguous() &&
+                   a.a2->scalar_type() == at::kBFloat16 && a.b2->scalar_type() == at::kBFloat16,
+                   "the second varlen-K problem needs contiguous bf16 A2 [rows, M2], B2 [rows, N2] over the same rows, and an output");
+        const int64_t M2 = a.a2->size(1), N2 = a.b2->size(1);
+        SEP_ASSERT(M2 % 8 == 0 && N2 % 8 == 0, "M2 and N2 must be multiples of 8");
+        p.N2 = N2; p.M_out2 = M2; p.num_m_tiles2 = (M2 + BM_ - 1) / BM_; p.num_n_tiles2 = (N2 + BN - 1) / BN;
+      }
+      if (rows == 0) { a.out0->zero_(); if (a.out2.has_value()) a.out2->zero_(); return; }
       ta = make_tmap(a.a.data_ptr(), M, rows, 1, M, rows * M, 64, 64);
       tb = make_tmap(a.b.data_ptr(), N, rows, 1, N, rows * N, 64, 64);
+      if (a.a2.has_value()) {
+        maps2[0] = make_tmap(a.a2->data_ptr(), p.M_out2, rows, 1, p.M_out2, rows * p.M_out2, 64, 64);
+        maps2[1] = make_tmap(a.b2->data_ptr(), p.N2, rows, 1, p.N2, rows * p.N2, 64, 64);
+        have_maps2 = true;
+      }
+      if (a.dynamic_tiles) p.tile_counter = counters_ + 10;
     }
     if (a.arrival_count.has_value()) {
       SEP_ASSERT(a.arrival_target.has_value(), "arrival_count needs arrival_target");
@@ -1108,6 +1127,7 @@ class Runtime {
       if (a.mode == kVarlenM) to0 = out_map(*a.out0, p.N, p.total_rows, 1, 32, CU_TENSOR_MAP_SWIZZLE_64B);
       else to0 = out_map(*a.out0, p.N, p.M_out, p.num_experts, 32, CU_TENSOR_MAP_SWIZZLE_64B);
       have_o0 = true;
+      if (have_maps2) maps2[2] = out_map(*a.out2, p.N2, p.M_out2, p.num_experts, 32, CU_TENSOR_MAP_SWIZZLE_64B);
     } else if (a.epilogue == kEpiSwiglu) {
       SEP_ASSERT(p.N % 16 == 0, "SwiGLU epilogue needs an output width that is a multiple of 16");
       to0 = out_map(*a.out0, p.N / 2, p.total_rows, 1, 16, CU_TENSOR_MAP_SWIZZLE_32B); have_o0 = true;
@@ -1117,7 +1137,8 @@ class Runtime {
       to1 = out_map(*a.out1, p.N, p.total_rows, 1, 32, CU_TENSOR_MAP_SWIZZLE_64B); have_o1 = true;
     }
     int n_ctas = a.num_ctas > 0 ? a.num_ctas : num_sms();
-    const int64_t total = static_cast<int64_t>(a.mode == kVarlenM ? p.num_m_tiles : p.num_experts * p.num_m_tiles) * p.num_n_tiles;
+    const int64_t total = a.mode == kVarlenM ? static_cast<int64_t>(p.num_m_tiles) * p.num_n_tiles
+        : static_cast<int64_t>(p.num_experts) * (static_cast<int64_t>(p.num_m_tiles) * p.num_n_tiles + static_cast<int64_t>(p.num_m_tiles2) * p.num_n_tiles2);
     PushParams pp{};
     const PushParams* ppp = nullptr;
     if (a.fused_push) {
@@ -1137,7 +1158,7 @@ class Runtime {
     ++launches_;
     cudaError_t setup_error = cudaSuccess;
     const bool launched = launch_grouped_gemm(p, &ta, &tb, have_o0 ? &to0 : nullptr, have_o1 ? &to1 : nullptr, ppp, n_ctas,
-                                              stream(), &setup_error);
+                                              stream(), &setup_error, have_maps2 ? maps2 : nullptr);
     SEP_ASSERT(launched, "no grouped GEMM kernel for this combination of mode, operand layouts, epilogue and fused push");
     SEP_CUDA_CHECK(setup_error);
     SEP_CUDA_CHECK(cudaGetLastError());
@@ -1280,16 +1301,22 @@ class Runtime {
     }
     mark_local_phase();
     if (tiles > 0) {
-      GemmArgs d2;
-      d2.mode = kVarlenK; d2.epilogue = kEpiStore; d2.block_n = tile_n_dw2; d2.a_mn_major = d2.b_mn_major = true;
-      d2.a = g->dl_do_pool; d2.b = postact_dw2; d2.out0 = dW2;
-      d2.expert_pool_block_offset = st->expert_pool_block_offset; d2.expert_frequency = st->expert_frequency;
-      grouped_gemm(d2);
-      GemmArgs d1;
-      d1.mode = kVarlenK; d1.epilogue = kEpiStore; d1.block_n = tile_n_dw1; d1.a_mn_major = d1.b_mn_major = true;
-      d1.a = dswiglu_in; d1.b = pool; d1.out0 = dW1;
-      d1.expert_pool_block_offset = st->expert_pool_block_offset; d1.expert_frequency = st->expert_frequency;
-      grouped_gemm(d1);
+      // dW1 and dW2 in one launch, tiles claimed dynamically: one tail instead of two, and experts of unequal row
+      // counts (tiles of unequal length) balance out.  dW1 first: its tiles are the longer ones (K = rows, N = H).
+      GemmArgs d;
+      d.mode = kVarlenK; d.epilogue = kEpiStore; d.a_mn_major = d.b_mn_major = true; d.dynamic_tiles = true;
+      d.expert_pool_block_offset = st->expert_pool_block_offset; d.expert_frequency = st->expert_frequency;
+      if (tile_n_dw1 == tile_n_dw2) {
+        d.block_n = tile_n_dw1;
+        d.a = dswiglu_in; d.b = pool; d.out0 = dW1;
+        d.a2 = g->dl_do_pool; d.b2 = postact_dw2; d.out2 = dW2;
+        grouped_gemm(d);
+      } else {
+        d.block_n = tile_n_dw2; d.a = g->dl_do_pool; d.b = postact_dw2; d.out0 = dW2;
+        grouped_gemm(d);
+        d.block_n = tile_n_dw1; d.a = dswiglu_in; d.b = pool; d.out0 = dW1;
+        grouped_gemm(d);
+      }
     } else {
       dW1.zero_(); dW2.zero_();
     }
@@ -1542,6 +1569,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def(py::init<>())
 #define RW(name) .def_readwrite(#name, &GemmArgs::name)
       RW(mode) RW(epilogue) RW(block_n) RW(num_ctas) RW(a_mn_major) RW(b_mn_major) RW(a) RW(b)
+      RW(a2) RW(b2) RW(out2) RW(dynamic_tiles)
       RW(tile_id_to_expert) RW(expert_pool_block_offset) RW(expert_frequency) RW(arrival_count) RW(arrival_target)
       RW(out0) RW(out1) RW(preact) RW(row_weight) RW(row_token) RW(dl_dweight) RW(scatter_local) RW(row_src) RW(row_k_slot)
       RW(tile_stripes_done) RW(k_remaining) RW(done_per_token) RW(remote_out) RW(remote_dw) RW(remote_out_offset) RW(remote_dw_offset) RW(num_m_tiles_dev)

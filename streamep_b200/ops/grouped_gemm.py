@@ -290,11 +290,19 @@ def streaming_moe_y_bwd(dL_do_pool: torch.Tensor, w2: torch.Tensor, preact_a: to
 
 def grouped_gemm_dw(lhs: torch.Tensor, rhs: torch.Tensor, expert_pool_block_offset: torch.Tensor,
                     expert_frequency: torch.Tensor, *, out: Optional[torch.Tensor] = None,
-                    tile_n: Optional[int] = None, num_sms: Optional[int] = None, buffer=None):
+                    tile_n: Optional[int] = None, num_sms: Optional[int] = None, buffer=None,
+                    lhs2: Optional[torch.Tensor] = None, rhs2: Optional[torch.Tensor] = None,
+                    out2: Optional[torch.Tensor] = None, dynamic_tiles: bool = False):
     """Per-expert weight gradient ``out[e] = lhs[rows_e]^T @ rhs[rows_e]`` with
     ``rows_e`` the expert's TRUE row range (padding rows never contribute, whatever
     they hold).  ``lhs [TKp, M]``, ``rhs [TKp, N]`` -> ``out [E, M, N]`` bf16, fp32
-    accumulation in tensor memory."""
+    accumulation in tensor memory.
+
+    ``lhs2`` / ``rhs2`` (over the same rows) add a second problem to the same launch (dW1 and dW2 of a layer
+    together: one tail wave instead of two); then ``(out, out2)`` is returned.  ``dynamic_tiles``: CTAs claim
+    tiles from a device counter instead of striding by the grid size, so tiles of unequal length (experts with
+    unequal row counts) balance out (reference: the ``atomicAdd`` claim of
+    stream_ep/stream_moe/tile_scheduler.py:336-342)."""
     E = expert_frequency.numel()
     M, N = lhs.shape[1], rhs.shape[1]
     if out is None:
@@ -304,10 +312,15 @@ def grouped_gemm_dw(lhs: torch.Tensor, rhs: torch.Tensor, expert_pool_block_offs
     a.a_mn_major = a.b_mn_major = True
     a.a, a.b, a.out0 = lhs, rhs, out
     a.expert_pool_block_offset, a.expert_frequency = expert_pool_block_offset, expert_frequency
+    a.dynamic_tiles = bool(dynamic_tiles)
+    if lhs2 is not None:
+        if out2 is None:
+            out2 = torch.empty(E, lhs2.shape[1], rhs2.shape[1], dtype=lhs.dtype, device=lhs.device)
+        a.a2, a.b2, a.out2 = lhs2, rhs2, out2
     if num_sms:
         a.num_ctas = num_sms
     _rt(buffer).grouped_gemm(a)
-    return out
+    return out if lhs2 is None else (out, out2)
 
 
 def fire_tiles_with_delay(count: torch.Tensor, target: torch.Tensor, delay_us: float = 0.0, buffer=None):

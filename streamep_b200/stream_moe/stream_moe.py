@@ -383,10 +383,15 @@ def _launch_dw(buffer, handle, cfg, dl_do_pool, postact_dw2, dswiglu_in, pool, d
     (stream_ep/stream_moe/stream_moe.py:1107-1146, including the empty-rank guard)."""
     buffer.runtime.mark_local_phase()
     if handle.total_tiles > 0:
-        gg.grouped_gemm_dw(dl_do_pool, postact_dw2, handle.expert_pool_block_offset, handle.expert_frequency,
-                           out=dW2, tile_n=cfg.tile_n_dW2, buffer=buffer)
-        gg.grouped_gemm_dw(dswiglu_in, pool, handle.expert_pool_block_offset, handle.expert_frequency,
-                           out=dW1, tile_n=cfg.tile_n_dW1, buffer=buffer)
+        if cfg.tile_n_dW1 == cfg.tile_n_dW2:      # one launch for both, tiles claimed dynamically
+            gg.grouped_gemm_dw(dswiglu_in, pool, handle.expert_pool_block_offset, handle.expert_frequency, out=dW1,
+                               lhs2=dl_do_pool, rhs2=postact_dw2, out2=dW2, tile_n=cfg.tile_n_dW1, dynamic_tiles=True,
+                               buffer=buffer)
+        else:
+            gg.grouped_gemm_dw(dl_do_pool, postact_dw2, handle.expert_pool_block_offset, handle.expert_frequency,
+                               out=dW2, tile_n=cfg.tile_n_dW2, dynamic_tiles=True, buffer=buffer)
+            gg.grouped_gemm_dw(dswiglu_in, pool, handle.expert_pool_block_offset, handle.expert_frequency,
+                               out=dW1, tile_n=cfg.tile_n_dW1, dynamic_tiles=True, buffer=buffer)
     else:
         dW1.zero_()
         dW2.zero_()

@@ -240,6 +240,31 @@ def test_grouped_gemm_dw(native, M, N, freqs):
     check_close("dW", out, want, atol=2e-2 * scale, rtol=2e-2)
 
 
+@pytest.mark.parametrize("M,N,M2,N2,freqs", [(256, 128, 128, 256, [130, 0, 63, 257]), (2816, 2048, 2048, 1408, [700, 90, 1300]),
+                                              (320, 200, 200, 72, [100, 300])])
+def test_grouped_gemm_dw_two_problems_dynamic_claim(native, M, N, M2, N2, freqs):
+    """dW1 and dW2 in one launch with tiles claimed from a device counter (experts of very unequal length, one
+    empty), twice in a row (the kernel puts the counter back to zero), against fp32 and against the static launch."""
+    gg = _ops()
+    E = len(freqs)
+    cases = [make_pool_case(E, freqs, w, seed=40 + i, device=DEV, garbage_padding=True) for i, w in enumerate((M, N, M2, N2))]
+    off, fr = cases[0]["offsets"], cases[0]["freqs"]
+    for rep in range(2):
+        o1, o2 = gg.grouped_gemm_dw(cases[0]["pool"], cases[1]["pool"], off, fr, lhs2=cases[2]["pool"], rhs2=cases[3]["pool"],
+                                    tile_n=256, dynamic_tiles=True)
+        torch.cuda.synchronize()
+        _check_status()
+        for out, (l, r) in ((o1, (cases[0], cases[1])), (o2, (cases[2], cases[3]))):
+            want = torch.zeros_like(out, dtype=torch.float32)
+            for e, f in enumerate(freqs):
+                r0 = int(off[e]) * 128
+                want[e] = l["pool"][r0:r0 + f].float().t() @ r["pool"][r0:r0 + f].float()
+            check_close(f"dW (rep {rep})", out, want, atol=2e-2 * max(freqs) ** 0.5, rtol=2e-2)
+    static = gg.grouped_gemm_dw(cases[0]["pool"], cases[1]["pool"], off, fr, tile_n=256)
+    torch.cuda.synchronize()
+    assert torch.equal(static, o1), "dynamic claim must not change the result of a tile"
+
+
 def test_pool_compress_roundtrip(native):
     gg = _ops()
     case = make_pool_case(3, [100, 0, 300], 520, seed=19, device=DEV)
