@@ -133,12 +133,26 @@ class Buffer:
     def __init__(self, group, num_nvl_bytes: int = 0, num_rdma_bytes: int = 0,
                  allow_mnnvl: bool = False, use_fabric: bool = False,
                  explicitly_destroy: bool = False, enable_shrink: bool = False,
-                 comm=None, *, timeout_ms: Optional[int] = None,
+                 comm=None, *, timeout_ms: Optional[int] = None, allocator: Optional[str] = None,
                  _local: Optional[Tuple["LocalWorld", int]] = None) -> None:
         import torch.distributed as dist
 
         if num_rdma_bytes:
             raise StreamEPError("the internode (RDMA) path is not available: one NVSwitch domain only")
+        if allow_mnnvl:
+            raise StreamEPError("allow_mnnvl: multi-node NVLink domains are not supported (one NVSwitch domain of up to 8 GPUs)")
+        if enable_shrink:
+            raise StreamEPError("enable_shrink is not supported (the reference allocates its mask buffers but no kernel "
+                                "reads them: csrc/stream_ep.cpp:526-533); use Buffer.recover() after a failed collective")
+        # Two allocators for the symmetric arena (reference: SharedMemoryAllocator, csrc/stream_ep.cpp:52-124):
+        # "ipc" = cudaMalloc + CUDA IPC handles, "vmm" = cuMemCreate + POSIX file descriptors + cuMemMap.  The
+        # reference's `use_fabric` asks for its second (VMM) allocator with fabric handles; inside one node the
+        # shareable handle is a file descriptor, so `use_fabric=True` selects "vmm" here.
+        if allocator is None:
+            allocator = os.environ.get("STREAM_EP_ALLOCATOR", "vmm" if use_fabric else "ipc")
+        if allocator not in ("ipc", "vmm"):
+            raise ValueError(f"allocator must be 'ipc' or 'vmm', got {allocator!r}")
+        self.allocator = allocator
         self._local = _local
         if _local is not None:
             world, rank = _local
@@ -175,11 +189,15 @@ class Buffer:
         arena_bytes = self.num_nvl_bytes if self.num_nvl_bytes > 0 else int(
             os.environ.get("STREAM_EP_ARENA_BYTES", str(2 << 30)))
         self.runtime = _C().Runtime(self.rank, self.group_size, arena_bytes, self.num_channels,
-                                    _C().MAX_EXPERTS, timeout_ms)
+                                    _C().MAX_EXPERTS, timeout_ms, allocator == "vmm")
         if _local is None:
             device_ids = all_gather_object(self.runtime.get_local_device_id())
-            handles = all_gather_object(self.runtime.get_local_ipc_handle() if self.group_size > 1 else None)
-            self.runtime.sync(device_ids, handles)
+            if allocator == "vmm" and self.group_size > 1:
+                self._sync_vmm(all_gather_object)
+            else:
+                handles = all_gather_object(self.runtime.get_local_ipc_handle()
+                                            if self.group_size > 1 and allocator == "ipc" else None)
+                self.runtime.sync(device_ids, handles)
             assert self.runtime.is_available()
         self._next_seq = 0
         self._push_blocks = 0  # 0 = auto
@@ -200,6 +218,51 @@ class Buffer:
         bulk = os.environ.get("STREAM_EP_BULK_PUSH")
         if bulk:
             self.runtime.set_bulk_push(bulk not in ("0", "false", "False"))
+
+    def _sync_vmm(self, all_gather_object) -> None:
+        """Hand every peer a file descriptor of this rank's arena allocation and map theirs.  Descriptors cross
+        process boundaries as SCM_RIGHTS messages on Unix sockets in the abstract namespace: every rank listens on
+        a name derived from a token that rank 0 draws, sends its descriptor to whoever connects, and connects to
+        every peer in turn."""
+        import socket
+        import threading
+        import uuid
+
+        token = all_gather_object(uuid.uuid4().hex if self.rank == 0 else None)[0]
+        name = lambda r: f"\0streamep_b200_{token}_{r}"   # noqa: E731
+        fd = self.runtime.export_vmm_fd()
+        srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+        srv.bind(name(self.rank))
+        srv.listen(self.group_size)
+        srv.settimeout(60)
+
+        def serve():
+            for _ in range(self.group_size - 1):
+                conn, _addr = srv.accept()
+                with conn:
+                    socket.send_fds(conn, [b"fd"], [fd])
+        th = threading.Thread(target=serve, daemon=True)
+        th.start()
+        sizes = all_gather_object(self.runtime.arena_total_bytes())     # also: every rank is listening by now
+        fds = [-1] * self.group_size
+        try:
+            for r in range(self.group_size):
+                if r == self.rank:
+                    continue
+                with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as c:
+                    c.settimeout(60)
+                    c.connect(name(r))
+                    _msg, got, _flags, _addr = socket.recv_fds(c, 16, 1)
+                    if len(got) != 1:
+                        raise StreamEPError(f"rank {self.rank}: no file descriptor received from rank {r}")
+                    fds[r] = got[0]
+            self.runtime.sync_vmm(fds, [int(v) for v in sizes])
+        finally:
+            th.join(timeout=60)
+            srv.close()
+            for f in fds + [fd]:
+                if f >= 0:
+                    os.close(f)
 
     # ------------------------------------------------------------------ lifecycle
     def destroy(self):
@@ -611,14 +674,15 @@ class LocalWorld:
     data paths; production runs one process per GPU.
     """
 
-    def __init__(self, num_ranks: int, arena_bytes: int = 256 << 20, timeout_ms: int = 2000):
+    def __init__(self, num_ranks: int, arena_bytes: int = 256 << 20, timeout_ms: int = 2000,
+                 allocator: Optional[str] = None):
         import threading
         self.num_ranks = num_ranks
         self._barrier = threading.Barrier(num_ranks)
         self._in_run = threading.local()
         self._static_bases = [None] * num_ranks
         self.buffers: List[Buffer] = [
-            Buffer(None, arena_bytes, _local=(self, r), timeout_ms=timeout_ms) for r in range(num_ranks)]
+            Buffer(None, arena_bytes, _local=(self, r), timeout_ms=timeout_ms, allocator=allocator) for r in range(num_ranks)]
         ptrs = [b.runtime.get_local_base_ptr() for b in self.buffers]
         for b in self.buffers:
             b.runtime.sync_local(ptrs)

@@ -87,6 +87,75 @@ static CUtensorMap make_tmap(const void* base, uint64_t d0, uint64_t d1, uint64_
 }
 
 // ---------------------------------------------------------------------------------------------
+// Peer-shareable device memory through the virtual-memory-management driver API: cuMemCreate with a POSIX file
+// descriptor as the shareable handle, cuMemAddressReserve + cuMemMap + cuMemSetAccess on the owner, and
+// cuMemImportFromShareableHandle + map on every peer (the descriptor travels between the processes of a node over a
+// Unix socket, see buffer.py).  Second allocator next to cudaMalloc + CUDA IPC, like the reference's
+// SharedMemoryAllocator (csrc/stream_ep.cpp:52-124, which uses fabric handles for multi-node NVLink); it is also
+// what a multicast (NVLS) binding of the arena would need.
+// ---------------------------------------------------------------------------------------------
+struct VmmApi {
+  CUresult (*create)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long);
+  CUresult (*release)(CUmemGenericAllocationHandle);
+  CUresult (*reserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long);
+  CUresult (*addr_free)(CUdeviceptr, size_t);
+  CUresult (*map)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long);
+  CUresult (*unmap)(CUdeviceptr, size_t);
+  CUresult (*set_access)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t);
+  CUresult (*export_handle)(void*, CUmemGenericAllocationHandle, CUmemAllocationHandleType, unsigned long long);
+  CUresult (*import_handle)(CUmemGenericAllocationHandle*, void*, CUmemAllocationHandleType);
+  CUresult (*granularity)(size_t*, const CUmemAllocationProp*, CUmemAllocationGranularity_flags);
+  static const VmmApi& get() {
+    static VmmApi api = [] {
+      VmmApi a{};
+      a.create = driver_fn<decltype(a.create)>("cuMemCreate");
+      a.release = driver_fn<decltype(a.release)>("cuMemRelease");
+      a.reserve = driver_fn<decltype(a.reserve)>("cuMemAddressReserve");
+      a.addr_free = driver_fn<decltype(a.addr_free)>("cuMemAddressFree");
+      a.map = driver_fn<decltype(a.map)>("cuMemMap");
+      a.unmap = driver_fn<decltype(a.unmap)>("cuMemUnmap");
+      a.set_access = driver_fn<decltype(a.set_access)>("cuMemSetAccess");
+      a.export_handle = driver_fn<decltype(a.export_handle)>("cuMemExportToShareableHandle");
+      a.import_handle = driver_fn<decltype(a.import_handle)>("cuMemImportFromShareableHandle");
+      a.granularity = driver_fn<decltype(a.granularity)>("cuMemGetAllocationGranularity");
+      return a;
+    }();
+    return api;
+  }
+};
+#define SEP_CU_CHECK(expr)                                                                                   \
+  do {                                                                                                       \
+    CUresult r__ = (expr);                                                                                   \
+    if (r__ != CUDA_SUCCESS)                                                                                 \
+      throw std::runtime_error(std::string("streamep_b200: driver call failed with code ") + std::to_string(r__) + \
+                               " in " #expr);                                                                \
+  } while (0)
+
+// One mapped range: a physical allocation (own or imported) behind a reserved virtual address range.
+struct VmmRange {
+  CUmemGenericAllocationHandle handle = 0;
+  CUdeviceptr va = 0;
+  size_t bytes = 0;
+  bool mapped = false;
+  void map_for(int device) {
+    const VmmApi& api = VmmApi::get();
+    SEP_CU_CHECK(api.reserve(&va, bytes, 0, 0, 0));
+    SEP_CU_CHECK(api.map(va, bytes, 0, handle, 0));
+    mapped = true;
+    CUmemAccessDesc acc{};
+    acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE; acc.location.id = device;
+    acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    SEP_CU_CHECK(api.set_access(va, bytes, &acc, 1));
+  }
+  void destroy() {
+    const VmmApi& api = VmmApi::get();
+    if (mapped) { api.unmap(va, bytes); mapped = false; }
+    if (va != 0) { api.addr_free(va, bytes); va = 0; }
+    if (handle != 0) { api.release(handle); handle = 0; }
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
 // Config (reference: csrc/config.hpp:23-132).  The five-tuple is kept for source compatibility;
 // this implementation has no rings, so the chunk sizes only bound the size hints.
 // ---------------------------------------------------------------------------------------------
@@ -321,8 +390,11 @@ struct StaticPlan {
 
 class Runtime {
  public:
-  Runtime(int rank, int num_ranks, int64_t arena_bytes, int num_channels, int num_experts_cap, int64_t timeout_ms)
-      : rank_(rank), num_ranks_(num_ranks), num_channels_(num_channels) {
+  // `use_vmm`: take the arena from the virtual-memory-management API (shareable by file descriptor) instead of
+  // cudaMalloc + CUDA IPC.
+  Runtime(int rank, int num_ranks, int64_t arena_bytes, int num_channels, int num_experts_cap, int64_t timeout_ms,
+          bool use_vmm = false)
+      : rank_(rank), num_ranks_(num_ranks), num_channels_(num_channels), use_vmm_(use_vmm) {
     SEP_ASSERT(num_ranks >= 1 && num_ranks <= kMaxRanks, "1..8 ranks supported inside one NVSwitch domain");
     SEP_ASSERT(num_channels >= 1 && num_channels <= kMaxChannels, "num_channels out of range");
     SEP_ASSERT(num_experts_cap >= 1 && num_experts_cap <= kMaxExperts, "num_experts_cap out of range");
@@ -343,7 +415,22 @@ class Runtime {
     ctl_ = make_control_layout(num_ranks, num_channels, num_experts_cap);
     arena_bytes_ = static_cast<size_t>(arena_bytes) + ctl_.total_bytes;
     arena_bytes_ = (arena_bytes_ + (2u << 20) - 1) / (2u << 20) * (2u << 20);
-    SEP_CUDA_CHECK(cudaMalloc(&base_, arena_bytes_));
+    if (use_vmm_) {
+      SEP_CUDA_CHECK(cudaFree(nullptr));     // make sure the primary context exists before driver calls
+      CUmemAllocationProp prop{};
+      prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+      prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE; prop.location.id = device_;
+      prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+      size_t gran = 0;
+      SEP_CU_CHECK(VmmApi::get().granularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED));
+      arena_bytes_ = (arena_bytes_ + gran - 1) / gran * gran;
+      own_range_.bytes = arena_bytes_;
+      SEP_CU_CHECK(VmmApi::get().create(&own_range_.handle, arena_bytes_, &prop, 0));
+      own_range_.map_for(device_);
+      base_ = reinterpret_cast<void*>(own_range_.va);
+    } else {
+      SEP_CUDA_CHECK(cudaMalloc(&base_, arena_bytes_));
+    }
     SEP_CUDA_CHECK(cudaMemset(base_, 0, ctl_.total_bytes));
     arena_ = std::make_shared<Arena>(ctl_.total_bytes, arena_bytes_ - ctl_.total_bytes);
     release_ctx_ = std::make_shared<ReleaseCtx>();
@@ -378,7 +465,10 @@ class Runtime {
       arena_->sweep(true);
     }
     for (int i = 0; i < num_ranks_; ++i)
-      if (i != rank_ && peer_base_[i] != nullptr && opened_[i]) cudaIpcCloseMemHandle(peer_base_[i]);
+      if (i != rank_ && peer_base_[i] != nullptr && opened_[i]) {
+        if (use_vmm_) peer_ranges_[i].destroy();
+        else cudaIpcCloseMemHandle(peer_base_[i]);
+      }
     // Tensors over arena blocks may outlive the runtime object; the slab itself is only freed when
     // the last of them is gone (they hold the shared arena, see alloc_symmetric).
     arena_guard_.reset();
@@ -397,6 +487,30 @@ class Runtime {
     return py::bytes(reinterpret_cast<const char*>(&h), sizeof(h));
   }
   int64_t get_local_base_ptr() const { return reinterpret_cast<int64_t>(base_); }
+  bool uses_vmm() const { return use_vmm_; }
+  int64_t arena_total_bytes() const { return static_cast<int64_t>(arena_bytes_); }
+  // VMM arena: a POSIX file descriptor for the physical allocation (the caller sends it to the peers and closes it).
+  int export_vmm_fd() const {
+    SEP_ASSERT(use_vmm_, "the arena was not allocated through the VMM API");
+    int fd = -1;
+    SEP_CU_CHECK(VmmApi::get().export_handle(&fd, own_range_.handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0));
+    return fd;
+  }
+  // VMM arena, multi-process: import every peer's allocation from the descriptor received for it (fds[r]; own entry ignored).
+  void sync_vmm(const std::vector<int>& fds, const std::vector<int64_t>& sizes) {
+    SEP_ASSERT(use_vmm_ && static_cast<int>(fds.size()) == num_ranks_ && sizes.size() == fds.size(), "one descriptor and size per rank expected");
+    for (int r = 0; r < num_ranks_; ++r) {
+      if (r == rank_) continue;
+      VmmRange& pr = peer_ranges_[r];
+      pr.bytes = static_cast<size_t>(sizes[r]);
+      SEP_CU_CHECK(VmmApi::get().import_handle(&pr.handle, reinterpret_cast<void*>(static_cast<uintptr_t>(fds[r])),
+                                               CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR));
+      pr.map_for(device_);
+      peer_base_[r] = reinterpret_cast<void*>(pr.va);
+      opened_[r] = true;
+    }
+    finish_sync();
+  }
 
   // Multi-process: open every peer's IPC handle.  `handles[r]` is rank r's handle.
   void sync(const std::vector<int>& device_ids, const std::vector<std::optional<py::bytes>>& handles) {
@@ -1417,7 +1531,12 @@ class Runtime {
   void finish_sync() {
     // keeps the slab alive as long as any arena tensor or the runtime itself exists
     void* base = base_;
-    arena_guard_ = std::shared_ptr<void>(base, [](void* p) { cudaFree(p); });
+    if (use_vmm_) {
+      VmmRange own = own_range_;
+      arena_guard_ = std::shared_ptr<void>(base, [own](void*) mutable { own.destroy(); });
+    } else {
+      arena_guard_ = std::shared_ptr<void>(base, [](void* p) { cudaFree(p); });
+    }
     available_ = true;
   }
   int num_sms() {
@@ -1439,6 +1558,9 @@ class Runtime {
   cudaStream_t last_stream_ = reinterpret_cast<cudaStream_t>(-1);
   void* peer_base_[kMaxRanks];
   bool opened_[kMaxRanks] = {false, false, false, false, false, false, false, false};
+  bool use_vmm_ = false;
+  VmmRange own_range_;
+  VmmRange peer_ranges_[kMaxRanks];
   void* scratch_ = nullptr;
   StatusBlock* status_ = nullptr;
   int* gate_flags_ = nullptr;
@@ -1579,8 +1701,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 #undef RW
 
   py::class_<Runtime>(m, "Runtime")
-      .def(py::init<int, int, int64_t, int, int, int64_t>(), py::arg("rank"), py::arg("num_ranks"), py::arg("arena_bytes"),
-           py::arg("num_channels"), py::arg("num_experts_cap"), py::arg("timeout_ms"))
+      .def(py::init<int, int, int64_t, int, int, int64_t, bool>(), py::arg("rank"), py::arg("num_ranks"), py::arg("arena_bytes"),
+           py::arg("num_channels"), py::arg("num_experts_cap"), py::arg("timeout_ms"), py::arg("use_vmm") = false)
+      .def("uses_vmm", &Runtime::uses_vmm)
+      .def("arena_total_bytes", &Runtime::arena_total_bytes)
+      .def("export_vmm_fd", &Runtime::export_vmm_fd)
+      .def("sync_vmm", &Runtime::sync_vmm)
       .def("destroy", &Runtime::destroy)
       .def("get_local_device_id", &Runtime::get_local_device_id)
       .def("get_local_ipc_handle", &Runtime::get_local_ipc_handle)

@@ -196,13 +196,17 @@ def missing_rank_check(buf, rank, R, dev):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--scenario", default="all")
+    ap.add_argument("--allocator", default=None, choices=[None, "ipc", "vmm"],
+                    help="arena allocator: cudaMalloc + CUDA IPC, or cuMemCreate + file descriptors + cuMemMap")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    buf = Buffer(dist.group.WORLD, 1 << 30, timeout_ms=5000)
+    buf = Buffer(dist.group.WORLD, 1 << 30, timeout_ms=5000, allocator=args.allocator)
+    if rank == 0:
+        print(f"arena allocator: {buf.allocator}", flush=True)
     if args.scenario in ("all", "comm"):
         comm_checks(buf, rank, world, dev)
     if args.scenario in ("all", "layer"):
@@ -216,7 +220,7 @@ def main():
         # pair to rank 0, so the regions are sized for the whole group's pairs
         cbuf = Buffer(dist.group.WORLD, Buffer.capacity_mode_bytes(700 + 64 * world, 512, 4, 4 * world, world,
                                                                    capacity_factor=float(world) + 0.5) + (256 << 20),
-                      timeout_ms=5000)
+                      timeout_ms=5000, allocator=args.allocator)
         cbuf.enable_capacity_mode(700 + 64 * world, 512, 4, 4 * world, capacity_factor=float(world) + 0.5)
         layer_checks(cbuf, rank, world, dev, tag0="capacity mode: ")
         layer_checks(cbuf, rank, world, dev, lopsided=True, tag0="capacity mode: ")

@@ -131,6 +131,37 @@ def test_layer_emulated_ranks(native, R, fused, level, routing, tokens):
         check_close("dW2", got_dw2, acc[1], atol=3e-2 * float(acc[1].abs().max()), rtol=3e-2)
 
 
+@pytest.mark.parametrize("R", [1, 4])
+def test_layer_on_the_vmm_allocator(native, R):
+    """The arena taken from the virtual-memory-management API (cuMemCreate / cuMemMap / cuMemSetAccess) instead of
+    cudaMalloc: same layer, same checks, plus a capacity-mode region on it."""
+    from streamep_b200 import LocalWorld
+    from streamep_b200.stream_moe import _resolve_tile_config, moe_backward, moe_forward
+    H, I, E, K, T = 256, 128, 16, 4, 300
+    EL = E // R
+    w1, w2, xs, idxs, ws, dys = _make(R, T, H, I, E, K, seed=9, sentinel_p=0.03)
+    world = LocalWorld(R, arena_bytes=128 << 20, allocator="vmm")
+    assert all(b.runtime.uses_vmm() for b in world.buffers)
+    streams = world.make_streams()
+    cfg = _resolve_tile_config(None, I, H)
+    for capacity in (False, True):
+        if capacity:
+            world.enable_capacity_mode(T, H, K, E, capacity_factor=1.6)
+
+        def rank_fn(r, buf):
+            ctx = SimpleNamespace()
+            w1l, w2l = w1[r * EL:(r + 1) * EL].contiguous(), w2[r * EL:(r + 1) * EL].contiguous()
+            out = moe_forward(ctx, streams, buf, xs[r], idxs[r], ws[r], None, w1l, w2l, E, cfg, 0, True)
+            return out, moe_backward(ctx, dys[r])
+        res = world.run(rank_fn)
+        torch.cuda.synchronize()
+        world.check_status()
+        acc = [None, None]
+        for r in range(R):
+            _check(r, res[r][0], res[r][1], xs[r], idxs[r], ws[r], dys[r], w1, w2, EL, acc)
+        del res
+
+
 def test_layer_stack_depth_and_arena_reuse(native):
     """Several layers back to back for several steps on one buffer (the reference's
     tests/test_pipeline_depth_stress.py without the fault injection): every layer's forward state

@@ -21,3 +21,9 @@ def test_multiprocess_nvlink_paths():
     sys.stdout.write(out.stdout[-6000:])
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "ALL PASS" in out.stdout
+    # the same layer and capacity-mode checks with the arena on the VMM allocator (descriptors over Unix sockets)
+    out = subprocess.run(cmd + ["--allocator", "vmm", "--scenario", "capacity"], capture_output=True, text=True,
+                         timeout=900, env=env)
+    sys.stdout.write(out.stdout[-3000:])
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert "ALL PASS" in out.stdout and "arena allocator: vmm" in out.stdout
