@@ -62,7 +62,9 @@ def reference_arm(args):
     (stream_ep/stream_moe/kernel_a.py:216, CHANGES.md:131)."""
     why = ("reference stream_moe_func is Hopper-only: kernel wrappers assert compute capability 9.x "
            "(stream_ep/stream_moe/kernel_a.py:216,525; kernel_y.py:734,937) and need the private quack fork "
-           "(lens_k, epi_subtile_store; CHANGES.md:131) that is not in the offline wheelhouse")
+           "(lens_k, epi_subtile_store; CHANGES.md:131) that is not in the offline wheelhouse; its communication "
+           "extension alone builds for sm_100 only with an added device-link step (baseline/build_reference_comm.sh) and its "
+           "own tests/test_dispatch.py then stops at csrc/config.hpp:129 (NVSHMEM disabled)")
     note = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "REFERENCE_INSTALL.txt")
     if os.path.exists(note):
         with open(note) as f:
