@@ -132,21 +132,33 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
     if (warp == 0) {
       // Order-preserving rank of every pair inside its (channel, expert) substream.
       const int n = (hi - lo) * K;
-      for (int base = 0; base < n; base += 32) {
-        const int i = base + lane;
-        long long e = -1;
-        if (i < n) e = p.topk_idx[static_cast<size_t>(lo) * K + i];
-        const bool valid = (e >= 0 && e < E);
-        const int key = valid ? static_cast<int>(e) : (-1 - lane);
-        const unsigned peers = __match_any_sync(0xffffffffu, key);
-        int rank_in = -1;
-        if (valid) {
-          rank_in = s_hist[e] + __popc(peers & ((1u << lane) - 1u));
+      // eight steps' worth of expert ids are fetched at once: one dependent global load per step would make this
+      // warp, the slowest of the block, wait ~40 times in a row
+      for (int base0 = 0; base0 < n; base0 += 256) {
+        long long ev[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int i = base0 + j * 32 + lane;
+          ev[j] = (i < n) ? p.topk_idx[static_cast<size_t>(lo) * K + i] : -1;
         }
-        __syncwarp();
-        if (valid && (__ffs(peers) - 1) == lane) s_hist[e] += __popc(peers);
-        __syncwarp();
-        if (i < n) p.pair_rank[static_cast<size_t>(lo) * K + i] = rank_in;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int base = base0 + j * 32;
+          if (base >= n) break;
+          const int i = base + lane;
+          const long long e = ev[j];
+          const bool valid = (e >= 0 && e < E);
+          const int key = valid ? static_cast<int>(e) : (-1 - lane);
+          const unsigned peers = __match_any_sync(0xffffffffu, key);
+          int rank_in = -1;
+          if (valid) {
+            rank_in = s_hist[e] + __popc(peers & ((1u << lane) - 1u));
+          }
+          __syncwarp();
+          if (valid && (__ffs(peers) - 1) == lane) s_hist[e] += __popc(peers);
+          __syncwarp();
+          if (i < n) p.pair_rank[static_cast<size_t>(lo) * K + i] = rank_in;
+        }
       }
     } else if (warp <= R) {
       // Order-preserving rank of every token among the channel's tokens that go to rank d.
@@ -185,7 +197,7 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
       ctl_inbox_tokens(p.peer_base[peer], p.ctl, parity, p.rank, c)[d] = (d < R) ? s_u[d] : 0;
     }
     if (c == 0 && tid < R) ctl_inbox_misc(p.peer_base[tid], p.ctl, parity, p.rank)[0] = p.region_id;
-    __threadfence_system();
+    fence_acq_rel_sys();      // this thread's rows are ordered before the flag the last block stores below
     __syncthreads();
     if (tid == 0) {
       const int old = atomicAdd(p.blocks_done, 1);
@@ -193,7 +205,7 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
     }
     __syncthreads();
     if (!s_is_last) return;
-    __threadfence_system();
+    fence_acq_rel_sys();
     if (tid < R) flags_signal(p.peer_base, p.ctl, kKindMetadata, p.epoch, p.rank, tid);
     if (tid == 0) *p.blocks_done = 0;
     if (!(p.phase_mask & 2)) return;
@@ -291,8 +303,9 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
     return;
   }
   // 3. host-visible sizes first, so the host poll overlaps the rest of this kernel
+  const bool host_polls = p.region_id < 0;     // capacity mode: nobody reads the sizes on the host, skip the PCIe writes
   if (tid < EL) {
-    p.host->recv_per_expert[tid] = s_hist[p.rank * EL + tid];
+    if (host_polls) p.host->recv_per_expert[tid] = s_hist[p.rank * EL + tid];
     p.expert_frequency[tid] = s_hist[p.rank * EL + tid];
     p.expert_pool_block_offset[tid] = s_off[p.rank * EL + tid];
   }
@@ -300,12 +313,11 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
     p.expert_pool_block_offset[EL] = s_total_tiles[p.rank];
     int recv = 0;
     for (int s = 0; s < R; ++s) recv += s_U[s][p.rank];
-    p.host->total_tiles = s_total_tiles[p.rank];
-    p.host->num_recv_tokens = recv;
+    if (host_polls) { p.host->total_tiles = s_total_tiles[p.rank]; p.host->num_recv_tokens = recv; }
     if (p.dev_sizes != nullptr) { p.dev_sizes[0] = s_total_tiles[p.rank]; p.dev_sizes[1] = recv; p.dev_sizes[2] = 0; }
   }
   __syncthreads();
-  if (tid == 0) {
+  if (tid == 0 && host_polls) {
     __threadfence_system();
     p.host->epoch = p.epoch;
   }
@@ -332,27 +344,36 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
       carry += total;
     }
   }
-  // 5. token-id bases and the prefix matrices of the handle
-  if (tid < R) {
-    const int d = tid;
+  // 5. token-id bases and the prefix matrices of the handle: one warp per rank, 32 channels per step (a single
+  //    thread walking the channels waits for one dependent global load per channel, 2 x 40 of them)
+  if (warp < R) {
+    const int d = warp;            // sender view: destination d
     int before = 0;
     for (int s = 0; s < p.rank; ++s) before += s_U[s][d];
-    int run = before, incl = 0;
-    for (int c = 0; c < C; ++c) {
-      p.send_token_base[c * R + d] = run;
-      const int u = ctl_inbox_tokens(own, p.ctl, parity, p.rank, c)[d];
-      run += u; incl += u;
-      p.channel_prefix_matrix[d * C + c] = incl;
+    int carry = 0;
+    for (int base = 0; base < C; base += 32) {
+      const int c = base + lane;
+      const int u = (c < C) ? ctl_inbox_tokens(own, p.ctl, parity, p.rank, c)[d] : 0;
+      int total;
+      const int excl = warp_excl_scan(u, lane, total);
+      if (c < C) {
+        p.send_token_base[c * R + d] = before + carry + excl;
+        p.channel_prefix_matrix[d * C + c] = carry + excl + u;
+      }
+      carry += total;
     }
-    // receiver view: source s = tid
-    const int s = tid;
+    const int s = warp;            // receiver view: source s
     int cum = 0;
     for (int ss = 0; ss <= s; ++ss) cum += s_U[ss][p.rank];
-    for (int dd = 0; dd < R; ++dd) p.rank_prefix_matrix[s * R + dd] = (dd == p.rank) ? cum : 0;
-    int rc = 0;
-    for (int c = 0; c < C; ++c) {
-      rc += ctl_inbox_tokens(own, p.ctl, parity, s, c)[p.rank];
-      p.recv_channel_prefix_matrix[s * C + c] = rc;
+    if (lane < R) p.rank_prefix_matrix[s * R + lane] = (lane == p.rank) ? cum : 0;
+    carry = 0;
+    for (int base = 0; base < C; base += 32) {
+      const int c = base + lane;
+      const int u = (c < C) ? ctl_inbox_tokens(own, p.ctl, parity, s, c)[p.rank] : 0;
+      int total;
+      const int excl = warp_excl_scan(u, lane, total);
+      if (c < C) p.recv_channel_prefix_matrix[s * C + c] = carry + excl + u;
+      carry += total;
     }
   }
   // 6. push order of this rank's pairs (p.push_order).
@@ -384,9 +405,13 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
     for (int e = tid; e < E; e += blockDim.x) {
       const int d = e / EL, el = e - d * EL;
       int run = s_off[el * R + ((d - p.rank + R) % R)];
-      for (int c = 0; c < C; ++c) {
-        p.send_order_base[static_cast<size_t>(c) * E + e] = run;
-        run += ctl_inbox_counts(own, p.ctl, parity, p.rank, c)[e];
+      for (int c0 = 0; c0 < C; c0 += 8) {     // eight loads in flight, then eight stores (a store per load would serialise them)
+        int v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = (c0 + j < C) ? ctl_inbox_counts(own, p.ctl, parity, p.rank, c0 + j)[e] : 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (c0 + j < C) { p.send_order_base[static_cast<size_t>(c0 + j) * E + e] = run; run += v[j]; }
       }
     }
     return;
