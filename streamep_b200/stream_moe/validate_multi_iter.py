@@ -170,7 +170,7 @@ def main():
                     check_close(name, got, want, atol=tol * s(want) * scale, rtol=tol * scale)
             except AssertionError as e:
                 msgs.append(str(e))
-            worst.append(f"{name} max|diff| {float((got.float() - want.to(got.device).float()).abs().max()):.2e} of max|ref| {s(want):.2e}")
+            worst.append(f"{name} max|diff| {float((got.detach().float() - want.detach().to(got.device).float()).abs().max()):.2e} of max|ref| {s(want):.2e}")
         for layer in layers:
             layer.w1.grad = None
             layer.w2.grad = None
