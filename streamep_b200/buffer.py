@@ -379,6 +379,7 @@ class Buffer:
             dist.all_gather_object(every, mine, self.group)
         agreed = [max(col) + 2 for col in zip(*every)]
         self.runtime.set_epochs(agreed)
+        self.runtime.static_reset()      # capacity mode: the alternating regions start over on every rank
         if self._local is None and self.group_size > 1:
             dist.barrier(self.group)
 

@@ -647,6 +647,16 @@ class Runtime {
     static_ = pl;
     return static_cast<int64_t>(base);
   }
+  // After a failed collective the ranks may have made different numbers of calls: put the alternation of the
+  // gradient / landing regions back to its start and re-zero the gradient tile counters.  Collective by convention
+  // (Buffer.recover calls it on every rank after the device drained); regions still claimed by live handles stay so.
+  void static_reset() {
+    if (!static_) return;
+    static_->landing_calls = 0; static_->bwd_calls = 0;
+    for (int i = 0; i < 2; ++i)
+      SEP_CUDA_CHECK(cudaMemsetAsync(static_cast<char*>(base_) + static_->bwd_cnt_off[i], 0, static_->tiles_cap * 4, stream()));
+    SEP_CUDA_CHECK(cudaStreamSynchronize(stream()));
+  }
   bool static_enabled() const { return static_ != nullptr; }
   // True when a dispatch of this shape can use the fixed regions.
   bool static_fits(int64_t tokens, int hidden, int topk) const {
@@ -1746,6 +1756,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("num_experts"), py::arg("tile_m"), py::arg("seq"), py::arg("capacity_mode") = false)
       .def("enable_static", &Runtime::enable_static)
       .def("static_enabled", &Runtime::static_enabled)
+      .def("static_reset", &Runtime::static_reset)
       .def("static_fits", &Runtime::static_fits)
       .def("static_capacity", &Runtime::static_capacity)
       .def("overflow_info", &Runtime::overflow_info)

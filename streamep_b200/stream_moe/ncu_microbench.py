@@ -23,7 +23,7 @@ import torch
 
 from ..ops import grouped_gemm as gg
 
-KERNELS = ("a", "a_preact", "y", "y_bwd", "a_bwd", "dw1", "dw2", "preact", "cublas")
+KERNELS = ("a", "a_preact", "y", "y_bwd", "a_bwd", "dw1", "dw2", "dw_merged", "preact", "cublas")
 
 
 def _peaks():
@@ -95,6 +95,10 @@ def make_launcher(kernel, c, tile_n=None):
     if kernel == "dw2":
         return (lambda: gg.grouped_gemm_dw(c["pool"], c["postact"], c["offsets"], c["freqs"], out=c["dw2"], tile_n=tile_n)), \
             2.0 * pairs * H * I, pairs * (I + H) * 2 + c["w2"].numel() * 2
+    if kernel == "dw_merged":   # dW1 and dW2 in one launch, tiles claimed from a device counter (what the layer runs)
+        return (lambda: gg.grouped_gemm_dw(c["dswiglu_in"], c["pool"], c["offsets"], c["freqs"], out=c["dw1"], lhs2=c["pool"],
+                                           rhs2=c["postact"], out2=c["dw2"], tile_n=tile_n or 256, dynamic_tiles=True)), \
+            6.0 * pairs * H * I, pairs * (3 * I + 2 * H) * 2 + (c["w1"].numel() + c["w2"].numel()) * 2
     if kernel == "router":   # tokens = rows, experts = --router-experts, top-6
         E = c["router_experts"]
         g = torch.Generator(device="cpu").manual_seed(3)
