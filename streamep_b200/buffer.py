@@ -215,6 +215,9 @@ class Buffer:
         ctas = os.environ.get("STREAM_EP_PUSH_CTAS")
         if ctas:
             self.runtime.set_push_ctas(int(ctas))
+        split = os.environ.get("STREAM_EP_SPLIT_LOCAL")
+        if split:
+            self.runtime.set_split_local(split not in ("0", "false", "False"))
         bulk = os.environ.get("STREAM_EP_BULK_PUSH")
         if bulk:
             self.runtime.set_bulk_push(bulk not in ("0", "false", "False"))

@@ -159,6 +159,9 @@ struct PushParams {
   int head_pairs_per_chunk;      // the first `head_chunks` chunks are this small, so that the first tiles complete early
   int head_chunks;               // (0 = every chunk has pairs_per_chunk pairs)
   int active_push_warps;         // push warps per CTA of the fused kernels that take chunks (0 = all)
+  int row_filter;                // which pairs this launch / CTA ships: 0 all, 1 only those that stay on this rank, 2 only remote ones
+  int split_local;               // with push-only CTAs: they ship the remote pairs, the push warps of the GEMM CTAs the local ones
+  int* work_counter_local;       // chunk claim of the local-pair walkers (zero on entry, reset by the kernel)
   int bulk_push;                 // push-only CTAs copy rows through the bulk-copy engine (shared-memory ring) instead of ld/st
   int push_ctas;                 // fused kernels: this many CTAs only push and the others only multiply (0 = every CTA does both)
   void* peer_base[kMaxRanks];

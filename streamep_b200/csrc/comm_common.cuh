@@ -137,12 +137,12 @@ struct PushRing {
 };
 
 __device__ __forceinline__ void push_chunk(const PushParams& p, const PushTargets& tg, int pos_begin,
-                                           int pos_end, int lane, PushRing* ring = nullptr) {
+                                           int pos_end, int lane, PushRing* ring = nullptr, int filter = 0) {
   const int K = p.num_topk, R = p.num_ranks;
   const int e_local = p.num_experts / R;
   const size_t row_bytes = static_cast<size_t>(p.hidden) * 2;
   const int vec_per_row = p.hidden / 8;   // 16-byte vectors
-  const int n = pos_end - pos_begin;
+  int n = pos_end - pos_begin;
 
   int t = -1, k = 0, slot = -1, dst = -1;
   if (lane < n) {
@@ -151,6 +151,19 @@ __device__ __forceinline__ void push_chunk(const PushParams& p, const PushTarget
     const long long e = p.topk_idx[pair];
     slot = p.pair_slot[pair];
     dst = static_cast<int>(e / e_local);
+  }
+  if (filter != 0) {
+    // Only the pairs of one kind are this walker's: compact them to the low lanes (order kept), the rest is left to
+    // the walkers of the other kind, which go through the same list with a counter of their own.
+    const bool mine = lane < n && ((filter == 1) == (dst == p.rank));
+    const unsigned mask = __ballot_sync(0xffffffffu, mine);
+    const int src_lane = __fns(mask, 0, lane + 1);          // lane of the (lane + 1)-th pair of this kind, or -1
+    const int from = src_lane < 0 ? lane : src_lane;
+    const int t2 = __shfl_sync(0xffffffffu, t, from), k2 = __shfl_sync(0xffffffffu, k, from);
+    const int s2 = __shfl_sync(0xffffffffu, slot, from), d2 = __shfl_sync(0xffffffffu, dst, from);
+    n = __popc(mask);
+    if (lane < n) { t = t2; k = k2; slot = s2; dst = d2; } else { t = -1; k = 0; slot = -1; dst = -1; }
+    if (n == 0) return;
   }
   if (ring != nullptr && ring->smem != 0) {
     const int pieces = static_cast<int>((row_bytes + kPushPieceBytes - 1) / kPushPieceBytes);

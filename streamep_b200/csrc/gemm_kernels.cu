@@ -258,7 +258,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (chunk >= num_chunks) break;
           int p0, p1;
           push_chunk_range(pp, num_send, chunk, p0, p1);
-          push_chunk(pp, s_tg, p0, p1, lane, &ring);
+          push_chunk(pp, s_tg, p0, p1, lane, &ring, pp.split_local ? 2 : 0);
         }
         if (p.timing != nullptr && lane == 0)
           atomicMax(reinterpret_cast<unsigned long long*>(p.timing + static_cast<size_t>(blockIdx.x) * kTimingCols + 5), globaltimer_ns());
@@ -755,7 +755,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
   } else if (PUSH) {
     // ------------------------------------------------------------------ dispatch push warps (mixed mode)
-    if ((pp.flags & 2) && num_push_ctas == 0) {
+    // (with push-only CTAs in the grid these warps either stay idle or, split_local, ship the pairs that stay on
+    // this rank: local copies drain fast and do not back up the load/store path)
+    const bool local_walker = num_push_ctas > 0 && pp.split_local && pp.work_counter_local != nullptr;
+    if ((pp.flags & 2) && (num_push_ctas == 0 || local_walker)) {
       const int pw = warp - base_warps(EPI);
       if (pw == 0 && lane < pp.num_ranks) {
         const unsigned long long* rec = pp.static_targets
@@ -773,12 +776,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           p.timing[static_cast<size_t>(blockIdx.x) * kTimingCols + 4] = static_cast<long long>(globaltimer_ns());
         for (;;) {
           int chunk = 0;
-          if (lane == 0) chunk = atomicAdd(pp.work_counter, 1);
+          if (lane == 0) chunk = atomicAdd(local_walker ? pp.work_counter_local : pp.work_counter, 1);
           chunk = __shfl_sync(0xffffffffu, chunk, 0);
           if (chunk >= num_chunks) break;
           int p0, p1;
           push_chunk_range(pp, num_send, chunk, p0, p1);
-          push_chunk(pp, s_tg, p0, p1, lane);
+          push_chunk(pp, s_tg, p0, p1, lane, nullptr, local_walker ? 1 : 0);
         }
         if (p.timing != nullptr && lane == 0) {
           long long* tm = p.timing + static_cast<size_t>(blockIdx.x) * kTimingCols;
@@ -810,7 +813,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int old = atomicAdd(done_ctr, 1);
       if (old == static_cast<int>(gridDim.x) - 1) {
         *done_ctr = 0;
-        if (PUSH) *pp.work_counter = 0;
+        if (PUSH) { *pp.work_counter = 0; if (pp.work_counter_local != nullptr) *pp.work_counter_local = 0; }
         if (p.tail.enabled) {
           // Every CTA's remote reductions were fenced at system scope before it counted itself.
           __threadfence_system();

@@ -565,6 +565,9 @@ class Runtime {
   int get_push_ctas() const { return push_ctas_; }
   // Push-only CTAs move rows with the bulk-copy engine (global -> shared -> owner's pool) instead of loads and stores.
   void set_bulk_push(bool on) { bulk_push_ = on; }
+  // With push-only CTAs: they ship only the pairs that go to other ranks; the push warps of the GEMM CTAs ship the
+  // pairs that stay on this rank (both walk the whole send list, each with its own claim counter).
+  void set_split_local(bool on) { split_local_ = on; }
   // The first `chunks` chunks of every push carry `pairs` pairs each (0 chunks = off).
   void set_push_head(int pairs, int chunks) {
     SEP_ASSERT(pairs >= 1 && pairs <= 32 && chunks >= 0, "head chunks: 1..32 pairs, a non-negative count");
@@ -985,6 +988,7 @@ class Runtime {
     p.pairs_per_chunk = pairs_per_chunk_; p.active_push_warps = active_push_warps_;
     p.head_pairs_per_chunk = head_pairs_per_chunk_; p.head_chunks = head_chunks_;
     p.push_ctas = push_ctas_; p.bulk_push = bulk_push_ ? 1 : 0;
+    p.split_local = split_local_ ? 1 : 0; p.work_counter_local = counters_ + 12 + (is_grads ? 1 : 0);
     fill_peers(p.peer_base); p.ctl = ctl_; p.own = rec;
     p.static_targets = st.region_id >= 0 ? 1 : 0;   // (a backward along a capacity-mode forward uses fixed regions too)
     p.own_arrival_count = own_count; p.own_arrival_target = st.pool_arrival_target.data_ptr<int>();
@@ -1588,6 +1592,7 @@ class Runtime {
   int head_pairs_per_chunk_ = 2, head_chunks_ = 0;
   int push_ctas_ = 0;
   bool bulk_push_ = false;
+  bool split_local_ = false;
   int active_push_warps_ = 0;
   bool router_on_tensor_cores_ = true;
   at::Tensor router_tiles_;            // zeros: every M tile of the router GEMM belongs to "expert" 0
@@ -1736,6 +1741,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_push_ctas", &Runtime::set_push_ctas)
       .def("get_push_ctas", &Runtime::get_push_ctas)
       .def("set_bulk_push", &Runtime::set_bulk_push)
+      .def("set_split_local", &Runtime::set_split_local)
       .def("set_active_push_warps", &Runtime::set_active_push_warps)
       .def("set_push_order", &Runtime::set_push_order)
       .def("set_router_on_tensor_cores", &Runtime::set_router_on_tensor_cores)

@@ -75,10 +75,11 @@ def sweep(args, buf, layers, routes, x, dy, rank, world, local):
                           f"capacity_factor={args.capacity_factor}; columns: mean over ranks of " + ", ".join(cols))
     for setting in args.sweep.split(","):
         f = [int(v) for v in setting.split(":")]
-        f += [2, 0, 0, 0][len(f) - 3:] if len(f) < 7 else []
-        ppc, warps, order, hp, hc, pctas, bulk = f[:7]
+        f += [2, 0, 0, 0, 0][len(f) - 3:] if len(f) < 8 else []
+        ppc, warps, order, hp, hc, pctas, bulk, split = f[:8]
         buf.runtime.set_push_ctas(pctas)
         buf.runtime.set_bulk_push(bool(bulk))
+        buf.runtime.set_split_local(bool(split))
         buf.runtime.set_pairs_per_chunk(ppc); buf.runtime.set_active_push_warps(warps); buf.runtime.set_push_order(order)
         buf.runtime.set_push_head(hp, hc)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -106,7 +107,7 @@ def sweep(args, buf, layers, routes, x, dy, rank, world, local):
             dist.all_reduce(t)
             t /= world
         v = t.tolist()
-        rank_zero_print(rank, f"chunk={ppc:2d} warps={warps:2d} order={order} head={hp}x{hc:5d} push_ctas={pctas:2d} bulk={bulk}: A[" + " ".join(f"{a:7.1f}" for a in v[0:5]) +
+        rank_zero_print(rank, f"chunk={ppc:2d} warps={warps:2d} order={order} head={hp}x{hc:5d} push_ctas={pctas:2d} bulk={bulk} split={split}: A[" + " ".join(f"{a:7.1f}" for a in v[0:5]) +
                         "]  Y_bwd[" + " ".join(f"{a:7.1f}" for a in v[5:10]) + f"]  step {v[10]:7.1f} us")
     barrier(world, local)
     if world > 1:
@@ -118,7 +119,7 @@ def main():
     ap = argparse.ArgumentParser()
     add_shape_args(ap)
     ap.add_argument("--steps", type=int, default=6)
-    ap.add_argument("--sweep", default="", help="comma-separated push settings 'pairs_per_chunk:push_warps:push_order[:head_pairs:head_chunks[:push_ctas[:bulk]]]' "
+    ap.add_argument("--sweep", default="", help="comma-separated push settings 'pairs_per_chunk:push_warps:push_order[:head_pairs:head_chunks[:push_ctas[:bulk[:split_local]]]]' "
                     "(push_warps 0 = all); prints one line per setting and kind, averaged over ranks")
     args = ap.parse_args()
     rank, world, local, dev, group = init_distributed()
