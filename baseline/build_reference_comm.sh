@@ -4,9 +4,9 @@
 # reference's own -DDISABLE_NVSHMEM switch (its setup.py turns the internode sources off when the
 # nvidia.nvshmem module cannot be imported; here the module is hidden behind an empty `nvidia` package
 # because its internode.cu needs <infiniband/mlx5dv.h>, which this image does not have).
-# Usage: baseline/build_reference_comm.sh [/path/to/reference]     (no GPU needed)
+# Usage: baseline/build_reference_comm.sh /path/to/reference     (no GPU needed)
 set -euo pipefail
-REF=${1:-/root/reference}
+REF=${1:?usage: build_reference_comm.sh /path/to/reference}
 HERE=$(cd "$(dirname "$0")" && pwd)
 WORK=$(mktemp -d /tmp/streamep_ref_build.XXXXXX)
 cp -r "$REF"/. "$WORK"/src

@@ -268,7 +268,7 @@ __global__ void __launch_bounds__(kMetaThreads, 1) dispatch_metadata_kernel(cons
   }
   __syncthreads();
   // 2b. every rank took the same region, and (capacity mode) every rank's layout fits it.  All ranks evaluate the
-  //     same numbers, so they all reach the same verdict and all turn a bad dispatch into an empty one.
+  //     same numbers, so they all come to the same conclusion and all turn a bad dispatch into an empty one.
   if (tid < R) {
     int bad = 0;
     if (ctl_inbox_misc(own, p.ctl, parity, tid)[0] != p.region_id) bad |= 2;
