@@ -30,6 +30,8 @@ def _lib():
     fn.restype = ctypes.c_int
     fn.argtypes = [ctypes.c_void_p] * 8 + [ctypes.c_int] * 4 + [ctypes.c_longlong, ctypes.c_void_p]
     lib.streamep_noalloc_last_error.restype = ctypes.c_char_p
+    lib.streamep_noalloc_device_status.restype = ctypes.c_int
+    lib.streamep_noalloc_device_status.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
     return lib
 
 
@@ -75,6 +77,10 @@ def test_no_alloc_entry_matches_regular_entry(native, H, I, freqs, klocal):
         check_close(f"o (call {call})", o, o_ref.float(), atol=2e-2 * scale * klocal, rtol=3e-2)
         assert (k_rem == 0).all()
         assert (done[k_total > 0] == 9 + call).all()
+        # a return of 0 only means "enqueued": the status block in the static array says whether a device wait gave up
+        code, where = ctypes.c_int(-1), ctypes.c_int(-1)
+        assert lib.streamep_noalloc_device_status(ctypes.byref(code), ctypes.byref(where)) == 0
+        assert code.value == 0
 
 
 def test_no_alloc_entry_rejects_oversize(native):
@@ -84,3 +90,5 @@ def test_no_alloc_entry_rejects_oversize(native):
     assert b"kNoAllocMaxTiles" in lib.streamep_noalloc_last_error()
     rc = lib.streamep_gemm_y_scatter_noalloc(None, 1, 1, 1, 1, 1, 1, 1, 4, 256, 256, 1, 0, None)
     assert rc == -2
+    rc = lib.streamep_gemm_y_scatter_noalloc(1, 1, 1, 1, 1, 1, 1, 1, -3, 256, 256, 1, 0, None)
+    assert rc == -2 and b"negative" in lib.streamep_noalloc_last_error()
