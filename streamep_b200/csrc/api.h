@@ -336,10 +336,12 @@ struct GemmParams {
   // Optional per-CTA time stamps, [gridDim.x][kTimingCols] int64 of %globaltimer nanoseconds (null = off):
   // 0 kernel start, 1 ns the operand pipeline stood still for tile gates, 2 first tile ready, 3 tiles this CTA had
   // finished when its push ended, 4 first push chunk
-  // claimed, 5 last push chunk done, 6 kernel end, 7 tiles this CTA multiplied.
+  // claimed, 5 last push chunk done, 6 kernel end, 7 tiles this CTA multiplied; and in SM clock cycles, of the
+  // thread that issues the MMAs: 8 its whole tile loop, 9 of that waiting for operands to land in shared memory,
+  // 10 of that waiting for the epilogue to give an accumulator back (11 unused).
   long long* timing;
 };
-constexpr int kTimingCols = 8;
+constexpr int kTimingCols = 12;
 
 // tmap_a / tmap_b: 128-byte CUtensorMap blobs (3-D, bf16, 128-byte swizzle) built by the host.
 // tmap_o0 / tmap_o1: output maps for the TMA-store epilogues (store, swiglu, dswiglu); box 32 rows x one

@@ -188,7 +188,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     if (p.timing != nullptr) {
       long long* tm = p.timing + static_cast<size_t>(blockIdx.x) * kTimingCols;
       tm[0] = static_cast<long long>(globaltimer_ns());
-      tm[1] = 0; tm[2] = 0; tm[3] = 0; tm[4] = 0; tm[5] = 0; tm[7] = 0;
+      tm[1] = 0; tm[2] = 0; tm[3] = 0; tm[4] = 0; tm[5] = 0; tm[7] = 0; tm[8] = 0; tm[9] = 0; tm[10] = 0;
     }
   }
   if (warp == 1) {
@@ -355,6 +355,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // ------------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
     int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
+    // with time stamps on: where this warp's time goes (SM cycles), see GemmParams::timing
+    const bool stamp = p.timing != nullptr;
+    long long cyc_operands = 0, cyc_accumulator = 0;
+    const long long cyc_begin = stamp ? clock64() : 0;
     for (int it = 0; ok; ++it) {
       int lin;
       if (dyn) {
@@ -367,11 +371,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const TileCoord t = decode_tile(p, lin, num_m);
       if (t.k_blocks == 0) continue;   // empty expert: the epilogue writes zeros on its own
       // all 32 lanes wait; the outcome is made warp-uniform so that no lane leaves ahead of elect_one / __syncwarp
+      const long long c_acc = stamp ? clock64() : 0;
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_empty[acc], acc_phase ^ 1, budget, p.status))) { ok = false; break; }
+      if (stamp) cyc_accumulator += clock64() - c_acc;
       tc_fence_after_sync();
       const uint32_t tmem_d = tmem_base + acc * BN;
       for (int kb = 0; kb < t.k_blocks; ++kb) {
+        const long long c_ops = stamp ? clock64() : 0;
         if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase, budget, p.status))) { ok = false; break; }
+        if (stamp) cyc_operands += clock64() - c_ops;
         unsigned char* sa = stage_base + stage * Cfg::kStageBytes;
         unsigned char* sb = sa + Cfg::kABytes;
         if (p.mode == kVarlenK && t.k_tail != 0 && kb == t.k_blocks - 1) {
@@ -405,6 +413,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
       }
       acc ^= 1; if (acc == 0) acc_phase ^= 1;
+    }
+    if (stamp && lane == 0) {
+      long long* tm = p.timing + static_cast<size_t>(blockIdx.x) * kTimingCols;
+      tm[8] = clock64() - cyc_begin; tm[9] = cyc_operands; tm[10] = cyc_accumulator;
     }
     if (!ok) report_failure(p.status, kStatusTimeoutPipeline, kKernelGemm, 1, p.rank, 0, 0, 0);
   } else if (warp < kGemmWarps) {

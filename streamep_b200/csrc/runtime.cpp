@@ -1211,8 +1211,12 @@ class Runtime {
     if (a.k_remaining.has_value()) p.k_remaining = a.k_remaining->data_ptr<int>();
     if (a.done_per_token.has_value()) p.done_per_token = reinterpret_cast<long long*>(a.done_per_token->data_ptr<int64_t>());
     p.seq = a.seq; p.num_topk = a.num_topk;
-    if (timing_.defined()) {   // one block of rows per kind of launch: epilogue index, +5 when a push is fused in
-      const int kind = a.epilogue + ((a.fused_push || a.fused_push_grads) ? 5 : 0);
+    if (timing_.defined()) {
+      // one block of rows per kind of launch: epilogue index, +5 when a push is fused in; 5 = row-tiled store (preact
+      // recompute, as opposed to dW in 0), 7 = scatter with an MN-major B (A_bwd, as opposed to Y in 2)
+      int kind = a.epilogue + ((a.fused_push || a.fused_push_grads) ? 5 : 0);
+      if (a.epilogue == kEpiStore && a.mode == kVarlenM) kind = 5;
+      if (a.epilogue == kEpiScatter && a.b_mn_major) kind = 7;
       p.timing = reinterpret_cast<long long*>(timing_.data_ptr<int64_t>()) + static_cast<int64_t>(kind) * num_sms() * kTimingCols;
     }
     p.num_ranks = num_ranks_; fill_peers(p.peer_base); p.ctl = ctl_;

@@ -6,8 +6,9 @@
 
 The GEMM kernels can record, per CTA, %globaltimer stamps (``Runtime.set_kernel_timing``): kernel start and end,
 nanoseconds the operand pipeline stood still for tile gates, when the first tile became ready, how many tiles the
-CTA had finished when its push ended, and when the CTA's push
-warps claimed their first chunk and finished their last.  This harness runs a few steps of the layer with the
+CTA had finished when its push ended, when the CTA's push
+warps claimed their first chunk and finished their last, and which share of its tile loop the thread that issues
+the MMAs spent waiting for operands (TMA not there yet) and for a free accumulator (epilogue not done yet).  This harness runs a few steps of the layer with the
 stamps on and prints, for each kind of launch, the split the reference's profile harness cannot give (its kernels
 carry no stamps; stream_ep/stream_moe/profile_pipeline.py:502-560 only has whole-kernel durations).
 All times are microseconds relative to the earliest CTA start of that launch on that rank.
@@ -22,12 +23,13 @@ import torch.distributed as dist
 
 from ._harness_common import add_shape_args, barrier, build_layers, init_distributed, rank_zero_print
 
-KINDS = {1: "GEMM-A SwiGLU", 2: "GEMM scatter (Y, then A_bwd: last launch wins)", 3: "GEMM-Y_bwd dSwiGLU",
-         0: "store (dW / preact: last launch wins)", 6: "dispatch (+) GEMM-A SwiGLU", 8: "dispatch_grads (+) GEMM-Y_bwd"}
+KINDS = {1: "GEMM-A SwiGLU", 6: "dispatch (+) GEMM-A SwiGLU", 2: "GEMM-Y (+ combine)", 3: "GEMM-Y_bwd dSwiGLU",
+         8: "dispatch_grads (+) GEMM-Y_bwd", 7: "GEMM-A_bwd (+ combine_grads)", 5: "preact recompute",
+         0: "dW1 + dW2 (last launch wins)"}
 
 
 def summarise(t: torch.Tensor) -> dict:
-    """``t``: [num_sms, 8] int64 stamps of one launch."""
+    """``t``: [num_sms, 12] int64 stamps of one launch."""
     live = t[:, 0] > 0
     if not bool(live.any()):
         return {}
@@ -37,6 +39,10 @@ def summarise(t: torch.Tensor) -> dict:
     out = {"ctas": int(live.sum()), "kernel_us": us(t[:, 6].max() - t0), "start_skew_us": us(t[:, 0].max() - t0),
            "gate_wait_us_mean": us(t[:, 1].mean()), "gate_wait_us_max": us(t[:, 1].max()),
            "tiles_per_cta": float(t[:, 7].mean())}
+    mma = t[:, 8] > 0
+    if bool(mma.any()):     # shares of the MMA-issuing thread's tile loop (SM cycles)
+        out["mma_wait_operands_frac"] = float((t[mma, 9] / t[mma, 8]).mean())
+        out["mma_wait_accumulator_frac"] = float((t[mma, 10] / t[mma, 8]).mean())
     gated = t[:, 2] > 0
     if bool(gated.any()):
         out["first_tile_ready_us_mean"] = us((t[gated, 2] - t0).mean())
@@ -163,7 +169,8 @@ def main():
         rank_zero_print(rank, "rank " + " ".join(f"{c:>24}" for c in keys))
         for r, rr in enumerate(every):
             if rr.get(k):
-                rank_zero_print(rank, f"{r:4d} " + " ".join(f"{rr[k].get(c, float('nan')):24.1f}" for c in keys))
+                rank_zero_print(rank, f"{r:4d} " + " ".join(
+                    f"{rr[k].get(c, float('nan')):24.3f}" if c.endswith("_frac") else f"{rr[k].get(c, float('nan')):24.1f}" for c in keys))
     barrier(world, local)
     if world > 1:
         dist.destroy_process_group()
