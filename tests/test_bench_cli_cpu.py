@@ -39,3 +39,20 @@ def test_comm_bench_routing_is_distinct_and_normalised():
     assert int(idx.min()) >= 0 and int(idx.max()) < 64
     assert all(len(set(row.tolist())) == 8 for row in idx)
     assert torch.allclose(w.sum(-1), torch.ones(257))
+
+
+def test_kernel_timing_summary_reads_every_stamp_column():
+    """The per-CTA stamp rows ([SMs, 12] int64) are turned into the figures the timing harness prints."""
+    from streamep_b200.stream_moe.kernel_timing import summarise
+    t = torch.zeros(4, 12, dtype=torch.int64)
+    assert summarise(t) == {}                                  # no CTA left a start stamp: that kind was not launched
+    #           start  gate_ns first  tiles@push push0 push1  end    tiles  mma_total mma_ops mma_acc spare
+    t[0] = torch.tensor([1000, 2000, 3000, 2, 1500, 9000, 11000, 7, 10000, 2500, 100, 0])
+    t[1] = torch.tensor([1400, 4000, 5000, 4, 1600, 7000, 21000, 9, 20000, 5000, 200, 0])
+    t[2] = torch.tensor([1200, 0, 0, 0, 0, 0, 15000, 0, 0, 0, 0, 0])   # a push-only CTA without gates or MMAs
+    s = summarise(t)
+    assert s["ctas"] == 3 and abs(s["kernel_us"] - 20.0) < 1e-9 and abs(s["start_skew_us"] - 0.4) < 1e-9
+    assert abs(s["gate_wait_us_mean"] - 2.0) < 1e-9 and abs(s["gate_wait_us_max"] - 4.0) < 1e-9
+    assert abs(s["first_tile_ready_us_mean"] - 3.0) < 1e-9      # (2.0 + 4.0) / 2 us after the earliest start
+    assert abs(s["push_end_us_max"] - 8.0) < 1e-9 and abs(s["tiles_done_at_push_end"] - 3.0) < 1e-9
+    assert abs(s["mma_wait_operands_frac"] - 0.25) < 1e-9 and abs(s["mma_wait_accumulator_frac"] - 0.01) < 1e-9
