@@ -19,6 +19,7 @@
 #include <atomic>
 #include <cstdio>
 #include <mutex>
+#include <type_traits>
 #include <cuda.h>
 
 #include "comm_common.cuh"
@@ -355,10 +356,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // ------------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
     int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
-    // with time stamps on: where this warp's time goes (SM cycles), see GemmParams::timing
-    const bool stamp = p.timing != nullptr;
+    // With time stamps on the loop also counts where this warp's time goes (SM cycles, see GemmParams::timing).  The
+    // loop is compiled twice: even a predicated-off clock read between "operands have landed" and the MMA issue
+    // cost 2 % of the whole step.
     long long cyc_operands = 0, cyc_accumulator = 0;
-    const long long cyc_begin = stamp ? clock64() : 0;
+    const long long cyc_begin = p.timing != nullptr ? clock64() : 0;
+    auto tile_loop = [&](auto timed) {
+    constexpr bool stamp = decltype(timed)::value;
     for (int it = 0; ok; ++it) {
       int lin;
       if (dyn) {
@@ -371,15 +375,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const TileCoord t = decode_tile(p, lin, num_m);
       if (t.k_blocks == 0) continue;   // empty expert: the epilogue writes zeros on its own
       // all 32 lanes wait; the outcome is made warp-uniform so that no lane leaves ahead of elect_one / __syncwarp
-      const long long c_acc = stamp ? clock64() : 0;
+      long long c_acc = 0;
+      if constexpr (stamp) c_acc = clock64();
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_empty[acc], acc_phase ^ 1, budget, p.status))) { ok = false; break; }
-      if (stamp) cyc_accumulator += clock64() - c_acc;
+      if constexpr (stamp) cyc_accumulator += clock64() - c_acc;
       tc_fence_after_sync();
       const uint32_t tmem_d = tmem_base + acc * BN;
       for (int kb = 0; kb < t.k_blocks; ++kb) {
-        const long long c_ops = stamp ? clock64() : 0;
+        long long c_ops = 0;
+        if constexpr (stamp) c_ops = clock64();
         if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase, budget, p.status))) { ok = false; break; }
-        if (stamp) cyc_operands += clock64() - c_ops;
+        if constexpr (stamp) cyc_operands += clock64() - c_ops;
         unsigned char* sa = stage_base + stage * Cfg::kStageBytes;
         unsigned char* sb = sa + Cfg::kABytes;
         if (p.mode == kVarlenK && t.k_tail != 0 && kb == t.k_blocks - 1) {
@@ -414,7 +420,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
       acc ^= 1; if (acc == 0) acc_phase ^= 1;
     }
-    if (stamp && lane == 0) {
+    };
+    if (p.timing != nullptr) tile_loop(std::true_type{}); else tile_loop(std::false_type{});
+    if (p.timing != nullptr && lane == 0) {
       long long* tm = p.timing + static_cast<size_t>(blockIdx.x) * kTimingCols;
       tm[8] = clock64() - cyc_begin; tm[9] = cyc_operands; tm[10] = cyc_accumulator;
     }

@@ -407,11 +407,13 @@ class Runtime {
     // up in an SM's load/store path and starve the epilogue warps of the same SM, so a push spread over all SMs
     // slows the GEMM to a third while it lasts.  On 8 ranks, 28 SMs that only push (about 20 GB/s each) keep the
     // links busy while the other 120 multiply at their stand-alone rate (dispatch (+) GEMM-A 680 -> 570-590 us,
-    // dispatch_grads (+) GEMM-Y_bwd 510 -> 435-460 us); on 2 and 4 ranks, where less of the push is remote, the
-    // two ways measured the same and every CTA keeps doing both.  The send list is walked tile by tile (order 1)
-    // and its first chunks are small: the consumers' first tiles complete after ~30 us instead of ~130.
+    // dispatch_grads (+) GEMM-Y_bwd 510 -> 435-460 us).  On 4 ranks the whole step measured 2.73-2.76 ms with 28
+    // (and with 36) push-only CTAs against 2.84-2.86 ms with none, 2.79 ms with 20 and 2.80 ms with 44; on 2 ranks,
+    // where half of the push stays local, the two ways measured the same and every CTA keeps doing both.  The send
+    // list is walked tile by tile (order 1) and its first chunks are small: the consumers' first tiles complete after
+    // ~30 us instead of ~130.
     if (num_ranks > 1) { push_order_ = 1; head_pairs_per_chunk_ = 2; head_chunks_ = 3000; }
-    if (num_ranks > 4) push_ctas_ = 28;
+    if (num_ranks > 2) push_ctas_ = 28;
     ctl_ = make_control_layout(num_ranks, num_channels, num_experts_cap);
     arena_bytes_ = static_cast<size_t>(arena_bytes) + ctl_.total_bytes;
     arena_bytes_ = (arena_bytes_ + (2u << 20) - 1) / (2u << 20) * (2u << 20);
