@@ -155,6 +155,8 @@ def main():
             dt = getattr(ev, "device_time_total", 0.0) or getattr(ev, "cuda_time_total", 0.0)
             if dt <= 0 or ev.device_type is None or "cuda" not in str(ev.device_type).lower():
                 continue
+            if ev.key.startswith("ProfilerStep") or ev.key.startswith("nccl:"):
+                continue    # the profiler's own step range and NCCL's user annotations are spans, not kernels
             label = classify(ev.key)
             a = agg.setdefault(label, [0, 0.0])
             a[0] += ev.count
